@@ -1,0 +1,32 @@
+"""Shared helpers for the parity tests."""
+import os
+
+import numpy as np
+import torch
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load_golden(name):
+    return dict(np.load(os.path.join(GOLDEN, name + ".npz")))
+
+
+def from_bits(arr, dtype):
+    """uint16 bit patterns (or fp32 values) stored in a fixture -> torch tensor of `dtype`."""
+    if dtype in (torch.bfloat16, torch.float16):
+        return torch.from_numpy(arr.view(np.int16).copy()).view(dtype)
+    return torch.from_numpy(arr.copy())
+
+
+def sets_equal_modulo_ties(idx_a, idx_b, score_row_fn=None):
+    """True when two index lists select the same set."""
+    return sorted(int(x) for x in idx_a) == sorted(int(x) for x in idx_b)
+
+
+def rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def max_abs(a, b):
+    return float((a.double() - b.double()).abs().max())
