@@ -1,0 +1,130 @@
+/*
+ * lcbsa -- B200-native block-sparse attention (BSA) forward for LongCat-Video.
+ *
+ * C ABI of liblcbsa.so.  Every entry point takes plain pointers and sizes; all buffers
+ * (inputs, outputs, workspace) are device memory owned by the caller; launches are
+ * asynchronous on the stream that is passed in (a cudaStream_t cast to void*).
+ *
+ * Every function that returns int returns LCBSA_OK (0) or a negative LCBSA_E* code;
+ * lcbsa_last_error() then gives a message for the calling thread.  Arguments are validated
+ * on the host before anything is launched; no entry point aborts or traps the device.
+ *
+ * Citations name files of the LongCat-Video project that each entry point stands in for.
+ */
+#ifndef LCBSA_H_
+#define LCBSA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LCBSA_VERSION 100
+
+enum {
+    LCBSA_OK = 0,
+    LCBSA_EINVAL = -1,       /* bad argument (shape, dtype, alignment, null pointer) */
+    LCBSA_EUNSUPPORTED = -2, /* valid request that no kernel here covers */
+    LCBSA_EWORKSPACE = -3,   /* workspace smaller than lcbsa_*_workspace_bytes() says */
+    LCBSA_ECUDA = -4,        /* a CUDA runtime / driver call failed */
+    LCBSA_EDEVICE = -5       /* a kernel gave up on a bounded wait and flagged it */
+};
+
+enum { LCBSA_BF16 = 0, LCBSA_FP16 = 1, LCBSA_FP32 = 2 };
+
+/* Which attention kernel lcbsa_attn_fwd runs. */
+enum {
+    LCBSA_ATTN_AUTO = 0, /* tcgen05 kernel when the shape allows it, otherwise the generic one */
+    LCBSA_ATTN_TC = 1,   /* TMA + tcgen05 + TMEM kernel (head_dim 128, 64-token blocks, bf16/fp16) */
+    LCBSA_ATTN_MMA = 2   /* generic warp-level MMA kernel (other block sizes / head dims) */
+};
+
+/* A [B, H, S, D] tensor as the DiT's attention layer hands it over
+ * (longcat_video/modules/attention.py:107-121): any B/H/S strides (in elements), D contiguous. */
+typedef struct LcbsaTensor {
+    void* data;
+    int32_t dtype; /* LCBSA_BF16 | LCBSA_FP16 | LCBSA_FP32 */
+    int32_t reserved;
+    int64_t size[4];
+    int64_t stride[4];
+} LcbsaTensor;
+
+/* Latent grid (T,H,W tokens, S = T*H*W) and the 3-D block ("chunk") that tiles it:
+ * latent_shape_* and chunk_3d_shape_* of flash_attn_bsa_3d
+ * (longcat_video/block_sparse_attention/bsa_interface.py:612-623). */
+typedef struct LcbsaGrid {
+    int32_t T, H, W;
+    int32_t ct, ch, cw;
+} LcbsaGrid;
+
+int lcbsa_version(void);
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char* lcbsa_last_error(void);
+
+/* Number of 3-D blocks of a grid (partial edge blocks count). */
+int lcbsa_num_blocks(const LcbsaGrid* g);
+
+/* int((1 - sparsity) * n_k_blocks) evaluated in double precision, i.e. exactly what
+ * bsa_interface.py:214 computes in Python. */
+int lcbsa_num_selected(double sparsity, int n_k_blocks);
+
+/*
+ * Mean-pool x over every 3-D block without rearranging it first.
+ * Stands in for rearrange_THW_to_3d_block + mean_pooling_compression
+ * (bsa_interface.py:600-604, 168-178).
+ * out: dense [B, H, Nblk, D], dtype of x.
+ */
+int lcbsa_pool(const LcbsaTensor* x, const LcbsaGrid* g, void* out, void* stream);
+
+/*
+ * Block scores and per-row top-k from pooled tensors; the scores never reach HBM.
+ * Stands in for cal_score + get_select_indices_topk_from_score (bsa_interface.py:180-184, 212-224).
+ * q_cmp: dense [BH, Nq, D]; k_cmp: dense [BH, Nk, D]; dtype as given.
+ * idx: int32 [BH, Nq, cap]; the first nsel entries of a row are the selected K-blocks in
+ *      ascending block order, the rest are -1.   cnt: int32 [BH, Nq] (= nsel).
+ * Ties: rows are ordered by (score descending, block index ascending).
+ */
+int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D,
+                     int nsel, int cap, int32_t* idx, int32_t* cnt, void* stream);
+
+/* Bytes of workspace lcbsa_block_select needs (pooled Q and pooled K). */
+size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq,
+                                    const LcbsaGrid* gk);
+
+/*
+ * The whole block-select stage: pool Q and K, score, top-k.
+ * Stands in for the gating part of _attention_bsa.forward (bsa_interface.py:547-549) with
+ * cdf_threshold=None.  idx/cnt as in lcbsa_score_topk with BH = B*H.
+ */
+int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk,
+                       int nsel, int cap, int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/*
+ * Block-sparse flash-attention forward over the listed K/V blocks, reading q/k/v and writing
+ * out directly in T,H,W token order.
+ * Stands in for the three rearrange_THW_to_3d_block copies, attn_fwd_bsa_varlen_triton and
+ * rearrange_3d_block_to_THW (bsa_interface.py:650-659, 290-341) and the Triton kernels
+ * _attn_fwd_bsa_varlen_align / _attn_fwd_bsa_varlen (flash_attn_bsa_varlen_mask.py:172-285, 35-153).
+ * idx: int32 [B*H, Nq, cap], cnt: int32 [B*H, Nq] (entries beyond cnt are ignored).
+ * out: [B, H, Sq, D], dtype of q.   lse: nullable, fp32 dense [B*H, Sq], natural log.
+ * impl: LCBSA_ATTN_*.
+ */
+int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaGrid* gq,
+                   const LcbsaGrid* gk, const int32_t* idx, const int32_t* cnt, int cap, float sm_scale,
+                   const LcbsaTensor* out, float* lse, int impl, void* stream);
+
+/*
+ * Synchronise the current device and report whether any kernel of this library flagged a
+ * bounded wait that ran out since the last call (LCBSA_EDEVICE), clearing the flag.
+ * Debug aid for tests; not part of the hot path.
+ */
+int lcbsa_check_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LCBSA_H_ */

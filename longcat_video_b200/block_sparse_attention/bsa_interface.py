@@ -1,0 +1,170 @@
+"""Host side of the B200 block-sparse attention: the reference's operator interface over liblcbsa.so.
+
+``flash_attn_bsa_3d`` keeps the name, arguments, defaults and error behaviour of
+``longcat_video/block_sparse_attention/bsa_interface.py:612-660`` so that
+``longcat_video/modules/attention.py:67`` can call it unchanged.  The stages underneath are
+exposed too, named after the reference functions they replace:
+
+  ``mean_pooling_compression_3d``  rearrange_THW_to_3d_block + mean_pooling_compression (:600, :168)
+  ``get_select_indices``           cal_score + get_select_indices_topk_from_score (:180, :212, :268)
+  ``attn_fwd_bsa_varlen``          attn_fwd_bsa_varlen_triton and the Triton kernels (:290)
+
+All computation happens in the CUDA kernels; PyTorch only allocates outputs and workspaces and
+provides the stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from .. import _lib as L
+
+
+def _prod(x: Sequence[int]) -> int:
+    return int(x[0]) * int(x[1]) * int(x[2])
+
+
+def num_blocks(latent_shape: Sequence[int], chunk: Sequence[int]) -> int:
+    g = L.grid_desc(latent_shape, chunk)
+    n = L.lib().lcbsa_num_blocks(ctypes.byref(g))
+    if n < 0:
+        L.check(n)
+    return n
+
+
+def num_selected(sparsity: float, n_k_blocks: int) -> int:
+    """``int((1 - sparsity) * Nk)`` -- bsa_interface.py:214, evaluated in double precision."""
+    return int(L.lib().lcbsa_num_selected(float(sparsity), int(n_k_blocks)))
+
+
+def _as_abi(t: torch.Tensor) -> torch.Tensor:
+    return t if L.abi_ok(t) else t.contiguous()
+
+
+def mean_pooling_compression_3d(x: torch.Tensor, latent_shape, chunk_3d_shape) -> torch.Tensor:
+    """Mean over every 3-D block of a T,H,W-ordered ``[B,H,S,D]`` tensor -> ``[B,H,Nblk,D]`` (dtype of x)."""
+    x = _as_abi(x)
+    B, H, S, D = x.shape
+    nb = num_blocks(latent_shape, chunk_3d_shape)
+    out = torch.empty(B, H, nb, D, dtype=x.dtype, device=x.device)
+    xd, g = L.tensor_desc(x), L.grid_desc(latent_shape, chunk_3d_shape)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().lcbsa_pool(ctypes.byref(xd), ctypes.byref(g), ctypes.c_void_p(out.data_ptr()),
+                                   L.current_stream(x.device)))
+    return out
+
+
+def get_select_indices_from_pooled(q_cmp: torch.Tensor, k_cmp: torch.Tensor, sparsity: float,
+                                   cdf_threshold: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-k block lists from pooled tensors: int32 ``idx [B,H,Nq,nsel]`` (ascending) and ``lens [B,H,Nq]``."""
+    if cdf_threshold is not None:
+        raise NotImplementedError("cdf_threshold selection is not built; use sparsity only")
+    if sparsity is None:
+        raise ValueError
+    q_cmp, k_cmp = q_cmp.contiguous(), k_cmp.contiguous()
+    B, H, Nq, D = q_cmp.shape
+    Nk = k_cmp.shape[2]
+    nsel = num_selected(sparsity, Nk)
+    cap = max(nsel, 1)
+    idx = torch.empty(B, H, Nq, cap, dtype=torch.int32, device=q_cmp.device)
+    cnt = torch.empty(B, H, Nq, dtype=torch.int32, device=q_cmp.device)
+    with torch.cuda.device(q_cmp.device):
+        L.check(L.lib().lcbsa_score_topk(q_cmp.data_ptr(), k_cmp.data_ptr(), L.dtype_code(q_cmp.dtype), B * H, Nq, Nk, D,
+                                         nsel, cap, idx.data_ptr(), cnt.data_ptr(), L.current_stream(q_cmp.device)))
+    return idx, cnt
+
+
+def get_select_indices(q: torch.Tensor, k: torch.Tensor, latent_shape_q, latent_shape_k, sparsity,
+                       cdf_threshold=None, chunk_3d_shape_q=(4, 4, 8), chunk_3d_shape_k=(4, 4, 8)
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The whole block-select stage on T,H,W-ordered q and k (pool, score, top-k) in one call."""
+    if sparsity is None and cdf_threshold is None:
+        raise ValueError
+    if cdf_threshold is not None:
+        raise NotImplementedError("cdf_threshold selection is not built; use sparsity only")
+    q, k = _as_abi(q), _as_abi(k)
+    B, H, _, D = q.shape
+    gq, gk = L.grid_desc(latent_shape_q, chunk_3d_shape_q), L.grid_desc(latent_shape_k, chunk_3d_shape_k)
+    nq, nk = num_blocks(latent_shape_q, chunk_3d_shape_q), num_blocks(latent_shape_k, chunk_3d_shape_k)
+    nsel = num_selected(sparsity, nk)
+    cap = max(nsel, 1)
+    qd, kd = L.tensor_desc(q), L.tensor_desc(k)
+    ws_bytes = L.lib().lcbsa_select_workspace_bytes(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk))
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
+    idx = torch.empty(B, H, nq, cap, dtype=torch.int32, device=q.device)
+    cnt = torch.empty(B, H, nq, dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        L.check(L.lib().lcbsa_block_select(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk), nsel, cap,
+                                           idx.data_ptr(), cnt.data_ptr(), ws.data_ptr(), ws_bytes,
+                                           L.current_stream(q.device)))
+    return idx, cnt
+
+
+def attn_fwd_bsa_varlen(q, k, v, sm_scale, block_indices, block_indices_lens, latent_shape_q, latent_shape_k,
+                        chunk_3d_shape_q, chunk_3d_shape_k, return_lse: bool = False, impl: int = L.ATTN_AUTO):
+    """Block-sparse attention forward over the listed K/V blocks; q/k/v and the result in T,H,W order."""
+    q, k, v = _as_abi(q), _as_abi(k), _as_abi(v)
+    B, H, Sq, D = q.shape
+    out = torch.empty(B, H, Sq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device) if return_lse else None
+    idx = block_indices.to(torch.int32).contiguous()
+    cnt = block_indices_lens.to(torch.int32).contiguous()
+    gq, gk = L.grid_desc(latent_shape_q, chunk_3d_shape_q), L.grid_desc(latent_shape_k, chunk_3d_shape_k)
+    qd, kd, vd, od = L.tensor_desc(q), L.tensor_desc(k), L.tensor_desc(v), L.tensor_desc(out)
+    with torch.cuda.device(q.device):
+        L.check(L.lib().lcbsa_attn_fwd(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(vd), ctypes.byref(gq), ctypes.byref(gk),
+                                       idx.data_ptr(), cnt.data_ptr(), idx.shape[-1], float(sm_scale), ctypes.byref(od),
+                                       lse.data_ptr() if lse is not None else None, int(impl),
+                                       L.current_stream(q.device)))
+    return (out, lse) if return_lse else out
+
+
+@torch.compiler.disable
+def flash_attn_bsa_3d(
+    q: torch.Tensor,  # [B, H, Sq, D]
+    k: torch.Tensor,  # [B, H, Skv, D]
+    v: torch.Tensor,  # [B, H, Skv, D]
+    latent_shape_q,
+    latent_shape_k,
+    # bsa_params
+    sparsity=0.875,
+    cdf_threshold=None,
+    chunk_3d_shape_q=[4, 4, 8],
+    chunk_3d_shape_k=[4, 4, 8],
+    allow_ragged: bool = False,
+) -> torch.Tensor:
+    """Drop-in for the reference's ``flash_attn_bsa_3d`` (same positional and keyword arguments).
+
+    ``allow_ragged=True`` (an extension; the reference asserts divisibility) lets T, H, W be any
+    size: edge blocks are partial, a partial block is pooled as (sum of present tokens) / block
+    size, absent keys take no part in the softmax and absent query rows are not written.
+    """
+    _, _, Sq, head_dim_q = q.shape
+    _, _, Sk, head_dim_k = k.shape
+    assert head_dim_q == head_dim_k
+    head_dim = head_dim_q
+    assert head_dim == v.shape[-1]
+    assert head_dim in {16, 32, 64, 128, 256}
+
+    Tq, Hq, Wq = latent_shape_q
+    Tk, Hk, Wk = latent_shape_k
+    assert Tq * Hq * Wq == Sq
+    assert Tk * Hk * Wk == Sk
+
+    tq, hq, wq = chunk_3d_shape_q
+    tk, hk, wk = chunk_3d_shape_k
+    if not allow_ragged:
+        assert Tq % tq == 0 and Hq % hq == 0 and Wq % wq == 0
+        assert Tk % tk == 0 and Hk % hk == 0 and Wk % wk == 0
+
+    if sparsity is None and cdf_threshold is None:
+        raise ValueError
+    if not q.is_cuda:
+        raise RuntimeError("flash_attn_bsa_3d (B200) needs CUDA tensors; there is no CPU path")
+
+    idx, cnt = get_select_indices(q, k, latent_shape_q, latent_shape_k, sparsity, cdf_threshold,
+                                  chunk_3d_shape_q, chunk_3d_shape_k)
+    return attn_fwd_bsa_varlen(q, k, v, 1 / head_dim ** 0.5, idx, cnt, latent_shape_q, latent_shape_k,
+                               chunk_3d_shape_q, chunk_3d_shape_k)

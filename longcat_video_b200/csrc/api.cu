@@ -1,0 +1,210 @@
+// C ABI of liblcbsa.so: argument validation and dispatch (see include/lcbsa.h).
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// Status words written by kernels whose bounded waits ran out: [0] = flag, [1..3] = where.
+__device__ unsigned int g_device_status[4];
+
+unsigned int* device_status_ptr() {
+    // one lookup per device; the symbol's address differs per device
+    static thread_local int cached_dev = -1;
+    static thread_local unsigned int* cached = nullptr;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (dev != cached_dev) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        cached = static_cast<unsigned int*>(p);
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+size_t elem_size(int dtype) { return dtype == LCBSA_FP32 ? 4 : 2; }
+
+bool grid_ok(const LcbsaGrid* g) {
+    return g && g->T > 0 && g->H > 0 && g->W > 0 && g->ct > 0 && g->ch > 0 && g->cw > 0 && g->ct < 1024 &&
+           g->ch < 1024 && g->cw < 1024;
+}
+
+// Checks a [B,H,S,D] operand against its grid and the 16-byte rules of the vector / TMA loads.
+int check_tensor(const char* name, const LcbsaTensor* t, const LcbsaGrid* g) {
+    if (!t || !t->data) return fail(LCBSA_EINVAL, "%s: null tensor", name);
+    if (t->dtype != LCBSA_BF16 && t->dtype != LCBSA_FP16 && t->dtype != LCBSA_FP32)
+        return fail(LCBSA_EINVAL, "%s: unknown dtype %d", name, t->dtype);
+    for (int i = 0; i < 4; ++i)
+        if (t->size[i] < 0) return fail(LCBSA_EINVAL, "%s: negative size", name);
+    const long long S = (long long)g->T * g->H * g->W;
+    if (t->size[2] != S)
+        return fail(LCBSA_EINVAL, "%s: sequence length %lld does not match the latent grid %dx%dx%d", name,
+                    (long long)t->size[2], g->T, g->H, g->W);
+    if (t->stride[3] != 1) return fail(LCBSA_EINVAL, "%s: the head_dim axis must be contiguous", name);
+    const size_t es = elem_size(t->dtype);
+    if (reinterpret_cast<uintptr_t>(t->data) % 16 != 0) return fail(LCBSA_EINVAL, "%s: data pointer not 16-byte aligned", name);
+    for (int i = 0; i < 3; ++i)
+        if ((t->stride[i] * (long long)es) % 16 != 0 || t->stride[i] < 0)
+            return fail(LCBSA_EINVAL, "%s: stride[%d] must be a non-negative multiple of 16 bytes", name, i);
+    if ((t->size[3] * (long long)es) % 16 != 0) return fail(LCBSA_EINVAL, "%s: head_dim row must be a multiple of 16 bytes", name);
+    return LCBSA_OK;
+}
+
+lcbsa::View view_of(const LcbsaTensor* t) { return lcbsa::View{t->data, t->stride[0], t->stride[1], t->stride[2]}; }
+
+int cuda_fail(cudaError_t e, const char* what, const char* why) {
+    if (why && *why) return fail(e == cudaErrorInvalidValue ? LCBSA_EUNSUPPORTED : LCBSA_ECUDA, "%s: %s", what, why);
+    return fail(LCBSA_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+}  // namespace
+
+extern "C" {
+
+int lcbsa_version(void) { return LCBSA_VERSION; }
+
+const char* lcbsa_last_error(void) { return g_err; }
+
+int lcbsa_num_blocks(const LcbsaGrid* g) {
+    if (!grid_ok(g)) return fail(LCBSA_EINVAL, "bad grid");
+    return lcbsa::make_geom(*g).nblk;
+}
+
+int lcbsa_num_selected(double sparsity, int n_k_blocks) { return (int)((1.0 - sparsity) * (double)n_k_blocks); }
+
+int lcbsa_pool(const LcbsaTensor* x, const LcbsaGrid* g, void* out, void* stream) {
+    if (!grid_ok(g)) return fail(LCBSA_EINVAL, "pool: bad grid");
+    if (int rc = check_tensor("pool input", x, g)) return rc;
+    if (!out) return fail(LCBSA_EINVAL, "pool: null output");
+    if (reinterpret_cast<uintptr_t>(out) % 16 != 0) return fail(LCBSA_EINVAL, "pool: output not 16-byte aligned");
+    const int D = (int)x->size[3];
+    const int lpr = (int)(D * elem_size(x->dtype) / 16);
+    if (lpr < 1 || lpr > 32 || (lpr & (lpr - 1)) != 0)
+        return fail(LCBSA_EUNSUPPORTED, "pool: head_dim row of %d bytes is not 16..512 bytes and a power of two", (int)(D * elem_size(x->dtype)));
+    cudaError_t e = lcbsa::launch_pool(x->dtype, view_of(x), (int)x->size[0], (int)x->size[1], D, lcbsa::make_geom(*g), out,
+                                       static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "pool", nullptr);
+    return LCBSA_OK;
+}
+
+int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, int nsel, int cap,
+                     int32_t* idx, int32_t* cnt, void* stream) {
+    if (!q_cmp || !k_cmp || !idx || !cnt) return fail(LCBSA_EINVAL, "score_topk: null pointer");
+    if (dtype != LCBSA_BF16 && dtype != LCBSA_FP16 && dtype != LCBSA_FP32) return fail(LCBSA_EINVAL, "score_topk: unknown dtype");
+    if (BH < 0 || Nq < 0 || Nk <= 0) return fail(LCBSA_EINVAL, "score_topk: bad sizes");
+    if (BH > 65535) return fail(LCBSA_EUNSUPPORTED, "score_topk: batch*heads above 65535");
+    if (nsel < 0 || nsel > Nk) return fail(LCBSA_EINVAL, "score_topk: nsel %d outside [0, %d]", nsel, Nk);
+    if (cap < nsel || cap < 1) return fail(LCBSA_EINVAL, "score_topk: list capacity %d below nsel %d", cap, nsel);
+    if (reinterpret_cast<uintptr_t>(q_cmp) % 16 || reinterpret_cast<uintptr_t>(k_cmp) % 16)
+        return fail(LCBSA_EINVAL, "score_topk: pooled tensors must be 16-byte aligned");
+    const char* why = "";
+    cudaError_t e = lcbsa::launch_score_topk(dtype, q_cmp, k_cmp, BH, Nq, Nk, D, nsel, cap, idx, cnt,
+                                             static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) return cuda_fail(e, "score_topk", why);
+    return LCBSA_OK;
+}
+
+size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk) {
+    if (!q || !k || !grid_ok(gq) || !grid_ok(gk)) return 0;
+    const size_t es = elem_size(q->dtype);
+    const size_t nq = (size_t)lcbsa::make_geom(*gq).nblk, nk = (size_t)lcbsa::make_geom(*gk).nblk;
+    const size_t bhd = (size_t)q->size[0] * (size_t)q->size[1] * (size_t)q->size[3] * es;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    return up(bhd * nq) + up(bhd * nk);
+}
+
+int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel,
+                       int cap, int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "block_select: bad grid");
+    if (int rc = check_tensor("q", q, gq)) return rc;
+    if (int rc = check_tensor("k", k, gk)) return rc;
+    if (q->dtype != k->dtype) return fail(LCBSA_EINVAL, "block_select: q and k dtypes differ");
+    if (q->size[0] != k->size[0] || q->size[1] != k->size[1] || q->size[3] != k->size[3])
+        return fail(LCBSA_EINVAL, "block_select: q and k disagree on batch, heads or head_dim");
+    const size_t need = lcbsa_select_workspace_bytes(q, k, gq, gk);
+    if (!workspace || workspace_bytes < need)
+        return fail(LCBSA_EWORKSPACE, "block_select: workspace of %zu bytes, need %zu", workspace_bytes, need);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(LCBSA_EINVAL, "block_select: workspace not 256-byte aligned");
+    const lcbsa::Geom ggq = lcbsa::make_geom(*gq), ggk = lcbsa::make_geom(*gk);
+    const size_t es = elem_size(q->dtype);
+    const size_t bhd = (size_t)q->size[0] * (size_t)q->size[1] * (size_t)q->size[3] * es;
+    unsigned char* qc = static_cast<unsigned char*>(workspace);
+    unsigned char* kc = qc + (bhd * ggq.nblk + 255) / 256 * 256;
+    if (int rc = lcbsa_pool(q, gq, qc, stream)) return rc;
+    if (int rc = lcbsa_pool(k, gk, kc, stream)) return rc;
+    return lcbsa_score_topk(qc, kc, q->dtype, (int)(q->size[0] * q->size[1]), ggq.nblk, ggk.nblk, (int)q->size[3], nsel, cap,
+                            idx, cnt, stream);
+}
+
+int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaGrid* gq, const LcbsaGrid* gk,
+                   const int32_t* idx, const int32_t* cnt, int cap, float sm_scale, const LcbsaTensor* out, float* lse,
+                   int impl, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "attn_fwd: bad grid");
+    if (int rc = check_tensor("q", q, gq)) return rc;
+    if (int rc = check_tensor("k", k, gk)) return rc;
+    if (int rc = check_tensor("v", v, gk)) return rc;
+    if (int rc = check_tensor("out", out, gq)) return rc;
+    if (!idx || !cnt || cap < 1) return fail(LCBSA_EINVAL, "attn_fwd: null block lists or zero capacity");
+    if (q->dtype != k->dtype || q->dtype != v->dtype || q->dtype != out->dtype) return fail(LCBSA_EINVAL, "attn_fwd: dtypes differ");
+    if (q->dtype == LCBSA_FP32) return fail(LCBSA_EUNSUPPORTED, "attn_fwd: attention kernels take bf16 or fp16");
+    for (int i : {0, 1, 3}) {
+        if (q->size[i] != k->size[i] || q->size[i] != v->size[i] || q->size[i] != out->size[i])
+            return fail(LCBSA_EINVAL, "attn_fwd: q, k, v, out disagree on batch, heads or head_dim");
+    }
+    if (!std::isfinite(sm_scale)) return fail(LCBSA_EINVAL, "attn_fwd: sm_scale is not finite");
+    if (q->size[0] * q->size[1] > 65535) return fail(LCBSA_EUNSUPPORTED, "attn_fwd: batch*heads above 65535");
+
+    lcbsa::AttnArgs a;
+    a.dtype = q->dtype;
+    a.q = view_of(q); a.k = view_of(k); a.v = view_of(v); a.o = view_of(out);
+    a.B = (int)q->size[0]; a.H = (int)q->size[1]; a.D = (int)q->size[3];
+    a.gq = lcbsa::make_geom(*gq); a.gk = lcbsa::make_geom(*gk);
+    a.idx = idx; a.cnt = cnt; a.cap = cap; a.sm_scale = sm_scale; a.lse = lse;
+    a.status = device_status_ptr();
+    if (!a.status) return fail(LCBSA_ECUDA, "attn_fwd: cannot resolve the device status words");
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const char* why = "";
+    cudaError_t e;
+    if (impl == LCBSA_ATTN_AUTO) impl = lcbsa::attn_tc_supported(a, &why) ? LCBSA_ATTN_TC : LCBSA_ATTN_MMA;
+    if (impl == LCBSA_ATTN_TC) {
+        if (!lcbsa::attn_tc_supported(a, &why)) return fail(LCBSA_EUNSUPPORTED, "attn_fwd (tcgen05): %s", why);
+        e = lcbsa::launch_attn_tc(a, st, &why);
+    } else if (impl == LCBSA_ATTN_MMA) {
+        e = lcbsa::launch_attn_mma(a, st, &why);
+    } else {
+        return fail(LCBSA_EINVAL, "attn_fwd: unknown impl %d", impl);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd", why);
+    return LCBSA_OK;
+}
+
+int lcbsa_check_device_status(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(LCBSA_ECUDA, "device synchronize: %s", cudaGetErrorString(e));
+    unsigned int h[4] = {0, 0, 0, 0};
+    e = cudaMemcpyFromSymbol(h, g_device_status, sizeof(h));
+    if (e != cudaSuccess) return fail(LCBSA_ECUDA, "status read: %s", cudaGetErrorString(e));
+    if (h[0] != 0) {
+        unsigned int z[4] = {0, 0, 0, 0};
+        cudaMemcpyToSymbol(g_device_status, z, sizeof(z));
+        return fail(LCBSA_EDEVICE, "a kernel gave up on a bounded wait: code %u at (%u, %u, %u)", h[0], h[1], h[2], h[3]);
+    }
+    return LCBSA_OK;
+}
+
+}  // extern "C"

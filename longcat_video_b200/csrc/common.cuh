@@ -1,0 +1,97 @@
+// Shared host/device helpers for the lcbsa kernels (internal header).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lcbsa.h"
+
+namespace lcbsa {
+
+// Strided view of one [B,H,S,D] operand as the kernels see it (element strides, D contiguous).
+struct View {
+    const void* data;
+    int64_t sb, sh, ss;  // batch, head, token strides in elements
+};
+
+// Block geometry of a latent grid, precomputed on the host.
+struct Geom {
+    int T, H, W;     // grid
+    int ct, ch, cw;  // block shape
+    int Nt, Nh, Nw;  // blocks per axis (ceil)
+    int nblk;        // Nt*Nh*Nw
+    int bs;          // ct*ch*cw
+    int ragged;      // 1 when some axis does not divide
+};
+
+inline Geom make_geom(const LcbsaGrid& g) {
+    Geom r;
+    r.T = g.T; r.H = g.H; r.W = g.W;
+    r.ct = g.ct; r.ch = g.ch; r.cw = g.cw;
+    r.Nt = (g.T + g.ct - 1) / g.ct;
+    r.Nh = (g.H + g.ch - 1) / g.ch;
+    r.Nw = (g.W + g.cw - 1) / g.cw;
+    r.nblk = r.Nt * r.Nh * r.Nw;
+    r.bs = g.ct * g.ch * g.cw;
+    r.ragged = (g.T % g.ct != 0) || (g.H % g.ch != 0) || (g.W % g.cw != 0);
+    return r;
+}
+
+template <typename T> struct DType;
+template <> struct DType<__nv_bfloat16> {
+    static constexpr int code = LCBSA_BF16;
+    __device__ static __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct DType<__half> {
+    static constexpr int code = LCBSA_FP16;
+    __device__ static __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct DType<float> {
+    static constexpr int code = LCBSA_FP32;
+    __device__ static __forceinline__ float to_f32(float v) { return v; }
+    __device__ static __forceinline__ float from_f32(float v) { return v; }
+};
+
+// Slot r of a block -> (lt, lh, lw) and the token offset relative to the block's first token.
+__device__ __forceinline__ void slot_coords(const Geom& g, int r, int& lt, int& lh, int& lw) {
+    lw = r % g.cw;
+    int q = r / g.cw;
+    lh = q % g.ch;
+    lt = q / g.ch;
+}
+
+__device__ __forceinline__ void block_coords(const Geom& g, int blk, int& bt, int& bh, int& bw) {
+    bw = blk % g.Nw;
+    int q = blk / g.Nw;
+    bh = q % g.Nh;
+    bt = q / g.Nh;
+}
+
+// Launchers implemented in the .cu files (host side). All return a cudaError_t from the launch.
+cudaError_t launch_pool(int dtype, const View& x, int B, int H, int D, const Geom& g, void* out, cudaStream_t st);
+
+cudaError_t launch_score_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel,
+                              int cap, int32_t* idx, int32_t* cnt, cudaStream_t st, const char** why);
+
+struct AttnArgs {
+    int dtype;
+    View q, k, v, o;
+    int B, H, D;
+    Geom gq, gk;
+    const int32_t* idx;
+    const int32_t* cnt;
+    int cap;
+    float sm_scale;
+    float* lse;  // nullable, [B*H, Sq]
+    unsigned int* status;  // device status words
+};
+
+cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);
+cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why);
+bool attn_tc_supported(const AttnArgs& a, const char** why);
+
+}  // namespace lcbsa
