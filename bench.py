@@ -1,0 +1,297 @@
+"""Benchmark of the BSA forward (block-select + block-sparse attention, plus the Ulysses all-to-all
+on more than one GPU) on synthetic tensors of the named workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--heads H] [--impl ours|reference]
+
+One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 prints ONE JSON line.
+  value      effective TFLOP/s of the whole job (algorithmic flops of the selected blocks / step time),
+             inputs resident in HBM;  ms_per_step is ms/layer.
+  e2e        the same metric through ``flash_attn_bsa_3d`` with HOST (pinned) inputs and output: the
+             host->device copies of q,k,v and the device->host copy of the result are inside the timing.
+  roofline   the attention kernel against the measured bf16 tensor peak (events around that launch);
+             roofline_select does the same for the block-select stage against the measured HBM copy rate.
+  cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
+             host cores, on a bounded sample of the same workload.
+``--impl reference`` times that CPU path alone (rank 0 only).
+Inputs (2.8 GB at 720p) are far larger than the 126 MB L2, so no flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from longcat_video_b200.synthetic import WORKLOADS, make_qkv  # noqa: E402
+
+METRIC = "bsa_fwd_effective_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram bytes (read + write) per attention launch from the committed ncu capture, scaled per unit of work;
+# see profiles/.  None until a capture exists for the workload.
+NCU_ATTN_DRAM_BYTES_PER_FLOP = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def n_selected(sparsity, nk):
+    return int((1 - sparsity) * nk)
+
+
+def algorithmic_flops(wl, heads, nsel):
+    """4 * B * H * Sq * (nsel * block) * D on legal grids; present rows / keys only on ragged ones."""
+    ct, ch, cw = wl.chunk
+    bs = ct * ch * cw
+    ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
+    if not ragged:
+        return 4.0 * wl.batch * heads * wl.sq * nsel * bs * wl.head_dim
+    return None  # counted from the lists at run time
+
+
+def flops_from_lists(wl, idx, cnt):
+    """Exact count for ragged grids: rows(i) * sum of present keys of the listed blocks."""
+    from oracle import bsa_oracle as O  # checker-side helper: block -> token map only
+    present_q = (O.token_map(wl.grid_q, wl.chunk) >= 0).sum(1).to(torch.float64)
+    present_k = (O.token_map(wl.grid_k, wl.chunk) >= 0).sum(1).to(torch.float64)
+    idx_c, cnt_c = idx.cpu().long(), cnt.cpu()
+    valid = torch.arange(idx_c.shape[-1])[None, None, None, :] < cnt_c[..., None]
+    keys = (present_k[idx_c.clamp_min(0)] * valid).sum(-1)  # [B,H,Nq]
+    return float(4.0 * wl.head_dim * (keys * present_q[None, None, :]).sum())
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if mx and x > 0.5 * mx] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_arm(wl, steps, warmup, heads_per_step=1):
+    """Times the CPU port of the reference path; each step is `heads_per_step` heads of the workload."""
+    from oracle.reference_path import bsa_forward_cpu
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v = make_qkv(wl, heads=heads_per_step)
+    nsel = n_selected(wl.sparsity, (wl.grid_k[0] // wl.chunk[0]) * (wl.grid_k[1] // wl.chunk[1]) * (wl.grid_k[2] // wl.chunk[2]))
+    fl = algorithmic_flops(wl, heads_per_step, nsel)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        bsa_forward_cpu(q, k, v, wl.grid_q, wl.grid_k, wl.sparsity, wl.chunk)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {"value": fl / t / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{heads_per_step} of {wl.heads} heads of {wl.name}, fp32, median of {len(times)} runs ({t * 1e3:.0f} ms each)"}, t
+
+
+def legal_twin(wl):
+    ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
+    return WORKLOADS["720p_legal"] if ragged else wl
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="720p_legal", choices=sorted(WORKLOADS))
+    ap.add_argument("--heads", type=int, default=None, help="total heads (default: the workload's 32)")
+    ap.add_argument("--attn-impl", default="auto", choices=["auto", "tc", "mma"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = WORKLOADS[args.workload]
+    heads = args.heads or wl.heads
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cpu_wl = legal_twin(wl)  # the reference asserts divisibility (bsa_interface.py:639-640)
+        base, t = cpu_reference_arm(cpu_wl, args.steps, args.warmup)
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": cpu_wl.name, "grid": list(cpu_wl.grid_k), "heads": 1, "sparsity": cpu_wl.sparsity,
+                           "block": list(cpu_wl.chunk), "note": "CPU port of the reference's PyTorch block-select + masked SDPA"},
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    from longcat_video_b200 import _lib as L
+    from longcat_video_b200.block_sparse_attention import bsa_interface as B
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    attn_impl = {"auto": L.ATTN_AUTO, "tc": L.ATTN_TC, "mma": L.ATTN_MMA}[args.attn_impl]
+    peaks, peak_src = load_peaks()
+
+    if world > 1:
+        from longcat_video_b200.context_parallel import bench_support
+        return bench_support.run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, attn_impl)
+
+    # ------------------------------------------------------------------ single GPU
+    q_h, k_h, v_h = (t.pin_memory() for t in make_qkv(wl, heads=heads))
+    q, k, v = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h))
+    scale = wl.head_dim ** -0.5
+    launches = {"n": 0}
+
+    def step(events=None):
+        if events:
+            events[0].record()
+        idx, cnt = B.get_select_indices(q, k, wl.grid_q, wl.grid_k, wl.sparsity, None, wl.chunk, wl.chunk)
+        if events:
+            events[1].record()
+        out = B.attn_fwd_bsa_varlen(q, k, v, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk, impl=attn_impl)
+        if events:
+            events[2].record()
+        launches["n"] += 4  # pool(q), pool(k), score+top-k, attention
+        return idx, cnt, out
+
+    for _ in range(args.warmup):
+        idx, cnt, out = step()
+    torch.cuda.synchronize()
+    L.check(L.lib().lcbsa_check_device_status())
+    nsel = int(cnt.flatten()[0])
+    flops = algorithmic_flops(wl, heads, nsel)
+    if flops is None:
+        flops = flops_from_lists(wl, idx, cnt)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches["n"] = 0
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        step(ev[i])
+    end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    L.check(L.lib().lcbsa_check_device_status())
+    ms = start.elapsed_time(end) / args.steps
+    ms_select = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    ms_attn = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    gpu_launches = launches["n"]
+
+    es = q.element_size()
+    select_bytes = es * wl.batch * heads * (wl.sq + wl.sk) * wl.head_dim  # read Q and K once
+    attn_tf = flops / ms_attn / 1e9
+    roofline = {"bound": "tensor", "kernel": "attn_tc_kernel" if attn_impl != L.ATTN_MMA else "attn_mma_kernel",
+                "achieved": attn_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
+                "peak_source": f"{peak_src} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
+                "ms_per_launch": ms_attn,
+                "traffic": (NCU_ATTN_DRAM_BYTES_PER_FLOP * flops) if NCU_ATTN_DRAM_BYTES_PER_FLOP else None}
+    sel_gbs = select_bytes / ms_select / 1e6
+    roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_topk_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
+                       "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"], "peak_source": peak_src, "ms_per_stage": ms_select,
+                       "traffic": None}
+
+    # ------------------------------------------------------------------ end to end from host buffers
+    e2e = None
+    if not args.skip_e2e:
+        out_h = torch.empty(q_h.shape, dtype=q_h.dtype).pin_memory()
+        qd, kd, vd = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
+        ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
+
+        def e2e_step():
+            qd.copy_(q_h, non_blocking=True)
+            kd.copy_(k_h, non_blocking=True)
+            vd.copy_(v_h, non_blocking=True)
+            o = B.flash_attn_bsa_3d(qd, kd, vd, wl.grid_q, wl.grid_k, allow_ragged=ragged, **params)
+            out_h.copy_(o, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, min(args.steps, 10))
+        s2.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e2.record()
+        torch.cuda.synchronize()
+        ms_e2e = s2.elapsed_time(e2) / n_e2e
+        e2e = {"value": flops / ms_e2e / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": int(q_h.numel() + k_h.numel() + v_h.numel()) * es,
+               "d2h_bytes_per_step": int(out_h.numel()) * es}
+
+    cpu_baseline = None
+    if not args.skip_cpu_baseline:
+        cpu_baseline, _ = cpu_reference_arm(legal_twin(wl), steps=3, warmup=1)
+
+    line = {"metric": METRIC, "value": flops / ms / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "grid_q": list(wl.grid_q), "grid_k": list(wl.grid_k), "heads": heads,
+                       "head_dim": wl.head_dim, "block": list(wl.chunk), "sparsity": wl.sparsity, "selected_blocks": nsel,
+                       "algorithmic_tflop": flops / 1e12, "ms_select": ms_select, "ms_attention": ms_attn,
+                       "l2": "inputs (q,k,v,out) exceed the 126 MB L2; no flush between iterations", "parallelism": "1 GPU"},
+            "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "clocks": clocks, "gpu_launches": gpu_launches}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -63,8 +63,7 @@ struct TcParams {
     int nq;         // query blocks per head
     int bh_total;   // B*H
     int heads;      // H
-    int merge_q;    // 0: batch folded into the head axis of the map, 1: into the T axis
-    int merge_k;
+    int merge_q, merge_k, merge_v, merge_o;  // 0: batch folded into the head axis of the map, 1: into the T axis
     int Tq, Tk;     // frames (for merge == 1 coordinates)
     Geom gq, gk;
     float scale2;   // sm_scale * log2(e)
@@ -401,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     ok = mbar_wait(bar_kv_empty(stage), ((ring / kStages) & 1) ^ 1, ctl, 20, ring);
                     if (!ok) break;
                     if (lane == 0) {
-                        const Coord cc = block_coord(P.gk, sel4(pend0, pend1, pend2, pend3, t), b, h, P.heads, P.merge_k, P.Tk);
+                        const Coord cc = block_coord(P.gk, sel4(pend0, pend1, pend2, pend3, t), b, h, P.heads, ev.is_pv ? P.merge_v : P.merge_k, P.Tk);
                         const CUtensorMap* tm = ev.is_pv ? &P.tm_v : &P.tm_k;
                         const uint32_t dst = sbase + kOffKV + stage * kTileBytes;
                         mbar_arrive_tx(bar_kv_full(stage), kTileBytes);
@@ -679,7 +678,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     for (int hh2 = 0; hh2 < 2; ++hh2) {
                         const int tt2 = 2 * p + hh2, qq = g * kTilesPerWork + tt2;
                         if (qq >= P.nq) continue;
-                        const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_q, P.Tq);
+                        const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
                         const uint32_t src = sbase + kOffQ + tt2 * kTileBytes;
                         tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
                         tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
@@ -766,18 +765,9 @@ bool attn_tc_supported(const AttnArgs& a, const char** why) {
     }
     const View* vs[4] = {&a.q, &a.k, &a.v, &a.o};
     const Geom* gs[4] = {&a.gq, &a.gk, &a.gk, &a.gq};
-    int mq = -2, mk = -2;
     for (int i = 0; i < 4; ++i) {
-        const int m = merge_mode(*vs[i], a.B, a.H, *gs[i]);
-        if (m < 0) { *why = "batch stride cannot be folded into a 5-D tensor map"; return false; }
+        if (merge_mode(*vs[i], a.B, a.H, *gs[i]) < 0) { *why = "batch stride cannot be folded into a 5-D tensor map"; return false; }
         if (vs[i]->ss * 2 >= (1ll << 40) || vs[i]->sh * 2 >= (1ll << 40)) { *why = "stride too large for a tensor map"; return false; }
-        if (i == 0 || i == 3) {
-            if (mq != -2 && mq != m) { *why = "q and out fold the batch axis differently"; return false; }
-            mq = m;
-        } else {
-            if (mk != -2 && mk != m) { *why = "k and v fold the batch axis differently"; return false; }
-            mk = m;
-        }
     }
     return true;
 }
@@ -786,14 +776,15 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
     if (a.gq.nblk == 0 || a.B * a.H == 0) return cudaSuccess;
     static thread_local TcParams P;
     const int mq = merge_mode(a.q, a.B, a.H, a.gq), mk = merge_mode(a.k, a.B, a.H, a.gk);
+    const int mv = merge_mode(a.v, a.B, a.H, a.gk), mo = merge_mode(a.o, a.B, a.H, a.gq);
     if (!make_map(&P.tm_q, a.dtype, a.q, a.B, a.H, a.gq, mq) || !make_map(&P.tm_k, a.dtype, a.k, a.B, a.H, a.gk, mk) ||
-        !make_map(&P.tm_v, a.dtype, a.v, a.B, a.H, a.gk, mk) || !make_map(&P.tm_o, a.dtype, a.o, a.B, a.H, a.gq, mq)) {
+        !make_map(&P.tm_v, a.dtype, a.v, a.B, a.H, a.gk, mv) || !make_map(&P.tm_o, a.dtype, a.o, a.B, a.H, a.gq, mo)) {
         *why = "cuTensorMapEncodeTiled rejected a tensor";
         return cudaErrorInvalidValue;
     }
     P.idx = a.idx; P.cnt = a.cnt; P.lse = a.lse; P.status = a.status;
     P.cap = a.cap; P.nq = a.gq.nblk; P.bh_total = a.B * a.H; P.heads = a.H;
-    P.merge_q = mq; P.merge_k = mk; P.Tq = a.gq.T; P.Tk = a.gk.T;
+    P.merge_q = mq; P.merge_k = mk; P.merge_v = mv; P.merge_o = mo; P.Tq = a.gq.T; P.Tk = a.gk.T;
     P.gq = a.gq; P.gk = a.gk;
     P.scale2 = a.sm_scale * 1.4426950408889634f;
     P.is_bf16 = a.dtype == LCBSA_BF16;
