@@ -50,7 +50,7 @@ def test_pool_strided_inputs(wl_data):
     wl, q, k, _ = wl_data
     ref = O.pool(k, wl.grid_k, wl.chunk)
     k_bshd = k.cuda().permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)  # shape [B,H,S,D], memory [B,S,H,D]
-    assert not k_bshd.is_contiguous()
+    assert k.shape[1] == 1 or not k_bshd.is_contiguous()
     got = B.mean_pooling_compression_3d(k_bshd, wl.grid_k, wl.chunk).cpu()
     assert torch.equal(_bits(got), _bits(ref))
     Bsz, H, S, D = k.shape
