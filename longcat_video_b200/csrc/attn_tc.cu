@@ -13,16 +13,23 @@
 // upper 16 lanes of the same columns, so that one softmax warpgroup (128 threads, one TMEM lane each)
 // serves both with every lane busy.
 //
-//   warps 0-3 : softmax warpgroup of pair 0      warp 8 : TMA producer (Q tiles, K/V tile ring)
-//   warps 4-7 : softmax warpgroup of pair 1      warp 9 : MMA issuer (one elected lane)
+//   warps 0-3 : softmax warpgroup of pair 0      warps 8,13,14,15 : TMA producers (Q tiles, ring of K/V slots)
+//   warps 4-7 : softmax warpgroup of pair 1      warps 9,10 : S = Q K^T issuers of pair 0 and pair 1
+//   warps 11,12 : O += P V issuers of pair 0 and pair 1
+// One thread can start a tcgen05.mma only about every 120 cycles (measured on B200, whatever the
+// shape), while these MMAs carry 32-64 cycles of math; four issuing warps bring the issue rate to
+// the rate of the tensor pipe.  The same holds for the 5-D TMA copies, hence four producers.
 //
-// Per selected K/V block and tile:  S = Q K^T  (M64 N64 K128, fp32 in TMEM)  ->  softmax warpgroup
+// Per selected K/V block and tile:  S = Q K^T  (M64 N64 K128, fp32 in TMEM)  ->  the softmax warpgroup
 // reads S with tcgen05.ld, exp2 online softmax in registers, P (input dtype) into swizzled shared
-// memory  ->  O += P V  (M64 N128 K64, fp32 in TMEM).  The running maximum baked into O is only
-// refreshed when the row maximum grows by more than 2^8 (the accumulated values stay finite and the
-// result is unchanged after the final division), so O is rarely rescaled in TMEM.
-// The MMA warp interleaves the two pairs (PV of one pair, then the next S of the same pair, then
-// the other pair) so the tensor pipe has work while a warpgroup does its softmax.
+// memory  ->  O += P V  (M64 N128 K64, fp32 in TMEM).  S is double-buffered in TMEM and is issued
+// up to two iterations ahead of the PV that consumes it, so a warpgroup finds its next S ready when
+// it finishes a round and the tensor pipe always has queued work from both pairs.
+// The running maximum baked into O is only refreshed when the row maximum grows by more than 2^8
+// (the accumulated values stay finite and the result is unchanged after the final division), so O is
+// rarely rescaled in TMEM.
+//
+// TMEM columns (512): S[pair][buf] at 64*(2*pair+buf), O[pair] at 256 + 128*pair.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA records where, raises an abort
 // flag that all roles poll, drains its outstanding bulk copies, frees its TMEM and returns.
@@ -35,21 +42,26 @@ namespace lcbsa {
 namespace {
 
 constexpr int kD = 128;
-constexpr int kBlk = 64;                 // tokens per query / key block
-constexpr int kTileBytes = kBlk * kD * 2;  // 16 KiB: one Q, K, V or O tile
+constexpr int kBlk = 64;                    // tokens per query / key block
+constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB: one Q, K, V or O tile
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128 B, 128B-swizzled
 constexpr int kPBytes = kBlk * kBlk * 2;    // 8 KiB: one P tile
-constexpr int kStages = 8;                  // K/V tile ring
+constexpr int kSlots = 4;                   // ring of K/V slots; a slot holds the tiles of both halves of a pair
+constexpr int kSlotBytes = 2 * kTileBytes;
 constexpr int kTilesPerWork = 4;
-constexpr int kThreads = 320;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kThreads = 512;
+// setmaxnreg per warpgroup: (184 + 184 + 72 + 72) * 128 threads = the 128 * 512 registers the CTA starts with
+constexpr int kRegsSoftmax = 184, kRegsOther = 72;
+constexpr unsigned kSpinsBeforeClock = 1u << 12;     // failed try_waits before the clock is consulted
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffQ = 0;                                   // 4 tiles (reused to stage O)
 constexpr int kOffKV = kOffQ + kTilesPerWork * kTileBytes;  // ring
-constexpr int kOffP = kOffKV + kStages * kTileBytes;        // 4 P tiles
+constexpr int kOffP = kOffKV + kSlots * kSlotBytes;         // 4 P tiles
 constexpr int kOffBar = kOffP + kTilesPerWork * kPBytes;
-constexpr int kNumBars = 2 * kStages + 2 /*q_full*/ + 2 /*q_empty*/ + 2 /*s_full*/ + 2 /*p_full*/ + 2 /*pv_done*/ + 2 /*o_staged*/;
+// barriers: slot_full[4] slot_empty[4] q_full[2] q_empty[2] s_full[2][2] p_full[2] pv_done[2] o_staged[2] s_free[2][2]
+constexpr int kNumBars = 2 * kSlots + 2 + 2 + 4 + 2 + 2 + 2 + 4;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;
 constexpr int kSmemBytes = kOffMisc + 64 + 1024;  // + slack for the 1024-byte alignment
 
@@ -70,18 +82,26 @@ struct TcParams {
     int is_bf16;
 #ifdef LCBSA_TC_DEBUG
     float* dbg;     // [4 tiles][64 rows][64] raw S of the first work item's first iteration, then [4][64][128] raw O
+    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: producer, MMA thread, softmax warps 0 and 4
 #endif
 };
+
+#ifdef LCBSA_TC_DEBUG
+#define LCBSA_TS(role, tag)                                                        \
+    do {                                                                           \
+        if (P.ts && blockIdx.x == 0 && ts_n < 4096) {                              \
+            P.ts[((role) * 4096 + ts_n) * 2] = (tag);                              \
+            P.ts[((role) * 4096 + ts_n) * 2 + 1] = clock64();                      \
+            ++ts_n;                                                                \
+        }                                                                          \
+    } while (0)
+#else
+#define LCBSA_TS(role, tag) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------------------------------ PTX
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -109,15 +129,15 @@ struct Ctl {
     unsigned int* status;   // global status words
 };
 
-// Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
-    const unsigned long long t0 = globaltimer();
+// Reached only after many failed tries: bound the wait by the cycle counter and flag a timeout.
+__device__ __forceinline__ bool mbar_wait_timeout(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int k = 0; k < 32; ++k)
+        for (int k = 0; k < 64; ++k)
             if (mbar_try(bar, parity)) return true;
         if (*c.abort) return false;
-        if (globaltimer() - t0 > kWaitLimitNs) {
+        if (clock64() - t0 > kWaitLimitCycles) {
             *c.abort = 1;
             if (atomicCAS(c.status, 0u, code) == 0u) {
                 c.status[1] = blockIdx.x;
@@ -129,14 +149,43 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const
         }
     }
 }
-// Called by all 32 lanes of a warp; the verdict is made warp-uniform so that the warp-collective
-// tcgen05 instructions that follow are never reached by only some of the lanes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
-    bool ok = mbar_try(bar, parity);
-    if (!ok) ok = mbar_wait_slow(bar, parity, c, code, it);
-    return __all_sync(0xffffffffu, ok);
+// Bounded wait of one thread. Returns false when the CTA is aborting (this wait or another one ran out).
+// try_wait itself blocks for a hardware-defined interval, so the loop turns over rarely.
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
+    unsigned spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if (*c.abort) return false;
+        if (++spins >= kSpinsBeforeClock) return mbar_wait_timeout(bar, parity, c, code, it);
+    }
+    return true;
 }
-
+// Bounded wait until a shared-memory word holds `want` (the producers publish which use of a ring slot
+// they have armed; see the MMA issuers).
+__device__ __forceinline__ bool word_wait_thread(const volatile uint32_t* word, uint32_t want, const Ctl& c, unsigned code,
+                                                 unsigned it) {
+    unsigned spins = 0;
+    long long t0 = 0;
+    while (*word != want) {
+        if (*c.abort) return false;
+        if (++spins == (kSpinsBeforeClock << 4)) t0 = clock64();
+        if (spins > (kSpinsBeforeClock << 4) && (spins & 1023u) == 0 && clock64() - t0 > kWaitLimitCycles) {
+            *c.abort = 1;
+            if (atomicCAS(c.status, 0u, code) == 0u) {
+                c.status[1] = blockIdx.x;
+                c.status[2] = threadIdx.x;
+                c.status[3] = it;
+            }
+            __threadfence();
+            return false;
+        }
+    }
+    return true;
+}
+// The same for all 32 lanes of a warp; the verdict is made warp-uniform so that the warp-collective
+// tcgen05 instructions that follow are never reached by only some of the lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
+    return __all_sync(0xffffffffu, mbar_wait_thread(bar, parity, c, code, it));
+}
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2,
                                             int c3, int c4) {
     asm volatile(
@@ -247,27 +296,27 @@ __device__ __forceinline__ uint32_t instr_desc(bool bf16, int M, int N, int b_mn
 
 // ------------------------------------------------------------------------------------------ schedule
 
-// The order in which K and V tiles enter the ring is the order in which the MMA warp first uses them.
-// For a work item with per-pair iteration counts n0, n1 the events are
-//   S(0,0) S(1,0) | PV(0,0) S(0,1) PV(1,0) S(1,1) | PV(0,1) S(0,2) ...
-// Event e of this list: e < 2 -> S(e, 0); otherwise k = e-2: pair = (k>>1)&1, i = k>>2, PV if (k&1)==0 else S(i+1).
+// The order in which K and V slots enter the ring is the order in which the MMA thread first uses them.
+// For a work item whose pairs run n0 and n1 iterations the events are
+//   S(0,0) S(1,0) S(0,1) S(1,1) | PV(0,0) S(0,2) PV(1,0) S(1,2) | PV(0,1) S(0,3) PV(1,1) S(1,3) | ...
+// (S runs two iterations ahead of the PV of the same pair; events past a pair's count are skipped).
 struct Event {
     int pair, iter, is_pv, valid;
 };
 __device__ __forceinline__ Event event_at(int e, int n0, int n1) {
     Event ev;
-    if (e < 2) {
-        ev.pair = e; ev.iter = 0; ev.is_pv = 0;
+    if (e < 4) {
+        ev.pair = e & 1; ev.iter = e >> 1; ev.is_pv = 0;
     } else {
-        const int k = e - 2;
+        const int k = e - 4;
         ev.pair = (k >> 1) & 1;
         ev.is_pv = (k & 1) == 0;
-        ev.iter = (k >> 2) + (ev.is_pv ? 0 : 1);
+        ev.iter = (k >> 2) + (ev.is_pv ? 0 : 2);
     }
     ev.valid = ev.iter < (ev.pair ? n1 : n0);
     return ev;
 }
-__device__ __forceinline__ int num_events(int n0, int n1) { return 2 + 4 * max(n0, n1); }
+__device__ __forceinline__ int num_events(int n0, int n1) { return 4 + 4 * max(n0, n1); }
 
 __device__ __forceinline__ int sel4(int a0, int a1, int a2, int a3, int i) {
     return i == 0 ? a0 : i == 1 ? a1 : i == 2 ? a2 : a3;
@@ -288,6 +337,10 @@ __device__ __forceinline__ Coord block_coord(const Geom& g, int blk, int b, int 
     return c;
 }
 
+__device__ __forceinline__ int clamp_cnt(const TcParams& P, int bh, int qt) {
+    return qt < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
+}
+
 // ------------------------------------------------------------------------------------------ kernel
 
 __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_constant__ TcParams P) {
@@ -295,33 +348,42 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + kOffBar;
-    auto bar_kv_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_kv_empty = [&](int s) { return bar0 + 8u * (kStages + s); };
-    auto bar_q_full = [&](int p) { return bar0 + 8u * (2 * kStages + p); };
-    auto bar_q_empty = [&](int p) { return bar0 + 8u * (2 * kStages + 2 + p); };
-    auto bar_s_full = [&](int p) { return bar0 + 8u * (2 * kStages + 4 + p); };
-    auto bar_p_full = [&](int p) { return bar0 + 8u * (2 * kStages + 6 + p); };
-    auto bar_pv_done = [&](int p) { return bar0 + 8u * (2 * kStages + 8 + p); };
-    auto bar_o_staged = [&](int p) { return bar0 + 8u * (2 * kStages + 10 + p); };
+    auto bar_slot_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_slot_empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
+    auto bar_q_full = [&](int p) { return bar0 + 8u * (2 * kSlots + p); };
+    auto bar_q_empty = [&](int p) { return bar0 + 8u * (2 * kSlots + 2 + p); };
+    auto bar_s_full = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 4 + 2 * p + buf); };
+    auto bar_p_full = [&](int p) { return bar0 + 8u * (2 * kSlots + 8 + p); };
+    auto bar_pv_done = [&](int p) { return bar0 + 8u * (2 * kSlots + 10 + p); };
+    auto bar_o_staged = [&](int p) { return bar0 + 8u * (2 * kSlots + 12 + p); };
+    auto bar_s_free = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 14 + 2 * p + buf); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
+    volatile uint32_t* slot_use = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc + 16);  // [kSlots] use number armed
     const Ctl ctl{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef LCBSA_TC_DEBUG
+    int ts_n = 0;
+#endif
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar_kv_full(s), 1);
-            mbar_init(bar_kv_empty(s), 1);
+        for (int s = 0; s < kSlots; ++s) slot_use[s] = 0xffffffffu;
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(bar_slot_full(s), 1);
+            mbar_init(bar_slot_empty(s), 1);
         }
         for (int p = 0; p < 2; ++p) {
             mbar_init(bar_q_full(p), 1);
             mbar_init(bar_q_empty(p), 1);
-            mbar_init(bar_s_full(p), 1);
-            mbar_init(bar_p_full(p), 128);
+            mbar_init(bar_s_full(p, 0), 1);
+            mbar_init(bar_s_full(p, 1), 1);
+            mbar_init(bar_p_full(p), 4);    // one elected arrival per softmax warp
             mbar_init(bar_pv_done(p), 1);
-            mbar_init(bar_o_staged(p), 128);
+            mbar_init(bar_o_staged(p), 4);
+            mbar_init(bar_s_free(p, 0), 4);
+            mbar_init(bar_s_free(p, 1), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -338,23 +400,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     const long long total_work = (long long)P.bh_total * groups;
     const bool bf16 = P.is_bf16 != 0;
 
-    if (warp == 8) {
-        // ================================================================== TMA producer
-        unsigned ring = 0;  // tiles pushed so far
+    // Register budgets are set inside each role's own branch: the compiler sizes a region by the
+    // setmaxnreg that dominates it.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+      if (warp == 8 || warp >= 13) {
+        // ================================================================== TMA producers
+        // Four producer warps (8, 13, 14, 15) share the ring: slot number n is pushed by producer n % 4.
+        // Each walks the whole event list (that is what numbers the slots) and keeps the block
+        // coordinates of every tile's pending iterations, but issues copies for its own slots only.
+        const int my_prod = warp == 8 ? 0 : warp - 12;
+        unsigned slot_n = 0;  // slots of the event list passed so far
         unsigned wk = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
             const int b = bh / P.heads, h = bh % P.heads;
-            int c[kTilesPerWork];
-#pragma unroll
-            for (int t = 0; t < kTilesPerWork; ++t) {
-                const int qt = g * kTilesPerWork + t;
-                c[t] = qt < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
-            }
-            // Q tiles of both pairs
-            for (int p = 0; p < 2 && ok; ++p) {
-                ok = mbar_wait(bar_q_empty(p), (wk & 1) ^ 1, ctl, 10 + p, wk);
+            const int c0 = clamp_cnt(P, bh, g * kTilesPerWork + 0), c1 = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            const int c2 = clamp_cnt(P, bh, g * kTilesPerWork + 2), c3 = clamp_cnt(P, bh, g * kTilesPerWork + 3);
+            // Q tiles of both pairs (the previous work item's output has left the same shared memory)
+            for (int p = 0; p < 2 && ok && my_prod == 0; ++p) {
+                ok = mbar_wait_warp(bar_q_empty(p), (wk & 1) ^ 1, ctl, 10 + p, wk);
                 if (!ok) break;
                 if (lane == 0) {
                     int ntile = 0;
@@ -370,138 +436,166 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                 }
             }
-            const int n0 = max(c[0], c[1]), n1 = max(c[2], c[3]);
+            const int n0 = max(c0, c1), n1 = max(c2, c3);
             const int nev = num_events(n0, n1);
-            // Block indices are prefetched by the whole warp: lane L holds the entry of tile (L & 3) for
-            // iteration win + (L >> 2); a second register holds the next window of eight iterations.
+            // Block coordinates are prefetched and decoded by the whole warp: lane L holds, for tile
+            // (L & 3) and iteration win + (L >> 2), the block's first token packed as t << 20 | h << 10 | w;
+            // a second register holds the next window of eight iterations.
             const int my_t = lane & 3, my_s = lane >> 2;
-            const int my_c = sel4(c[0], c[1], c[2], c[3], my_t);
+            const int my_c = sel4(c0, c1, c2, c3, my_t);
             const int32_t* my_l = P.idx + ((long long)bh * P.nq + min(g * kTilesPerWork + my_t, P.nq - 1)) * P.cap;
+            auto fetch = [&](int it) {
+                if (it >= my_c) return 0;
+                int bt, bhh, bw;
+                block_coords(P.gk, my_l[it], bt, bhh, bw);
+                return ((bt * P.gk.ct) << 20) | ((bhh * P.gk.ch) << 10) | (bw * P.gk.cw);
+            };
             int win = 0;
-            int cur = (my_s < my_c) ? my_l[my_s] : 0;
-            int nxt = (8 + my_s < my_c) ? my_l[8 + my_s] : 0;
-            int pend0 = 0, pend1 = 0, pend2 = 0, pend3 = 0;  // block of each tile's iteration in flight (K queued, V not yet)
+            int cur = fetch(my_s);
+            int nxt = fetch(8 + my_s);
+            // packed coordinates of the iterations whose K is queued and whose V is not yet: [tile][iteration parity]
+            int pe0 = 0, pe1 = 0, pe2 = 0, pe3 = 0, po0 = 0, po1 = 0, po2 = 0, po3 = 0;
             for (int e = 0; e < nev && ok; ++e) {
                 const Event ev = event_at(e, n0, n1);
                 if (!ev.valid) continue;
-                for (int hf = 0; hf < 2 && ok; ++hf) {
-                    const int t = 2 * ev.pair + hf;
-                    if (ev.iter >= sel4(c[0], c[1], c[2], c[3], t)) continue;
-                    if (!ev.is_pv) {
-                        while (ev.iter >= win + 8) {
-                            win += 8;
-                            cur = nxt;
-                            nxt = (win + 8 + my_s < my_c) ? my_l[win + 8 + my_s] : 0;
-                        }
-                        const int v = __shfl_sync(0xffffffffu, cur, ((ev.iter - win) << 2) | t);
-                        if (t == 0) pend0 = v; else if (t == 1) pend1 = v; else if (t == 2) pend2 = v; else pend3 = v;
+                const int ta = 2 * ev.pair, tb = ta + 1;
+                const bool act_a = ev.iter < sel4(c0, c1, c2, c3, ta), act_b = ev.iter < sel4(c0, c1, c2, c3, tb);
+                if (!ev.is_pv) {
+                    while (ev.iter >= win + 8) {
+                        win += 8;
+                        cur = nxt;
+                        nxt = fetch(win + 8 + my_s);
                     }
-                    const int stage = ring % kStages;
-                    ok = mbar_wait(bar_kv_empty(stage), ((ring / kStages) & 1) ^ 1, ctl, 20, ring);
-                    if (!ok) break;
-                    if (lane == 0) {
-                        const Coord cc = block_coord(P.gk, sel4(pend0, pend1, pend2, pend3, t), b, h, P.heads, ev.is_pv ? P.merge_v : P.merge_k, P.Tk);
-                        const CUtensorMap* tm = ev.is_pv ? &P.tm_v : &P.tm_k;
-                        const uint32_t dst = sbase + kOffKV + stage * kTileBytes;
-                        mbar_arrive_tx(bar_kv_full(stage), kTileBytes);
-                        tma_load_5d(dst, tm, bar_kv_full(stage), 0, cc.c1, cc.c2, cc.c3, cc.c4);
-                        tma_load_5d(dst + kHalfBytes, tm, bar_kv_full(stage), 64, cc.c1, cc.c2, cc.c3, cc.c4);
+                    const int va = __shfl_sync(0xffffffffu, cur, ((ev.iter - win) << 2) | ta);
+                    const int vb = __shfl_sync(0xffffffffu, cur, ((ev.iter - win) << 2) | tb);
+                    if (ev.iter & 1) {
+                        if (ev.pair) { po2 = va; po3 = vb; } else { po0 = va; po1 = vb; }
+                    } else {
+                        if (ev.pair) { pe2 = va; pe3 = vb; } else { pe0 = va; pe1 = vb; }
                     }
-                    ++ring;
+                }
+                const unsigned n = slot_n++;
+                if ((int)(n & 3) != my_prod) continue;
+                const int slot = n % kSlots;
+                ok = mbar_wait_warp(bar_slot_empty(slot), ((n / kSlots) & 1) ^ 1, ctl, 20, n);
+                if (!ok) break;
+                if (lane == 0) {
+                    LCBSA_TS(0, 100 + e);
+                    const CUtensorMap* tm = ev.is_pv ? &P.tm_v : &P.tm_k;
+                    const int merge = ev.is_pv ? P.merge_v : P.merge_k;
+                    const int c3_add = merge ? b * P.Tk : 0, c4 = merge ? h : b * P.heads + h;
+                    slot_use[slot] = n / kSlots;  // this use of the slot is armed: its consumer may now wait on slot_full
+                    mbar_arrive_tx(bar_slot_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        if (!(hf ? act_b : act_a)) continue;
+                        const int pk = (ev.iter & 1) ? sel4(po0, po1, po2, po3, ta + hf) : sel4(pe0, pe1, pe2, pe3, ta + hf);
+                        const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3_add;
+                        const uint32_t dst = sbase + kOffKV + slot * kSlotBytes + hf * kTileBytes;
+                        tma_load_5d(dst, tm, bar_slot_full(slot), 0, cw, chh, ctt, c4);
+                        tma_load_5d(dst + kHalfBytes, tm, bar_slot_full(slot), 64, cw, chh, ctt, c4);
+                    }
                 }
             }
         }
         if (!ok && lane == 0) {
             // drain: give the copies this warp issued a bounded time to land before the CTA exits
-            const unsigned long long t0 = globaltimer();
-            for (unsigned r = ring > kStages ? ring - kStages : 0; r < ring; ++r)
-                while (!mbar_try(bar_kv_full(r % kStages), (r / kStages) & 1) && globaltimer() - t0 < 20000000ull) {
+            const long long t0 = clock64();
+            for (unsigned r = slot_n > kSlots ? slot_n - kSlots : 0; r < slot_n; ++r)
+                while ((int)(r & 3) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
+                       clock64() - t0 < 40000000ll) {
                 }
         }
-    } else if (warp == 9) {
-        // ================================================================== MMA issuer
+      } else if (warp <= 12) {
+        // ================================================================== MMA issuers
+        // warp 9 / 10: S of pair 0 / 1.   warp 11 / 12: PV of pair 0 / 1.
+        // Every issuer walks the same event list as the producer (that fixes which ring slot belongs to
+        // which event) and acts on its own events only.
+        const int my_pair = (warp - 9) & 1;
+        const bool my_pv = warp >= 11;
         const uint32_t idesc_s = instr_desc(bf16, 64, 64, 0);
         const uint32_t idesc_pv = instr_desc(bf16, 64, 128, 1);
-        unsigned ring = 0, wk = 0;
-        unsigned n_p0 = 0, n_p1 = 0;  // completed (pair, iteration) events: phase counters of p_full
+        unsigned slot_n = 0, wk = 0;
+        unsigned n_own = 0;  // own events issued so far: S buffer = n_own & 1, phase of p_full = n_own & 1
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
-            int c[kTilesPerWork];
-#pragma unroll
-            for (int t = 0; t < kTilesPerWork; ++t) {
-                const int qt = g * kTilesPerWork + t;
-                c[t] = qt < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
-            }
-            const int n0 = max(c[0], c[1]), n1 = max(c[2], c[3]);
+            const int c0 = clamp_cnt(P, bh, g * kTilesPerWork + 0), c1 = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            const int c2 = clamp_cnt(P, bh, g * kTilesPerWork + 2), c3 = clamp_cnt(P, bh, g * kTilesPerWork + 3);
+            const int n0 = max(c0, c1), n1 = max(c2, c3);
             const int nev = num_events(n0, n1);
+            const int ca = my_pair ? c2 : c0, cb = my_pair ? c3 : c1;
             for (int e = 0; e < nev && ok; ++e) {
                 const Event ev = event_at(e, n0, n1);
                 if (!ev.valid) continue;
-                const int p = ev.pair;
-                if (!ev.is_pv) {
-                    // ---- S(p, iter) = Q K^T for the active halves
-                    if (ev.iter == 0) ok = mbar_wait(bar_q_full(p), wk & 1, ctl, 30 + p, wk);
-                    // S(p, iter) overwrites S(p, iter-1): the warpgroup has read it once P(iter-1) is posted,
-                    // and that was already waited for before PV(p, iter-1).
-                    for (int hf = 0; hf < 2 && ok; ++hf) {
-                        const int t = 2 * p + hf;
-                        if (ev.iter >= sel4(c[0], c[1], c[2], c[3], t)) continue;
-                        const int stage = ring % kStages;
-                        ok = mbar_wait(bar_kv_full(stage), (ring / kStages) & 1, ctl, 40, ring);
-                        if (!ok) break;
-                        tc_fence_after();
-                        if (lane == 0) {
-                            const uint32_t qa = sbase + kOffQ + t * kTileBytes;
-                            const uint32_t kb = sbase + kOffKV + stage * kTileBytes;
-                            const uint32_t d = tmem + 64u * p + ((16u * hf) << 16);
+                const unsigned slot = slot_n % kSlots, slot_phase = (slot_n / kSlots) & 1;
+                ++slot_n;
+                if (ev.pair != my_pair || (ev.is_pv != 0) != my_pv) continue;
+                const uint32_t slot_addr = sbase + kOffKV + slot * kSlotBytes;
+                const bool act_a = ev.iter < ca, act_b = ev.iter < cb;
+                // The slots of the ring are consumed by four different warps, so this warp may get here while the
+                // slot is still two uses back; a parity wait on slot_full would then be satisfied by the wrong
+                // phase.  The producer publishes the use number it has armed, which makes the parity wait exact.
+                const unsigned slot_use_no = (slot_n - 1) / kSlots;
+                ok = __all_sync(0xffffffffu, word_wait_thread(slot_use + slot, slot_use_no, ctl, 38, slot_n));
+                if (!ok) break;
+                if (!my_pv) {
+                    // ---- S(p, iter) = Q K^T into buffer n_own & 1, once the warpgroup has read out what
+                    // was there two iterations ago
+                    const int buf = n_own & 1;
+                    if (ev.iter == 0) ok = mbar_wait_warp(bar_q_full(my_pair), wk & 1, ctl, 30 + my_pair, wk);
+                    if (ok) ok = mbar_wait_warp(bar_s_free(my_pair, buf), ((n_own >> 1) & 1) ^ 1, ctl, 34 + my_pair, n_own);
+                    if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 40, slot_n);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint64_t qa = smem_desc(sbase + kOffQ + (2 * my_pair) * kTileBytes, 16, 1024);
+                        const uint64_t qb = smem_desc(sbase + kOffQ + (2 * my_pair + 1) * kTileBytes, 16, 1024);
+                        const uint64_t ka = smem_desc(slot_addr, 16, 1024), kb = smem_desc(slot_addr + kTileBytes, 16, 1024);
+                        const uint32_t d = tmem + 64u * (2 * my_pair + buf);
 #pragma unroll
-                            for (int j = 0; j < kD / 16; ++j) {
-                                const uint32_t off = (j >> 2) * kHalfBytes + (j & 3) * 32;
-                                tc_mma(d, smem_desc(qa + off, 16, 1024), smem_desc(kb + off, 16, 1024), idesc_s, j > 0);
-                            }
-                            tc_commit(bar_kv_empty(stage));  // K tile free once these MMAs have read it
+                        for (int j = 0; j < kD / 16; ++j) {
+                            // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
+                            const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
+                            if (act_a) tc_mma(d, qa + off, ka + off, idesc_s, j > 0);
+                            if (act_b) tc_mma(d + (16u << 16), qb + off, kb + off, idesc_s, j > 0);
                         }
-                        __syncwarp();
-                        ++ring;
+                        tc_commit(bar_slot_empty(slot));  // K tiles free once these MMAs have read them
+                        tc_commit(bar_s_full(my_pair, buf));
                     }
-                    if (ok && lane == 0) tc_commit(bar_s_full(p));
                     __syncwarp();
                 } else {
-                    // ---- O(p) += P V for the active halves (ring order is event order: this event's V tiles are next)
-                    const unsigned np_cur = p ? n_p1 : n_p0;
-                    ok = mbar_wait(bar_p_full(p), np_cur & 1, ctl, 50 + p, np_cur);
+                    // ---- O(p) += P V
+                    ok = mbar_wait_warp(bar_p_full(my_pair), n_own & 1, ctl, 50 + my_pair, n_own);
+                    if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 60, slot_n);
                     if (!ok) break;
-                    if (p) ++n_p1; else ++n_p0;
-                    for (int hf = 0; hf < 2 && ok; ++hf) {
-                        const int t = 2 * p + hf;
-                        if (ev.iter >= sel4(c[0], c[1], c[2], c[3], t)) continue;
-                        const int stage = ring % kStages;
-                        ok = mbar_wait(bar_kv_full(stage), (ring / kStages) & 1, ctl, 60, ring);
-                        if (!ok) break;
-                        tc_fence_after();
-                        if (lane == 0) {
-                            const uint32_t pa = sbase + kOffP + t * kPBytes;
-                            const uint32_t vb = sbase + kOffKV + stage * kTileBytes;
-                            const uint32_t d = tmem + 128u + 128u * p + ((16u * hf) << 16);
+                    tc_fence_after();
+                    if (lane == 0) {
+                        // A: P tile, K-major, 32 bytes per 16-key step.
+                        // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
+                        const uint64_t pa = smem_desc(sbase + kOffP + (2 * my_pair) * kPBytes, 16, 1024);
+                        const uint64_t pb = smem_desc(sbase + kOffP + (2 * my_pair + 1) * kPBytes, 16, 1024);
+                        const uint64_t va = smem_desc(slot_addr, kHalfBytes, 1024);
+                        const uint64_t vb = smem_desc(slot_addr + kTileBytes, kHalfBytes, 1024);
+                        const uint32_t d = tmem + 256u + 128u * my_pair;
 #pragma unroll
-                            for (int j = 0; j < kBlk / 16; ++j) {
-                                // A: P tile, K-major, 32 bytes per 16-key step.
-                                // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
-                                tc_mma(d, smem_desc(pa + j * 32, 16, 1024), smem_desc(vb + j * 2048, kHalfBytes, 1024),
-                                       idesc_pv, (ev.iter > 0 || j > 0) ? 1u : 0u);
-                            }
-                            tc_commit(bar_kv_empty(stage));
+                        for (int j = 0; j < kBlk / 16; ++j) {
+                            const uint32_t acc = (ev.iter > 0 || j > 0) ? 1u : 0u;
+                            if (act_a) tc_mma(d, pa + (uint64_t)((j * 32) >> 4), va + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
+                            if (act_b) tc_mma(d + (16u << 16), pb + (uint64_t)((j * 32) >> 4), vb + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
                         }
-                        __syncwarp();
-                        ++ring;
+                        tc_commit(bar_slot_empty(slot));
+                        tc_commit(bar_pv_done(my_pair));
                     }
-                    if (ok && lane == 0) tc_commit(bar_pv_done(p));
                     __syncwarp();
                 }
+                ++n_own;
             }
         }
+        __syncwarp();
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ================================================================== softmax warpgroups
         const int p = warp >> 2;          // pair
         const int wq = warp & 3;          // TMEM quadrant of this warp
@@ -509,8 +603,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         const int row = wq * 16 + (lane & 15);  // row of that tile
         const int t = 2 * p + hf;
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
-        const uint32_t tm_s = tmem + 64u * p + t_lane;
-        const uint32_t tm_o = tmem + 128u + 128u * p + t_lane;
+        const uint32_t tm_o = tmem + 256u + 128u * p + t_lane;
         unsigned char* p_tile = smem + kOffP + t * kPBytes;
         unsigned char* o_tile = smem + kOffQ + t * kTileBytes;
         unsigned n_s = 0, n_pv = 0, wk = 0;
@@ -520,27 +613,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             const int bh = (int)(w / groups), g = (int)(w % groups);
             const int b = bh / P.heads, h = bh % P.heads;
             const int qt = g * kTilesPerWork + t;
-            const int qt_other = g * kTilesPerWork + (t ^ 1);
             const bool tile_valid = qt < P.nq;
-            const int my_cnt = tile_valid ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
-            const int other_cnt = qt_other < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt_other], 0), P.cap) : 0;
+            const int my_cnt = clamp_cnt(P, bh, qt);
+            const int other_cnt = clamp_cnt(P, bh, g * kTilesPerWork + (t ^ 1));
             const int n_iter = max(my_cnt, other_cnt);
             const int32_t* my_list = P.idx + ((long long)bh * P.nq + (tile_valid ? qt : 0)) * P.cap;
 
             float m_ref = -INFINITY, l_sum = 0.f;
 
-            ok = mbar_wait(bar_q_full(p), wk & 1, ctl, 70 + p, wk);
+            ok = mbar_wait_warp(bar_q_full(p), wk & 1, ctl, 70 + p, wk);
             if (!ok) break;
 
             for (int i = 0; i < n_iter && ok; ++i) {
                 const bool active = i < my_cnt;
-                ok = mbar_wait(bar_s_full(p), n_s & 1, ctl, 80 + p, n_s);
+                const int buf = n_s & 1;
+                ok = mbar_wait_warp(bar_s_full(p, buf), (n_s >> 1) & 1, ctl, 80 + p, n_s);
                 if (!ok) break;
                 ++n_s;
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 10000 + i);
                 tc_fence_after();
                 uint32_t sr[64];
-                tc_ld64(tm_s, sr);
+                tc_ld64(tmem + 64u * (2 * p + buf) + t_lane, sr);
                 tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_s_free(p, buf));  // this S buffer may be overwritten
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 20000 + i);
 #ifdef LCBSA_TC_DEBUG
                 if (P.dbg && w == 0 && i == 0)
                     for (int j = 0; j < 64; ++j) P.dbg[(t * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
@@ -562,9 +660,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             }
                         }
                     }
-                    float mx = -INFINITY;
+                    float mx8[8];
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
+                    for (int j = 0; j < 8; ++j) mx8[j] = __uint_as_float(sr[j]);
+#pragma unroll
+                    for (int j = 8; j < 64; ++j) mx8[j & 7] = fmaxf(mx8[j & 7], __uint_as_float(sr[j]));
+                    const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                           fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                     const float m_new = fmaxf(m_ref, mx * P.scale2);
                     if (i == 0) {
                         m_ref = (m_new == -INFINITY) ? 0.f : m_new;
@@ -574,13 +676,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                         m_ref = m_new;
                     }
                 }
-                // P(i-1) is still being read by PV(i-1), and O must be at rest before it is rescaled
-                if (i > 0) {
-                    ok = mbar_wait(bar_pv_done(p), n_pv & 1, ctl, 90 + p, n_pv);
-                    if (!ok) break;
-                    ++n_pv;
-                }
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 30000 + i);
                 l_sum *= alpha;  // alpha is 1 unless this row's reference maximum moved
+                uint4 pk[8];     // this row of P in the input dtype, 8 keys per 16-byte chunk
                 if (active) {
                     float rs = 0.f;
 #pragma unroll
@@ -591,16 +689,26 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             pv[j] = ex2(fmaf(__uint_as_float(sr[cch * 8 + j]), P.scale2, -m_ref));
                             rs += pv[j];
                         }
-                        uint4 pk;
-                        pk.x = pack2(bf16, pv[0], pv[1]);
-                        pk.y = pack2(bf16, pv[2], pv[3]);
-                        pk.z = pack2(bf16, pv[4], pv[5]);
-                        pk.w = pack2(bf16, pv[6], pv[7]);
-                        *reinterpret_cast<uint4*>(p_tile + row * 128 + ((cch ^ (row & 7)) << 4)) = pk;
+                        pk[cch].x = pack2(bf16, pv[0], pv[1]);
+                        pk[cch].y = pack2(bf16, pv[2], pv[3]);
+                        pk[cch].z = pack2(bf16, pv[4], pv[5]);
+                        pk[cch].w = pack2(bf16, pv[6], pv[7]);
                     }
                     l_sum += rs;
                 }
-                // O is rescaled after P is out of the registers (both only need PV(i-1) to have finished)
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 40000 + i);
+                // P(i-1) is still being read by PV(i-1), and O must be at rest before it is rescaled
+                if (i > 0) {
+                    ok = mbar_wait_warp(bar_pv_done(p), n_pv & 1, ctl, 90 + p, n_pv);
+                    if (!ok) break;
+                    ++n_pv;
+                }
+                if (active) {
+#pragma unroll
+                    for (int cch = 0; cch < 8; ++cch)
+                        *reinterpret_cast<uint4*>(p_tile + row * 128 + ((cch ^ (row & 7)) << 4)) = pk[cch];
+                }
+                // O is rescaled once PV(i-1) has finished with it (rare: only when a row maximum jumps)
                 if (__any_sync(0xffffffffu, need)) {
                     tc_fence_after();
 #pragma unroll
@@ -614,15 +722,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                     tc_wait_st();
                 }
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 50000 + i);
                 fence_proxy_async();
                 tc_fence_before();
-                mbar_arrive(bar_p_full(p));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_p_full(p));
+                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 60000 + i);
             }
             if (!ok) break;
 
             // ---- epilogue of this work item
             if (n_iter > 0) {
-                ok = mbar_wait(bar_pv_done(p), n_pv & 1, ctl, 100 + p, n_pv);
+                ok = mbar_wait_warp(bar_pv_done(p), n_pv & 1, ctl, 100 + p, n_pv);
                 if (!ok) break;
                 ++n_pv;
                 tc_fence_after();
@@ -645,11 +756,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     for (int q8 = 0; q8 < 4; ++q8) {
                         uint4 pk;
                         if (my_cnt > 0) {
-                            const uint32_t* s8 = orr + q8 * 8;
-                            pk.x = pack2(bf16, __uint_as_float(s8[0]) * inv, __uint_as_float(s8[1]) * inv);
-                            pk.y = pack2(bf16, __uint_as_float(s8[2]) * inv, __uint_as_float(s8[3]) * inv);
-                            pk.z = pack2(bf16, __uint_as_float(s8[4]) * inv, __uint_as_float(s8[5]) * inv);
-                            pk.w = pack2(bf16, __uint_as_float(s8[6]) * inv, __uint_as_float(s8[7]) * inv);
+                            pk.x = pack2(bf16, __uint_as_float(orr[q8 * 8 + 0]) * inv, __uint_as_float(orr[q8 * 8 + 1]) * inv);
+                            pk.y = pack2(bf16, __uint_as_float(orr[q8 * 8 + 2]) * inv, __uint_as_float(orr[q8 * 8 + 3]) * inv);
+                            pk.z = pack2(bf16, __uint_as_float(orr[q8 * 8 + 4]) * inv, __uint_as_float(orr[q8 * 8 + 5]) * inv);
+                            pk.w = pack2(bf16, __uint_as_float(orr[q8 * 8 + 6]) * inv, __uint_as_float(orr[q8 * 8 + 7]) * inv);
                         } else {
                             pk = make_uint4(0u, 0u, 0u, 0u);
                         }
@@ -671,9 +781,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 }
             }
             fence_proxy_async();
-            mbar_arrive(bar_o_staged(p));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_o_staged(p));
             if (warp == 4 * p) {  // first warp of the warpgroup: wait for all 128 rows, then one lane stores
-                ok = mbar_wait(bar_o_staged(p), wk & 1, ctl, 110 + p, wk);
+                ok = mbar_wait_warp(bar_o_staged(p), wk & 1, ctl, 110 + p, wk);
                 if (ok && lane == 0) {
                     for (int hh2 = 0; hh2 < 2; ++hh2) {
                         const int tt2 = 2 * p + hh2, qq = g * kTilesPerWork + tt2;
@@ -747,12 +858,14 @@ bool make_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, const Geo
 
 #ifdef LCBSA_TC_DEBUG
 float* g_tc_debug = nullptr;
+long long* g_tc_ts = nullptr;
 #endif
 
 }  // namespace
 
 #ifdef LCBSA_TC_DEBUG
 extern "C" void lcbsa_debug_set_buffer(float* p) { g_tc_debug = p; }
+extern "C" void lcbsa_debug_set_timeline(long long* p) { g_tc_ts = p; }
 #endif
 
 bool attn_tc_supported(const AttnArgs& a, const char** why) {
@@ -761,6 +874,10 @@ bool attn_tc_supported(const AttnArgs& a, const char** why) {
     if (a.gq.bs != kBlk || a.gk.bs != kBlk) { *why = "needs 64-token query and key blocks"; return false; }
     if (a.gq.ct > 256 || a.gq.ch > 256 || a.gq.cw > 256 || a.gk.ct > 256 || a.gk.ch > 256 || a.gk.cw > 256) {
         *why = "block axis above the TMA box limit";
+        return false;
+    }
+    if (a.gk.T > 1023 || a.gk.H > 1023 || a.gk.W > 1023) {
+        *why = "key grid axis above 1023 tokens (block coordinates are packed into 10-bit fields)";
         return false;
     }
     const View* vs[4] = {&a.q, &a.k, &a.v, &a.o};
@@ -790,6 +907,7 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
     P.is_bf16 = a.dtype == LCBSA_BF16;
 #ifdef LCBSA_TC_DEBUG
     P.dbg = g_tc_debug;
+    P.ts = g_tc_ts;
 #endif
 
     static int sm_count = 0;
