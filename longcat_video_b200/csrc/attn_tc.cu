@@ -13,12 +13,12 @@
 // upper 16 lanes of the same columns, so that one softmax warpgroup (128 threads, one TMEM lane each)
 // serves both with every lane busy.
 //
-//   warps 0-3 : softmax warpgroup of pair 0      warps 8,13,14,15 : TMA producers (Q tiles, ring of K/V slots)
-//   warps 4-7 : softmax warpgroup of pair 1      warps 9,10 : S = Q K^T issuers of pair 0 and pair 1
-//   warps 11,12 : O += P V issuers of pair 0 and pair 1
+//   warps 0-3 : softmax warpgroup of pair 0      warps 8,15 : TMA producers (Q tiles, ring of K/V slots)
+//   warps 4-7 : softmax warpgroup of pair 1      warps 9-12 : S = Q K^T issuers, one per tile
+//   warps 13,14 : O += P V issuers of pair 0 and pair 1
 // One thread can start a tcgen05.mma only about every 120 cycles (measured on B200, whatever the
-// shape), while these MMAs carry 32-64 cycles of math; four issuing warps bring the issue rate to
-// the rate of the tensor pipe.  The same holds for the 5-D TMA copies, hence four producers.
+// shape), while these MMAs carry 32-64 cycles of math; six issuing warps, eight MMAs per iteration
+// each, bring the issue rate to the rate of the tensor pipe.
 //
 // Per selected K/V block and tile:  S = Q K^T  (M64 N64 K128, fp32 in TMEM)  ->  the softmax warpgroup
 // reads S with tcgen05.ld, exp2 online softmax in registers, P (input dtype) into swizzled shared
@@ -372,13 +372,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         for (int s = 0; s < kSlots; ++s) slot_use[s] = 0xffffffffu;
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(bar_slot_full(s), 1);
-            mbar_init(bar_slot_empty(s), 1);
+            mbar_init(bar_slot_empty(s), 2);  // K slots: the two S issuers of a pair; V slots: the PV issuer, twice
         }
         for (int p = 0; p < 2; ++p) {
             mbar_init(bar_q_full(p), 1);
             mbar_init(bar_q_empty(p), 1);
-            mbar_init(bar_s_full(p, 0), 1);
-            mbar_init(bar_s_full(p, 1), 1);
+            mbar_init(bar_s_full(p, 0), 2);  // one commit per S issuer (tile) of the pair
+            mbar_init(bar_s_full(p, 1), 2);
             mbar_init(bar_p_full(p), 4);    // one elected arrival per softmax warp
             mbar_init(bar_pv_done(p), 1);
             mbar_init(bar_o_staged(p), 4);
@@ -404,12 +404,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     // setmaxnreg that dominates it.
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-      if (warp == 8 || warp >= 13) {
+      if (warp == 8 || warp == 15) {
         // ================================================================== TMA producers
-        // Four producer warps (8, 13, 14, 15) share the ring: slot number n is pushed by producer n % 4.
+        // Two producer warps (8 and 15) share the ring: slot number n is pushed by producer n % 2.
         // Each walks the whole event list (that is what numbers the slots) and keeps the block
         // coordinates of every tile's pending iterations, but issues copies for its own slots only.
-        const int my_prod = warp == 8 ? 0 : warp - 12;
+        const int my_prod = warp == 8 ? 0 : 1;
         unsigned slot_n = 0;  // slots of the event list passed so far
         unsigned wk = 0;
         bool ok = true;
@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                 }
                 const unsigned n = slot_n++;
-                if ((int)(n & 3) != my_prod) continue;
+                if ((int)(n & 1) != my_prod) continue;
                 const int slot = n % kSlots;
                 ok = mbar_wait_warp(bar_slot_empty(slot), ((n / kSlots) & 1) ^ 1, ctl, 20, n);
                 if (!ok) break;
@@ -502,17 +502,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             // drain: give the copies this warp issued a bounded time to land before the CTA exits
             const long long t0 = clock64();
             for (unsigned r = slot_n > kSlots ? slot_n - kSlots : 0; r < slot_n; ++r)
-                while ((int)(r & 3) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
+                while ((int)(r & 1) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
                        clock64() - t0 < 40000000ll) {
                 }
         }
-      } else if (warp <= 12) {
+      } else {
         // ================================================================== MMA issuers
-        // warp 9 / 10: S of pair 0 / 1.   warp 11 / 12: PV of pair 0 / 1.
+        // warps 9-12: S of (pair, tile) = (0,0) (0,1) (1,0) (1,1).   warps 13 / 14: PV of pair 0 / 1.
         // Every issuer walks the same event list as the producer (that fixes which ring slot belongs to
         // which event) and acts on its own events only.
-        const int my_pair = (warp - 9) & 1;
-        const bool my_pv = warp >= 11;
+        const bool my_pv = warp >= 13;
+        const int my_pair = my_pv ? warp - 13 : (warp - 9) >> 1;
+        const int my_hf = (warp - 9) & 1;  // S issuers: which tile of the pair
         const uint32_t idesc_s = instr_desc(bf16, 64, 64, 0);
         const uint32_t idesc_pv = instr_desc(bf16, 64, 128, 1);
         unsigned slot_n = 0, wk = 0;
@@ -549,18 +550,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        const uint64_t qa = smem_desc(sbase + kOffQ + (2 * my_pair) * kTileBytes, 16, 1024);
-                        const uint64_t qb = smem_desc(sbase + kOffQ + (2 * my_pair + 1) * kTileBytes, 16, 1024);
-                        const uint64_t ka = smem_desc(slot_addr, 16, 1024), kb = smem_desc(slot_addr + kTileBytes, 16, 1024);
-                        const uint32_t d = tmem + 64u * (2 * my_pair + buf);
+                        if (my_hf ? act_b : act_a) {
+                            const uint64_t qd = smem_desc(sbase + kOffQ + (2 * my_pair + my_hf) * kTileBytes, 16, 1024);
+                            const uint64_t kd = smem_desc(slot_addr + my_hf * kTileBytes, 16, 1024);
+                            const uint32_t d = tmem + 64u * (2 * my_pair + buf) + ((16u * my_hf) << 16);
 #pragma unroll
-                        for (int j = 0; j < kD / 16; ++j) {
-                            // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
-                            const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
-                            if (act_a) tc_mma(d, qa + off, ka + off, idesc_s, j > 0);
-                            if (act_b) tc_mma(d + (16u << 16), qb + off, kb + off, idesc_s, j > 0);
+                            for (int j = 0; j < kD / 16; ++j) {
+                                // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
+                                const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
+                                tc_mma(d, qd + off, kd + off, idesc_s, j > 0);
+                            }
                         }
-                        tc_commit(bar_slot_empty(slot));  // K tiles free once these MMAs have read them
+                        tc_commit(bar_slot_empty(slot));  // this tile's K is free once these MMAs have read it
                         tc_commit(bar_s_full(my_pair, buf));
                     }
                     __syncwarp();
@@ -585,6 +586,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             if (act_b) tc_mma(d + (16u << 16), pb + (uint64_t)((j * 32) >> 4), vb + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
                         }
                         tc_commit(bar_slot_empty(slot));
+                        tc_commit(bar_slot_empty(slot));  // the barrier counts two arrivals (see the K slots)
                         tc_commit(bar_pv_done(my_pair));
                     }
                     __syncwarp();
@@ -645,6 +647,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
 #endif
                 float alpha = 1.f;
                 bool need = false;
+                uint4 pk[8];  // this row of P in the input dtype, 8 keys per 16-byte chunk
                 if (active) {
                     if (P.gk.ragged) {  // keys of a partial block that lie outside the grid
                         const int blk = my_list[i];
@@ -660,6 +663,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             }
                         }
                     }
+                    // One pass: the probabilities are computed against the current reference maximum while
+                    // the row maximum is tracked on the side; only if the maximum has moved by more than 2^8
+                    // (or this is the first block) is the pass repeated with the new reference.
+                    auto probs = [&](float mref, float& rsum) {
+                        float r4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int cch = 0; cch < 8; ++cch) {
+                            float pv[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                pv[j] = ex2(fmaf(__uint_as_float(sr[cch * 8 + j]), P.scale2, -mref));
+                                r4[j & 3] += pv[j];
+                            }
+                            pk[cch].x = pack2(bf16, pv[0], pv[1]);
+                            pk[cch].y = pack2(bf16, pv[2], pv[3]);
+                            pk[cch].z = pack2(bf16, pv[4], pv[5]);
+                            pk[cch].w = pack2(bf16, pv[6], pv[7]);
+                        }
+                        rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+                    };
+                    float rs = 0.f;
+                    if (i > 0) probs(m_ref, rs);
                     float mx8[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) mx8[j] = __uint_as_float(sr[j]);
@@ -668,34 +693,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                                            fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                     const float m_new = fmaxf(m_ref, mx * P.scale2);
-                    if (i == 0) {
+                    if (i == 0 || m_new - m_ref > 8.f) {
+                        if (i > 0) {
+                            need = true;
+                            alpha = ex2(m_ref - m_new);
+                        }
                         m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-                    } else if (m_new - m_ref > 8.f) {
-                        need = true;
-                        alpha = ex2(m_ref - m_new);
-                        m_ref = m_new;
+                        probs(m_ref, rs);
                     }
+                    l_sum = l_sum * alpha + rs;  // alpha is 1 unless this row's reference maximum moved
                 }
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 30000 + i);
-                l_sum *= alpha;  // alpha is 1 unless this row's reference maximum moved
-                uint4 pk[8];     // this row of P in the input dtype, 8 keys per 16-byte chunk
-                if (active) {
-                    float rs = 0.f;
-#pragma unroll
-                    for (int cch = 0; cch < 8; ++cch) {
-                        float pv[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            pv[j] = ex2(fmaf(__uint_as_float(sr[cch * 8 + j]), P.scale2, -m_ref));
-                            rs += pv[j];
-                        }
-                        pk[cch].x = pack2(bf16, pv[0], pv[1]);
-                        pk[cch].y = pack2(bf16, pv[2], pv[3]);
-                        pk[cch].z = pack2(bf16, pv[4], pv[5]);
-                        pk[cch].w = pack2(bf16, pv[6], pv[7]);
-                    }
-                    l_sum += rs;
-                }
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 40000 + i);
                 // P(i-1) is still being read by PV(i-1), and O must be at rest before it is rescaled
                 if (i > 0) {
