@@ -21,15 +21,18 @@
 // each, bring the issue rate to the rate of the tensor pipe.
 //
 // Per selected K/V block and tile:  S = Q K^T  (M64 N64 K128, fp32 in TMEM)  ->  the softmax warpgroup
-// reads S with tcgen05.ld, exp2 online softmax in registers, P (input dtype) into swizzled shared
-// memory  ->  O += P V  (M64 N128 K64, fp32 in TMEM).  S is double-buffered in TMEM and is issued
-// up to two iterations ahead of the PV that consumes it, so a warpgroup finds its next S ready when
-// it finishes a round and the tensor pipe always has queued work from both pairs.
+// reads S with tcgen05.ld, exp2 online softmax in registers, P (input dtype) back into TMEM with
+// tcgen05.st  ->  O += P V  (M64 N128 K64, A operand from TMEM, fp32 accumulator in TMEM).
+// P never touches shared memory: the kernel is bound by shared-memory bandwidth (every K/V byte is
+// written by TMA and read by one MMA; Q is re-read for every block), so the P round trip is kept out of it.
+// The next S of a pair is issued as soon as the warpgroup has pulled the current one into registers, and
+// P is double-buffered, so a warpgroup never waits for the PV of the iteration before.
 // The running maximum baked into O is only refreshed when the row maximum grows by more than 2^8
 // (the accumulated values stay finite and the result is unchanged after the final division), so O is
 // rarely rescaled in TMEM.
 //
-// TMEM columns (512): S[pair][buf] at 64*(2*pair+buf), O[pair] at 256 + 128*pair.
+// TMEM columns (512), per pair at 256*pair: S at +0 (64 columns, fp32), P[buf] at +64 + 32*buf (the
+// probabilities in the input dtype, two per column, double-buffered), O at +128 (128 columns, fp32).
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA records where, raises an abort
 // flag that all roles poll, drains its outstanding bulk copies, frees its TMEM and returns.
@@ -45,8 +48,7 @@ constexpr int kD = 128;
 constexpr int kBlk = 64;                    // tokens per query / key block
 constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB: one Q, K, V or O tile
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128 B, 128B-swizzled
-constexpr int kPBytes = kBlk * kBlk * 2;    // 8 KiB: one P tile
-constexpr int kSlots = 4;                   // ring of K/V slots; a slot holds the tiles of both halves of a pair
+constexpr int kSlots = 5;                   // ring of K/V slots; a slot holds the tiles of both halves of a pair
 constexpr int kSlotBytes = 2 * kTileBytes;
 constexpr int kTilesPerWork = 4;
 constexpr int kThreads = 512;
@@ -58,10 +60,10 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffQ = 0;                                   // 4 tiles (reused to stage O)
 constexpr int kOffKV = kOffQ + kTilesPerWork * kTileBytes;  // ring
-constexpr int kOffP = kOffKV + kSlots * kSlotBytes;         // 4 P tiles
-constexpr int kOffBar = kOffP + kTilesPerWork * kPBytes;
-// barriers: slot_full[4] slot_empty[4] q_full[2] q_empty[2] s_full[2][2] p_full[2] pv_done[2] o_staged[2] s_free[2][2]
-constexpr int kNumBars = 2 * kSlots + 2 + 2 + 4 + 2 + 2 + 2 + 4;
+constexpr int kOffBar = kOffKV + kSlots * kSlotBytes;
+// barriers: slot_full[5] slot_empty[5] q_full[2] q_empty[2] s_full[2][2] p_full[2][2] pv_done[2][2] o_staged[2] s_free[2][2]
+// (of s_full / s_free only entry [pair][0] is in use: S is single-buffered)
+constexpr int kNumBars = 2 * kSlots + 2 + 2 + 4 + 4 + 4 + 2 + 4;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;
 constexpr int kSmemBytes = kOffMisc + 64 + 1024;  // + slack for the 1024-byte alignment
 
@@ -221,6 +223,16 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         : "memory");
 }
 
+// A operand from TMEM (M x K, two 16-bit elements per column), B from shared memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accum)
+        : "memory");
+}
+
 // 32 lanes x 32 columns of fp32: thread i of the warp gets lane (base + i), columns c .. c+31
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -343,6 +355,7 @@ __device__ __forceinline__ int clamp_cnt(const TcParams& P, int bh, int qt) {
 
 // ------------------------------------------------------------------------------------------ kernel
 
+template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -353,13 +366,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     auto bar_q_full = [&](int p) { return bar0 + 8u * (2 * kSlots + p); };
     auto bar_q_empty = [&](int p) { return bar0 + 8u * (2 * kSlots + 2 + p); };
     auto bar_s_full = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 4 + 2 * p + buf); };
-    auto bar_p_full = [&](int p) { return bar0 + 8u * (2 * kSlots + 8 + p); };
-    auto bar_pv_done = [&](int p) { return bar0 + 8u * (2 * kSlots + 10 + p); };
-    auto bar_o_staged = [&](int p) { return bar0 + 8u * (2 * kSlots + 12 + p); };
-    auto bar_s_free = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 14 + 2 * p + buf); };
+    // p_full and pv_done exist once per P buffer: the warpgroup may run two rounds ahead of the PV issuer, and a
+    // parity wait is only exact while the waiter is at most one phase away from the barrier.
+    auto bar_p_full = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 8 + 2 * p + buf); };
+    auto bar_pv_done = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 12 + 2 * p + buf); };
+    auto bar_o_staged = [&](int p) { return bar0 + 8u * (2 * kSlots + 16 + p); };
+    auto bar_s_free = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 18 + 2 * p + buf); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
-    volatile uint32_t* slot_use = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc + 16);  // [kSlots] use number armed
+    volatile uint32_t* slot_use = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc + 16);  // [kSlots] use number armed (20 bytes)
     const Ctl ctl{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -379,8 +394,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             mbar_init(bar_q_empty(p), 1);
             mbar_init(bar_s_full(p, 0), 2);  // one commit per S issuer (tile) of the pair
             mbar_init(bar_s_full(p, 1), 2);
-            mbar_init(bar_p_full(p), 4);    // one elected arrival per softmax warp
-            mbar_init(bar_pv_done(p), 1);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(bar_p_full(p, b), 4);  // one elected arrival per softmax warp
+                mbar_init(bar_pv_done(p, b), 1);
+            }
             mbar_init(bar_o_staged(p), 4);
             mbar_init(bar_s_free(p, 0), 4);
             mbar_init(bar_s_free(p, 1), 4);
@@ -398,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
 
     const int groups = (P.nq + kTilesPerWork - 1) / kTilesPerWork;
     const long long total_work = (long long)P.bh_total * groups;
-    const bool bf16 = P.is_bf16 != 0;
+    constexpr bool bf16 = kBf16;
 
     // Register budgets are set inside each role's own branch: the compiler sizes a region by the
     // setmaxnreg that dominates it.
@@ -406,7 +423,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
       if (warp == 8 || warp == 15) {
         // ================================================================== TMA producers
-        // Two producer warps (8 and 15) share the ring: slot number n is pushed by producer n % 2.
+        // Two producer warps (8 and 15) share the ring: a ring slot is always filled by the same producer
+        // (slot index & 1), which keeps its parity wait on slot_empty exact.
         // Each walks the whole event list (that is what numbers the slots) and keeps the block
         // coordinates of every tile's pending iterations, but issues copies for its own slots only.
         const int my_prod = warp == 8 ? 0 : 1;
@@ -475,12 +493,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                 }
                 const unsigned n = slot_n++;
-                if ((int)(n & 1) != my_prod) continue;
                 const int slot = n % kSlots;
+                if ((slot & 1) != my_prod) continue;
                 ok = mbar_wait_warp(bar_slot_empty(slot), ((n / kSlots) & 1) ^ 1, ctl, 20, n);
                 if (!ok) break;
                 if (lane == 0) {
-                    LCBSA_TS(0, 100 + e);
+                    if (warp == 15) LCBSA_TS(0, 100000 + ev.iter * 10 + ev.pair);
                     const CUtensorMap* tm = ev.is_pv ? &P.tm_v : &P.tm_k;
                     const int merge = ev.is_pv ? P.merge_v : P.merge_k;
                     const int c3_add = merge ? b * P.Tk : 0, c4 = merge ? h : b * P.heads + h;
@@ -502,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             // drain: give the copies this warp issued a bounded time to land before the CTA exits
             const long long t0 = clock64();
             for (unsigned r = slot_n > kSlots ? slot_n - kSlots : 0; r < slot_n; ++r)
-                while ((int)(r & 1) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
+                while ((int)((r % kSlots) & 1) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
                        clock64() - t0 < 40000000ll) {
                 }
         }
@@ -541,19 +559,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 ok = __all_sync(0xffffffffu, word_wait_thread(slot_use + slot, slot_use_no, ctl, 38, slot_n));
                 if (!ok) break;
                 if (!my_pv) {
-                    // ---- S(p, iter) = Q K^T into buffer n_own & 1, once the warpgroup has read out what
-                    // was there two iterations ago
-                    const int buf = n_own & 1;
+                    // ---- S(p, iter) = Q K^T, once the warpgroup has pulled the previous S into registers
+                    if (warp == 9 && lane == 0) LCBSA_TS(1, 10000 + ev.iter);
                     if (ev.iter == 0) ok = mbar_wait_warp(bar_q_full(my_pair), wk & 1, ctl, 30 + my_pair, wk);
-                    if (ok) ok = mbar_wait_warp(bar_s_free(my_pair, buf), ((n_own >> 1) & 1) ^ 1, ctl, 34 + my_pair, n_own);
+                    if (ok) ok = mbar_wait_warp(bar_s_free(my_pair, 0), (n_own & 1) ^ 1, ctl, 34 + my_pair, n_own);
+                    if (warp == 9 && lane == 0) LCBSA_TS(1, 20000 + ev.iter);
                     if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 40, slot_n);
                     if (!ok) break;
+                    if (warp == 9 && lane == 0) LCBSA_TS(1, 30000 + ev.iter);
                     tc_fence_after();
                     if (lane == 0) {
                         if (my_hf ? act_b : act_a) {
                             const uint64_t qd = smem_desc(sbase + kOffQ + (2 * my_pair + my_hf) * kTileBytes, 16, 1024);
                             const uint64_t kd = smem_desc(slot_addr + my_hf * kTileBytes, 16, 1024);
-                            const uint32_t d = tmem + 64u * (2 * my_pair + buf) + ((16u * my_hf) << 16);
+                            const uint32_t d = tmem + 256u * my_pair + ((16u * my_hf) << 16);
 #pragma unroll
                             for (int j = 0; j < kD / 16; ++j) {
                                 // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
@@ -562,32 +581,33 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             }
                         }
                         tc_commit(bar_slot_empty(slot));  // this tile's K is free once these MMAs have read it
-                        tc_commit(bar_s_full(my_pair, buf));
+                        tc_commit(bar_s_full(my_pair, 0));
+                        if (warp == 9) LCBSA_TS(1, 40000 + ev.iter);
                     }
                     __syncwarp();
                 } else {
                     // ---- O(p) += P V
-                    ok = mbar_wait_warp(bar_p_full(my_pair), n_own & 1, ctl, 50 + my_pair, n_own);
+                    ok = mbar_wait_warp(bar_p_full(my_pair, n_own & 1), (n_own >> 1) & 1, ctl, 50 + my_pair, n_own);
                     if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 60, slot_n);
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        // A: P tile, K-major, 32 bytes per 16-key step.
+                        // A: P in TMEM (buffer n_own & 1), 8 columns per 16-key step; the second tile of the pair
+                        // sits 16 lanes up, like its accumulators.
                         // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
-                        const uint64_t pa = smem_desc(sbase + kOffP + (2 * my_pair) * kPBytes, 16, 1024);
-                        const uint64_t pb = smem_desc(sbase + kOffP + (2 * my_pair + 1) * kPBytes, 16, 1024);
+                        const uint32_t pa = tmem + 256u * my_pair + 64u + 32u * (n_own & 1);
                         const uint64_t va = smem_desc(slot_addr, kHalfBytes, 1024);
                         const uint64_t vb = smem_desc(slot_addr + kTileBytes, kHalfBytes, 1024);
-                        const uint32_t d = tmem + 256u + 128u * my_pair;
+                        const uint32_t d = tmem + 256u * my_pair + 128u;
 #pragma unroll
                         for (int j = 0; j < kBlk / 16; ++j) {
                             const uint32_t acc = (ev.iter > 0 || j > 0) ? 1u : 0u;
-                            if (act_a) tc_mma(d, pa + (uint64_t)((j * 32) >> 4), va + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
-                            if (act_b) tc_mma(d + (16u << 16), pb + (uint64_t)((j * 32) >> 4), vb + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
+                            if (act_a) tc_mma_ts(d, pa + 8u * j, va + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
+                            if (act_b) tc_mma_ts(d + (16u << 16), pa + 8u * j + (16u << 16), vb + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
                         }
                         tc_commit(bar_slot_empty(slot));
                         tc_commit(bar_slot_empty(slot));  // the barrier counts two arrivals (see the K slots)
-                        tc_commit(bar_pv_done(my_pair));
+                        tc_commit(bar_pv_done(my_pair, n_own & 1));
                     }
                     __syncwarp();
                 }
@@ -605,10 +625,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         const int row = wq * 16 + (lane & 15);  // row of that tile
         const int t = 2 * p + hf;
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
-        const uint32_t tm_o = tmem + 256u + 128u * p + t_lane;
-        unsigned char* p_tile = smem + kOffP + t * kPBytes;
+        const uint32_t tm_s = tmem + 256u * p + t_lane;
+        const uint32_t tm_o = tm_s + 128u;
         unsigned char* o_tile = smem + kOffQ + t * kTileBytes;
-        unsigned n_s = 0, n_pv = 0, wk = 0;
+        unsigned n_s = 0, wk = 0;      // S rounds done (= P buffers filled) over the whole kernel
+        unsigned n_pv0 = 0, n_pv1 = 0;  // pv_done phases consumed, per P buffer
         bool ok = true;
 
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
@@ -628,18 +649,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
 
             for (int i = 0; i < n_iter && ok; ++i) {
                 const bool active = i < my_cnt;
-                const int buf = n_s & 1;
-                ok = mbar_wait_warp(bar_s_full(p, buf), (n_s >> 1) & 1, ctl, 80 + p, n_s);
+                const unsigned round = n_s;  // index of this (pair, iteration) over the whole kernel
+                ok = mbar_wait_warp(bar_s_full(p, 0), n_s & 1, ctl, 80 + p, n_s);
                 if (!ok) break;
                 ++n_s;
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 10000 + i);
                 tc_fence_after();
                 uint32_t sr[64];
-                tc_ld64(tmem + 64u * (2 * p + buf) + t_lane, sr);
+                tc_ld64(tm_s, sr);
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_s_free(p, buf));  // this S buffer may be overwritten
+                if (lane == 0) mbar_arrive(bar_s_free(p, 0));  // S may be overwritten by the next one
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 20000 + i);
 #ifdef LCBSA_TC_DEBUG
                 if (P.dbg && w == 0 && i == 0)
@@ -705,19 +726,39 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 }
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 30000 + i);
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 40000 + i);
-                // P(i-1) is still being read by PV(i-1), and O must be at rest before it is rescaled
-                if (i > 0) {
-                    ok = mbar_wait_warp(bar_pv_done(p), n_pv & 1, ctl, 90 + p, n_pv);
+                // P buffer (round & 1) was last read by the PV two rounds ago; O must be at rest (PV of the round
+                // before finished) before it is rescaled.  pv_done phases are consumed strictly in order.
+                const bool any_need = __any_sync(0xffffffffu, need);
+                // PV of round r signals pv_done[r & 1] (as that barrier's phase r >> 1).  Every PV up to round x must
+                // have finished, x = round - 2 (it read the P buffer about to be overwritten) or round - 1 when O is
+                // going to be rescaled.  Phases are consumed in order, per buffer.
+                {
+                    const int x = (int)round - (any_need ? 1 : 2);
+                    const unsigned need0 = x >= 0 ? (unsigned)(x >> 1) + 1u : 0u;   // even rounds <= x
+                    const unsigned need1 = x >= 1 ? (unsigned)((x + 1) >> 1) : 0u;  // odd rounds <= x
+                    while (n_pv0 < need0 && ok) {
+                        ok = mbar_wait_warp(bar_pv_done(p, 0), n_pv0 & 1, ctl, 90 + p, n_pv0);
+                        ++n_pv0;
+                    }
+                    while (n_pv1 < need1 && ok) {
+                        ok = mbar_wait_warp(bar_pv_done(p, 1), n_pv1 & 1, ctl, 92 + p, n_pv1);
+                        ++n_pv1;
+                    }
                     if (!ok) break;
-                    ++n_pv;
                 }
-                if (active) {
+                {   // all 32 lanes take part in the store (a lane whose tile has run out of blocks writes don't-cares)
+                    uint32_t pr[32];
 #pragma unroll
-                    for (int cch = 0; cch < 8; ++cch)
-                        *reinterpret_cast<uint4*>(p_tile + row * 128 + ((cch ^ (row & 7)) << 4)) = pk[cch];
+                    for (int cch = 0; cch < 8; ++cch) {
+                        pr[4 * cch + 0] = pk[cch].x;
+                        pr[4 * cch + 1] = pk[cch].y;
+                        pr[4 * cch + 2] = pk[cch].z;
+                        pr[4 * cch + 3] = pk[cch].w;
+                    }
+                    tc_st32(tm_s + 64u + 32u * (round & 1), pr);
                 }
                 // O is rescaled once PV(i-1) has finished with it (rare: only when a row maximum jumps)
-                if (__any_sync(0xffffffffu, need)) {
+                if (any_need) {
                     tc_fence_after();
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
@@ -728,24 +769,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                         for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
                         tc_st32(tm_o + 32 * cch, orr);
                     }
-                    tc_wait_st();
                 }
+                tc_wait_st();
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 50000 + i);
-                fence_proxy_async();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_p_full(p));
+                if (lane == 0) mbar_arrive(bar_p_full(p, round & 1));
                 if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 60000 + i);
             }
             if (!ok) break;
 
             // ---- epilogue of this work item
-            if (n_iter > 0) {
-                ok = mbar_wait_warp(bar_pv_done(p), n_pv & 1, ctl, 100 + p, n_pv);
-                if (!ok) break;
-                ++n_pv;
-                tc_fence_after();
+            while (n_pv0 < ((n_s + 1) >> 1) && ok) {  // every PV of this work item has finished
+                ok = mbar_wait_warp(bar_pv_done(p, 0), n_pv0 & 1, ctl, 100 + p, n_pv0);
+                ++n_pv0;
             }
+            while (n_pv1 < (n_s >> 1) && ok) {
+                ok = mbar_wait_warp(bar_pv_done(p, 1), n_pv1 & 1, ctl, 102 + p, n_pv1);
+                ++n_pv1;
+            }
+            if (!ok) break;
+            tc_fence_after();
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
             for (int cch = 0; cch < 4; ++cch) {
@@ -924,12 +968,13 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     }
-    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    auto kern = P.is_bf16 ? attn_tc_kernel<true> : attn_tc_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     const long long groups = (a.gq.nblk + kTilesPerWork - 1) / kTilesPerWork;
     const long long work = groups * a.B * a.H;
     const int grid = (int)(work < sm_count ? work : sm_count);
-    attn_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(P);
+    kern<<<grid, kThreads, kSmemBytes, st>>>(P);
     return cudaGetLastError();
 }
 
