@@ -118,6 +118,21 @@ int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor
                    const LcbsaTensor* out, float* lse, int impl, void* stream);
 
 /*
+ * lcbsa_block_select for callers that cannot allocate device memory for the workspace (a frozen
+ * memory pool, a plugin that only receives its input and output buffers, code that must not touch the
+ * CUDA allocator).  No counterpart in the reference: there the workspace is whatever PyTorch allocates.
+ * The scratch is a device array built into the library, lcbsa_static_scratch_bytes() (32 MiB) per
+ * GPU, reserved on every GPU that loads the library until the process exits.  Problems whose pooled Q
+ * and K do not fit are refused with LCBSA_EWORKSPACE.  The call allocates nothing; it launches the same
+ * three kernels as lcbsa_block_select.  All calls on one device share the array: calls that can
+ * overlap on the GPU race and must be ordered by the caller.  The first call on a device resolves
+ * the array's address and should be made outside stream capture.
+ */
+size_t lcbsa_static_scratch_bytes(void);
+int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk,
+                              int nsel, int cap, int32_t* idx, int32_t* cnt, void* stream);
+
+/*
  * Synchronise the current device and report whether any kernel of this library flagged a
  * bounded wait that ran out since the last call (LCBSA_EDEVICE), clearing the flag.
  * Debug aid for tests; not part of the hot path.

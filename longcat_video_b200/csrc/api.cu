@@ -73,6 +73,10 @@ int cuda_fail(cudaError_t e, const char* what, const char* why) {
 
 }  // namespace
 
+namespace lcbsa {
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace lcbsa
+
 extern "C" {
 
 int lcbsa_version(void) { return LCBSA_VERSION; }

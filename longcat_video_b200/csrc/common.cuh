@@ -71,6 +71,9 @@ __device__ __forceinline__ void block_coords(const Geom& g, int blk, int& bt, in
     bt = q / g.Nh;
 }
 
+// Message returned by lcbsa_last_error() for the calling thread (api.cu owns the buffer).
+void set_last_error(const char* msg);
+
 // Launchers implemented in the .cu files (host side). All return a cudaError_t from the launch.
 cudaError_t launch_pool(int dtype, const View& x, int B, int H, int D, const Geom& g, void* out, cudaStream_t st);
 

@@ -36,6 +36,7 @@ def test_host_helpers():
     assert lib.lcbsa_num_blocks(ctypes.byref(g)) == 6 * 12 * 10
     for sp, nk in ((0.9375, 1440), (0.9, 10), (0.875, 1320), (0.5, 4), (0.96875, 1440), (0.0, 7), (1.0, 7)):
         assert lib.lcbsa_num_selected(sp, nk) == int((1 - sp) * nk)
+    assert lib.lcbsa_static_scratch_bytes() == 32 << 20
 
 
 def test_validation_happens_before_any_launch():
