@@ -1,0 +1,139 @@
+"""Multi-GPU leg of ``bench.py``: one attention layer's BSA forward with Ulysses head sharding.
+
+One process per GPU (torchrun), NCCL.  Every rank starts with its ``[1, H, S/N, D]`` slice of q, k, v
+(the layout the DiT has under context parallelism), the decorated attention function trades them for
+``[1, H/N, S, D]`` with the all-to-all, runs block-select + block-sparse attention on its heads over the
+rank-major grid ``(N*T, H/sh, W/sw)`` (``longcat_video/modules/attention.py:60-66``), and trades the result
+back.  The total work is that of one layer whatever N is ("strong" scaling).
+"""
+from __future__ import annotations
+
+import json
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from ..synthetic import Workload, make_qkv
+
+
+def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, attn_impl):
+    from .. import _lib as L
+    from ..block_sparse_attention import bsa_interface as B
+    from . import context_parallel_util as cpu_
+    from .ulysses_wrapper import ulysses_wrapper
+
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    cpu_.init_context_parallel(world, rank, world)
+    if heads % world:
+        raise SystemExit(f"{heads} heads do not split over {world} ranks")
+    sh, sw = cpu_.get_optimal_split(world)
+    T, Hh, W = wl.grid_k
+    if wl.grid_q != wl.grid_k or Hh % sh or W % sw or (Hh // sh) % wl.chunk[1] or (W // sw) % wl.chunk[2]:
+        raise SystemExit(f"grid {wl.grid_k} does not split {sh}x{sw} into block-aligned parts; use 720p_legal or 480p_legal")
+    local_grid = (T, Hh // sh, W // sw)
+    bsa_grid = (world * T, Hh // sh, W // sw)
+    local = Workload(wl.name + f"_rank{rank}", wl.seed + 17 * rank, 1, heads, wl.head_dim, local_grid, local_grid, wl.chunk,
+                     wl.sparsity, wl.dtype, wl.recipe)
+    q_h, k_h, v_h = (t.pin_memory() for t in make_qkv(local))
+    q, k, v = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h))
+    params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
+    scale = wl.head_dim ** -0.5
+    attn_events, launches = [], {"n": 0}
+
+    class Layer:
+        @ulysses_wrapper
+        def attn(self, q_, k_, v_, shape):
+            idx, cnt = B.get_select_indices(q_, k_, shape, shape, wl.sparsity, None, wl.chunk, wl.chunk)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            o = B.attn_fwd_bsa_varlen(q_, k_, v_, scale, idx, cnt, shape, shape, wl.chunk, wl.chunk, impl=attn_impl)
+            e1.record()
+            attn_events.append((e0, e1))
+            launches["n"] += 4
+            return o
+
+    layer = Layer()
+
+    def sync():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        out = layer.attn(q, k, v, bsa_grid)
+    sync()
+    L.check(L.lib().lcbsa_check_device_status())
+    assert out.shape == q.shape
+
+    nsel = int((1 - wl.sparsity) * ((bsa_grid[0] // wl.chunk[0]) * (bsa_grid[1] // wl.chunk[1]) * (bsa_grid[2] // wl.chunk[2])))
+    flops = 4.0 * heads * (wl.sq) * nsel * (wl.chunk[0] * wl.chunk[1] * wl.chunk[2]) * wl.head_dim  # whole job
+
+    sampler = None
+    if rank == 0:
+        from ..clocks import ClockSampler
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+    attn_events.clear()
+    launches["n"] = 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    start.record()
+    for _ in range(args.steps):
+        layer.attn(q, k, v, bsa_grid)
+    end.record()
+    sync()
+    clocks = sampler.stop() if sampler else None
+    L.check(L.lib().lcbsa_check_device_status())
+    ms_local = start.elapsed_time(end) / args.steps
+    ms_attn_local = sum(a.elapsed_time(b) for a, b in attn_events) / args.steps
+    t = torch.tensor([ms_local, ms_attn_local], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_attn = float(t[0]), float(t[1])
+
+    # end to end: host-resident shards in, host-resident result out, every step
+    e2e = None
+    if not args.skip_e2e:
+        out_h = torch.empty(q_h.shape, dtype=q_h.dtype).pin_memory()
+        qd, kd, vd = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+        def e2e_step():
+            qd.copy_(q_h, non_blocking=True)
+            kd.copy_(k_h, non_blocking=True)
+            vd.copy_(v_h, non_blocking=True)
+            out_h.copy_(layer.attn(qd, kd, vd, bsa_grid), non_blocking=True)
+
+        e2e_step()
+        n_e2e = max(3, min(args.steps, 10))
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        s2.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e2.record()
+        sync()
+        t2 = torch.tensor([s2.elapsed_time(e2) / n_e2e], device=dev)
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        es = q.element_size()
+        e2e = {"value": flops / float(t2[0]) / 1e9, "unit": "TFLOP/s", "ms_per_step": float(t2[0]),
+               "h2d_bytes_per_step": int(q_h.numel() * 3 * es * world), "d2h_bytes_per_step": int(out_h.numel() * es * world)}
+
+    if rank == 0:
+        attn_tf = flops / ms_attn / 1e9
+        peak = peaks["bf16_tflops"] * world
+        line = {"metric": "bsa_fwd_effective_tflops", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": wl.name, "grid": list(wl.grid_k), "rank_major_grid": list(bsa_grid), "heads": heads,
+                           "heads_per_gpu": heads // world, "head_dim": wl.head_dim, "block": list(wl.chunk),
+                           "sparsity": wl.sparsity, "selected_blocks": nsel, "algorithmic_tflop": flops / 1e12,
+                           "ms_attention_kernels": ms_attn, "cp_split_hw": [sh, sw],
+                           "l2": "inputs exceed the 126 MB L2; no flush between iterations",
+                           "parallelism": f"ulysses{world} (NCCL all-to-all in/out, pipelined by head group)"},
+                "roofline": {"bound": "tensor", "kernel": "attn_tc_kernel", "achieved": attn_tf, "peak": peak, "unit": "TFLOP/s",
+                             "frac": attn_tf / peak, "peak_source": f"{peak_src} (burst cuBLAS bf16 x {world} GPUs)",
+                             "ms_per_step_in_kernel": ms_attn, "traffic": None},
+                "cpu_baseline": None, "e2e": e2e, "clocks": clocks, "gpu_launches": launches["n"]}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

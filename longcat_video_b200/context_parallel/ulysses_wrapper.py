@@ -7,10 +7,10 @@ heads for ``[B, H/N, S, D]`` (all tokens of its own heads, sequence rank-major);
 inverse.  Identity when the context-parallel size is 1.
 
 What is different from the reference is how the bytes move:
-  * the exchange is one grouped NCCL send/recv per peer directly between views of the source and
-    destination tensors -- for a head group of one head and B = 1 both sides are already contiguous
-    slabs ``[S/N, D]``, so the two permute+contiguous copies the reference makes on each side of
-    every all-to-all disappear (other shapes take one staging copy instead of two);
+  * the exchange is one grouped NCCL send/recv per peer and head, directly between ``[S/N, D]`` slabs
+    of the source and destination tensors -- with B = 1 both sides are already contiguous, so the two
+    permute+contiguous copies the reference makes on each side of every all-to-all disappear (other
+    shapes take one staging copy instead of two);
   * ``ulysses_wrapper`` pipelines by head group: the all-to-all of group g+1 and the return
     all-to-all of group g-1 run on NCCL's stream while attention works on group g.  Heads are
     independent in BSA, so the result is the same as doing it in one piece.
@@ -65,9 +65,24 @@ def _views_or_staging(t: torch.Tensor, views: List[torch.Tensor]) -> Tuple[List[
     return [stage[i] for i in range(len(views))], stage
 
 
+def _finish(works, stage_pairs, out):
+    def finish():
+        for w in works:
+            if w is not None:
+                w.wait()
+        for dst, src in stage_pairs:
+            dst.copy_(src)
+        return out
+    return finish
+
+
 def heads_scatter_seq_gather(x: torch.Tensor, group, head_lo: int = 0, head_hi: Optional[int] = None,
                              async_op: bool = False):
-    """``[B, H, S/N, D] -> [B, h, S, D]`` for local heads ``head_lo:head_hi`` of this rank's ``H/N``."""
+    """``[B, H, S/N, D] -> [B, h, S, D]`` for local heads ``head_lo:head_hi`` of this rank's ``H/N``.
+
+    With B = 1 and contiguous ``[S/N, D]`` slabs the exchange is one grouped send/recv per head straight
+    between the slabs of ``x`` and of the result (no copy); otherwise it goes through one staging copy
+    per side."""
     n = dist.get_world_size(group)
     B, H, Sl, D = x.shape
     if H % n != 0:
@@ -76,24 +91,25 @@ def heads_scatter_seq_gather(x: torch.Tensor, group, head_lo: int = 0, head_hi: 
     head_hi = hn if head_hi is None else head_hi
     h = head_hi - head_lo
     out = torch.empty(B, h, n * Sl, D, dtype=x.dtype, device=x.device)
-    send_views = [x[:, r * hn + head_lo: r * hn + head_hi] for r in range(n)]
-    recv_views = [out[:, :, r * Sl:(r + 1) * Sl] for r in range(n)]
-    send, s_stage = _views_or_staging(x, send_views)
-    recv, r_stage = _views_or_staging(out, recv_views)
-    if s_stage is not None:
-        for r in range(n):
-            send[r].copy_(send_views[r])
-    work = _exchange(send, recv, group, async_op=async_op)
-
-    def finish():
-        if work is not None:
-            work.wait()
-        if r_stage is not None:
+    works, stage_pairs = [], []
+    if B == 1 and x[0, 0].is_contiguous():
+        for j in range(h):
+            send = [x[0, r * hn + head_lo + j] for r in range(n)]
+            recv = [out[0, j, r * Sl:(r + 1) * Sl] for r in range(n)]
+            works.append(_exchange(send, recv, group, async_op=async_op))
+    else:
+        send_views = [x[:, r * hn + head_lo: r * hn + head_hi] for r in range(n)]
+        recv_views = [out[:, :, r * Sl:(r + 1) * Sl] for r in range(n)]
+        send, s_stage = _views_or_staging(x, send_views)
+        recv, r_stage = _views_or_staging(out, recv_views)
+        if s_stage is not None:
             for r in range(n):
-                recv_views[r].copy_(recv[r])
-        return out
-
-    return finish if async_op else finish()
+                send[r].copy_(send_views[r])
+        works.append(_exchange(send, recv, group, async_op=async_op))
+        if r_stage is not None:
+            stage_pairs = [(recv_views[r], recv[r]) for r in range(n)]
+    fin = _finish(works, stage_pairs, out)
+    return fin if async_op else fin()
 
 
 def seq_scatter_heads_gather(x: torch.Tensor, group, out: Optional[torch.Tensor] = None, head_lo: int = 0,
@@ -108,24 +124,25 @@ def seq_scatter_heads_gather(x: torch.Tensor, group, out: Optional[torch.Tensor]
     hn = h if heads_per_rank is None else heads_per_rank
     if out is None:
         out = torch.empty(B, n * hn, Sl, D, dtype=x.dtype, device=x.device)
-    send_views = [x[:, :, r * Sl:(r + 1) * Sl] for r in range(n)]
-    recv_views = [out[:, r * hn + head_lo: r * hn + head_lo + h] for r in range(n)]
-    send, s_stage = _views_or_staging(x, send_views)
-    recv, r_stage = _views_or_staging(out, recv_views)
-    if s_stage is not None:
-        for r in range(n):
-            send[r].copy_(send_views[r])
-    work = _exchange(send, recv, group, async_op=async_op)
-
-    def finish():
-        if work is not None:
-            work.wait()
-        if r_stage is not None:
+    works, stage_pairs = [], []
+    if B == 1 and x.is_contiguous() and out[0, 0].is_contiguous():
+        for j in range(h):
+            send = [x[0, j, r * Sl:(r + 1) * Sl] for r in range(n)]
+            recv = [out[0, r * hn + head_lo + j] for r in range(n)]
+            works.append(_exchange(send, recv, group, async_op=async_op))
+    else:
+        send_views = [x[:, :, r * Sl:(r + 1) * Sl] for r in range(n)]
+        recv_views = [out[:, r * hn + head_lo: r * hn + head_lo + h] for r in range(n)]
+        send, s_stage = _views_or_staging(x, send_views)
+        recv, r_stage = _views_or_staging(out, recv_views)
+        if s_stage is not None:
             for r in range(n):
-                recv_views[r].copy_(recv[r])
-        return out
-
-    return finish if async_op else finish()
+                send[r].copy_(send_views[r])
+        works.append(_exchange(send, recv, group, async_op=async_op))
+        if r_stage is not None:
+            stage_pairs = [(recv_views[r], recv[r]) for r in range(n)]
+    fin = _finish(works, stage_pairs, out)
+    return fin if async_op else fin()
 
 
 def all_to_all(tensor, scatter_idx, gather_idx, group=None, gather=True):
@@ -179,9 +196,11 @@ def ulysses_a2a_out(output):
 
 
 def _heads_per_group(local_heads: int) -> int:
-    """Heads per pipeline stage: 1 (zero-copy slabs) unless LCBSA_ULYSSES_GROUP_HEADS says otherwise;
-    0 disables the pipelining."""
-    v = int(os.environ.get("LCBSA_ULYSSES_GROUP_HEADS", "1"))
+    """Heads per pipeline stage.  LCBSA_ULYSSES_GROUP_HEADS overrides it (0 = no pipelining); by default
+    the local heads are split into four stages (two when there are four heads or fewer), which keeps every
+    attention launch at several waves of work items while hiding most of the exchange."""
+    default = max(1, local_heads // 4) if local_heads > 4 else max(1, local_heads // 2)
+    v = int(os.environ.get("LCBSA_ULYSSES_GROUP_HEADS", str(default)))
     if v <= 0 or v >= local_heads:
         return local_heads
     while local_heads % v:
