@@ -35,9 +35,13 @@ from longcat_video_b200.synthetic import WORKLOADS, make_qkv  # noqa: E402
 METRIC = "bsa_fwd_effective_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram bytes (read + write) per attention launch from the committed ncu capture, scaled per unit of work;
-# see profiles/.  None until a capture exists for the workload.
-NCU_ATTN_DRAM_BYTES_PER_FLOP = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch over the bytes of q, k, v and out, from
+# the ncu capture summarised in profiles/attn_tc_kernel_480p_16heads.md (599.2 MB against 654.3 MB).  K and V of a
+# head are re-read from L2, so the traffic of a launch grows with the tensors, not with the selected blocks.
+NCU_ATTN_DRAM_PER_IO_BYTE = 599.2 / 654.3
+# the same for the block-select stage (profiles/score_topk_kernel_480p_16heads.md): two pool launches read q and k
+# once (163.6 + 4.1 MB each against 163.6 algorithmic), the score/top-k launch adds 5.1 MB.
+NCU_SELECT_DRAM_PER_IO_BYTE = (2 * 167.7 + 5.1) / (2 * 163.6)
 
 
 def load_peaks():
@@ -194,16 +198,18 @@ def main():
 
     es = q.element_size()
     select_bytes = es * wl.batch * heads * (wl.sq + wl.sk) * wl.head_dim  # read Q and K once
+    attn_io_bytes = es * wl.batch * heads * (2 * wl.sq + 2 * wl.sk) * wl.head_dim  # q, out, k, v once
     attn_tf = flops / ms_attn / 1e9
     roofline = {"bound": "tensor", "kernel": "attn_tc_kernel" if attn_impl != L.ATTN_MMA else "attn_mma_kernel",
                 "achieved": attn_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
                 "peak_source": f"{peak_src} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
                 "ms_per_launch": ms_attn,
-                "traffic": (NCU_ATTN_DRAM_BYTES_PER_FLOP * flops) if NCU_ATTN_DRAM_BYTES_PER_FLOP else None}
+                "traffic": (NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes) if attn_impl != L.ATTN_MMA else None,
+                "traffic_source": "ncu capture of 480p_legal/16 heads scaled by the bytes of q,k,v,out"}
     sel_gbs = select_bytes / ms_select / 1e6
     roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_topk_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
                        "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"], "peak_source": peak_src, "ms_per_stage": ms_select,
-                       "traffic": None}
+                       "traffic": NCU_SELECT_DRAM_PER_IO_BYTE * select_bytes}
 
     # ------------------------------------------------------------------ end to end from host buffers
     e2e = None
