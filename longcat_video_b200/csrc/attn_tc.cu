@@ -7,32 +7,35 @@
 //
 // Shape handled: head_dim 128, query and key blocks of 64 tokens, bf16 or fp16.
 //
-// One persistent CTA per SM.  A work item is four consecutive query blocks of one head, handled as
-// two pairs.  Each query block is a 64-row tile, i.e. an M=64 tcgen05 MMA whose accumulator
-// occupies 16 lanes of every 32-lane TMEM quadrant; the two tiles of a pair sit in the lower and the
-// upper 16 lanes of the same columns, so that one softmax warpgroup (128 threads, one TMEM lane each)
-// serves both with every lane busy.
+// One persistent CTA per SM.  A work item is a pair of consecutive query blocks of one head.  Each
+// query block is a 64-row tile, i.e. an M=64 tcgen05 MMA whose accumulator occupies 16 lanes of every
+// 32-lane TMEM quadrant; the two tiles of the pair sit in the lower and the upper 16 lanes of the same
+// columns, so that the softmax warpgroup (128 threads, one TMEM lane each) serves both with every lane busy.
 //
-//   warps 0-3 : softmax warpgroup of pair 0      warps 8,15 : TMA producers (Q tiles, ring of K/V slots)
-//   warps 4-7 : softmax warpgroup of pair 1      warps 9-12 : S = Q K^T issuers, one per tile
-//   warps 13,14 : O += P V issuers of pair 0 and pair 1
-// One thread can start a tcgen05.mma only about every 120 cycles (measured on B200, whatever the
-// shape), while these MMAs carry 32-64 cycles of math; six issuing warps, eight MMAs per iteration
-// each, bring the issue rate to the rate of the tensor pipe.
+//   warps 0-3 : softmax warpgroup           warp 4 : TMA producer (Q tiles, K ring, V ring)
+//   warp 5    : S = Q K^T issuer            warp 6 : O += P V issuer           warp 7 : output TMA stores
 //
-// Per selected K/V block and tile:  S = Q K^T  (M64 N64 K128, fp32 in TMEM)  ->  the softmax warpgroup
-// reads S with tcgen05.ld, exp2 online softmax in registers, P (input dtype) back into TMEM with
-// tcgen05.st  ->  O += P V  (M64 N128 K64, A operand from TMEM, fp32 accumulator in TMEM).
-// P never touches shared memory: the kernel is bound by shared-memory bandwidth (every K/V byte is
-// written by TMA and read by one MMA; Q is re-read for every block), so the P round trip is kept out of it.
-// The next S of a pair is issued as soon as the warpgroup has pulled the current one into registers, and
-// P is double-buffered, so a warpgroup never waits for the PV of the iteration before.
+// Per selected K/V block i and tile:  S(i) = Q K^T  (M64 N64 K128, fp32 in TMEM, double-buffered)  ->  the
+// warpgroup reads S(i) with tcgen05.ld (which frees the buffer for S(i+2)), exp2 online softmax in
+// registers, P(i) in the input dtype back into TMEM with tcgen05.st (double-buffered)  ->
+// O += P(i) V(i)  (M64 N128 K64, A operand from TMEM, fp32 accumulator in TMEM).
+// S runs two blocks ahead of the softmax and the softmax never waits for the PV of the block before, so
+// the three stages overlap; K and V have a ring of three slots each (a slot = the tiles of both query
+// blocks), filled in the order K0 K1 K2 V0 K3 V1 ..., which hides about two iterations of load latency.
+//
+// The MMAs are issued by whole converged warps with one elected lane (about 23 cycles per MMA for the
+// warp; a single lane inside a divergent branch needs 50 and more).
+//
 // The running maximum baked into O is only refreshed when the row maximum grows by more than 2^8
 // (the accumulated values stay finite and the result is unchanged after the final division), so O is
 // rarely rescaled in TMEM.
 //
-// TMEM columns (512), per pair at 256*pair: S at +0 (64 columns, fp32), P[buf] at +64 + 32*buf (the
-// probabilities in the input dtype, two per column, double-buffered), O at +128 (128 columns, fp32).
+// TMEM columns: S[buf] at 64*buf, P[buf] at 128 + 32*buf (two 16-bit probabilities per column),
+// O at 192 (128 columns); the second tile of the pair 16 lanes up in each.
+//
+// The finished O tile is staged in the V slot that the last PV of the work item has just released and
+// leaves by TMA store; the Q tiles are released as soon as the last S of the item has been computed, so
+// the next item's Q, K and S are in flight while this one finishes.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA records where, raises an abort
 // flag that all roles poll, drains its outstanding bulk copies, frees its TMEM and returns.
@@ -48,22 +51,23 @@ constexpr int kD = 128;
 constexpr int kBlk = 64;                    // tokens per query / key block
 constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB: one Q, K, V or O tile
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128 B, 128B-swizzled
-constexpr int kSlots = 5;                   // ring of K/V slots; a slot holds the tiles of both halves of a pair
-constexpr int kSlotBytes = 2 * kTileBytes;
-constexpr int kTilesPerWork = 4;
-constexpr int kThreads = 512;
-// setmaxnreg per warpgroup: (184 + 184 + 72 + 72) * 128 threads = the 128 * 512 registers the CTA starts with
-constexpr int kRegsSoftmax = 184, kRegsOther = 72;
+constexpr int kTilesPerWork = 2;            // the two query blocks of a pair
+constexpr int kSlotBytes = kTilesPerWork * kTileBytes;  // a ring slot holds the K (or V) tiles of both query blocks
+constexpr int kKSlots = 3, kVSlots = 3;
+constexpr int kThreads = 256;
 constexpr unsigned kSpinsBeforeClock = 1u << 12;     // failed try_waits before the clock is consulted
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s
 
+// TMEM columns
+constexpr uint32_t kTmS = 0, kTmP = 128, kTmO = 192;
+
 // shared memory map (offsets from a 1024-byte aligned base)
-constexpr int kOffQ = 0;                                   // 4 tiles (reused to stage O)
-constexpr int kOffKV = kOffQ + kTilesPerWork * kTileBytes;  // ring
-constexpr int kOffBar = kOffKV + kSlots * kSlotBytes;
-// barriers: slot_full[5] slot_empty[5] q_full[2] q_empty[2] s_full[2][2] p_full[2][2] pv_done[2][2] o_staged[2] s_free[2][2]
-// (of s_full / s_free only entry [pair][0] is in use: S is single-buffered)
-constexpr int kNumBars = 2 * kSlots + 2 + 2 + 4 + 4 + 4 + 2 + 4;
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kTilesPerWork * kTileBytes;
+constexpr int kOffV = kOffK + kKSlots * kSlotBytes;
+constexpr int kOffBar = kOffV + kVSlots * kSlotBytes;
+// barriers: k_full[3] k_empty[3] v_full[3] v_empty[3] q_full q_empty s_full[2] s_free[2] p_full[2] pv_done[2] o_free o_staged
+constexpr int kNumBars = 2 * kKSlots + 2 * kVSlots + 2 + 8 + 2;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;
 constexpr int kSmemBytes = kOffMisc + 64 + 1024;  // + slack for the 1024-byte alignment
 
@@ -83,8 +87,8 @@ struct TcParams {
     float scale2;   // sm_scale * log2(e)
     int is_bf16;
 #ifdef LCBSA_TC_DEBUG
-    float* dbg;     // [4 tiles][64 rows][64] raw S of the first work item's first iteration, then [4][64][128] raw O
-    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: producer, MMA thread, softmax warps 0 and 4
+    float* dbg;     // [2 tiles][64 rows][64] raw S of the first work item's first iteration, then [2][64][128] raw O
+    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: PV issuer, S issuer, softmax warp 0, producer
 #endif
 };
 
@@ -161,28 +165,6 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
     }
     return true;
 }
-// Bounded wait until a shared-memory word holds `want` (the producers publish which use of a ring slot
-// they have armed; see the MMA issuers).
-__device__ __forceinline__ bool word_wait_thread(const volatile uint32_t* word, uint32_t want, const Ctl& c, unsigned code,
-                                                 unsigned it) {
-    unsigned spins = 0;
-    long long t0 = 0;
-    while (*word != want) {
-        if (*c.abort) return false;
-        if (++spins == (kSpinsBeforeClock << 4)) t0 = clock64();
-        if (spins > (kSpinsBeforeClock << 4) && (spins & 1023u) == 0 && clock64() - t0 > kWaitLimitCycles) {
-            *c.abort = 1;
-            if (atomicCAS(c.status, 0u, code) == 0u) {
-                c.status[1] = blockIdx.x;
-                c.status[2] = threadIdx.x;
-                c.status[3] = it;
-            }
-            __threadfence();
-            return false;
-        }
-    }
-    return true;
-}
 // The same for all 32 lanes of a warp; the verdict is made warp-uniform so that the warp-collective
 // tcgen05 instructions that follow are never reached by only some of the lanes.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
@@ -210,15 +192,23 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// The three issuing wrappers below are called by ALL lanes of a converged warp; one elected lane issues.
+// Measured on B200: issued this way a tcgen05.mma costs its warp about 23 cycles, against about 50 (and up to
+// 125 next to busy arithmetic warps) when a single lane issues it from inside a divergent branch.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
         : "memory");
 }
@@ -226,9 +216,10 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
 // A operand from TMEM (M x K, two 16-bit elements per column), B from shared memory
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accum)
         : "memory");
 }
@@ -306,33 +297,7 @@ __device__ __forceinline__ uint32_t instr_desc(bool bf16, int M, int N, int b_mn
            ((uint32_t)(M >> 4) << 24);
 }
 
-// ------------------------------------------------------------------------------------------ schedule
-
-// The order in which K and V slots enter the ring is the order in which the MMA thread first uses them.
-// For a work item whose pairs run n0 and n1 iterations the events are
-//   S(0,0) S(1,0) S(0,1) S(1,1) | PV(0,0) S(0,2) PV(1,0) S(1,2) | PV(0,1) S(0,3) PV(1,1) S(1,3) | ...
-// (S runs two iterations ahead of the PV of the same pair; events past a pair's count are skipped).
-struct Event {
-    int pair, iter, is_pv, valid;
-};
-__device__ __forceinline__ Event event_at(int e, int n0, int n1) {
-    Event ev;
-    if (e < 4) {
-        ev.pair = e & 1; ev.iter = e >> 1; ev.is_pv = 0;
-    } else {
-        const int k = e - 4;
-        ev.pair = (k >> 1) & 1;
-        ev.is_pv = (k & 1) == 0;
-        ev.iter = (k >> 2) + (ev.is_pv ? 0 : 2);
-    }
-    ev.valid = ev.iter < (ev.pair ? n1 : n0);
-    return ev;
-}
-__device__ __forceinline__ int num_events(int n0, int n1) { return 4 + 4 * max(n0, n1); }
-
-__device__ __forceinline__ int sel4(int a0, int a1, int a2, int a3, int i) {
-    return i == 0 ? a0 : i == 1 ? a1 : i == 2 ? a2 : a3;
-}
+// ------------------------------------------------------------------------------------------ kernel
 
 struct Coord {
     int c1, c2, c3, c4;
@@ -353,165 +318,165 @@ __device__ __forceinline__ int clamp_cnt(const TcParams& P, int bh, int qt) {
     return qt < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
 }
 
-// ------------------------------------------------------------------------------------------ kernel
-
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + kOffBar;
-    auto bar_slot_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_slot_empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
-    auto bar_q_full = [&](int p) { return bar0 + 8u * (2 * kSlots + p); };
-    auto bar_q_empty = [&](int p) { return bar0 + 8u * (2 * kSlots + 2 + p); };
-    auto bar_s_full = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 4 + 2 * p + buf); };
-    // p_full and pv_done exist once per P buffer: the warpgroup may run two rounds ahead of the PV issuer, and a
-    // parity wait is only exact while the waiter is at most one phase away from the barrier.
-    auto bar_p_full = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 8 + 2 * p + buf); };
-    auto bar_pv_done = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 12 + 2 * p + buf); };
-    auto bar_o_staged = [&](int p) { return bar0 + 8u * (2 * kSlots + 16 + p); };
-    auto bar_s_free = [&](int p, int buf) { return bar0 + 8u * (2 * kSlots + 18 + 2 * p + buf); };
+    auto bar_k_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_k_empty = [&](int s) { return bar0 + 8u * (kKSlots + s); };
+    auto bar_v_full = [&](int s) { return bar0 + 8u * (2 * kKSlots + s); };
+    auto bar_v_empty = [&](int s) { return bar0 + 8u * (2 * kKSlots + kVSlots + s); };
+    constexpr int kB0 = 2 * kKSlots + 2 * kVSlots;
+    const uint32_t bar_q_full = bar0 + 8u * kB0, bar_q_empty = bar0 + 8u * (kB0 + 1);
+    auto bar_s_full = [&](int buf) { return bar0 + 8u * (kB0 + 2 + buf); };
+    auto bar_s_free = [&](int buf) { return bar0 + 8u * (kB0 + 4 + buf); };
+    auto bar_p_full = [&](int buf) { return bar0 + 8u * (kB0 + 6 + buf); };
+    auto bar_pv_done = [&](int buf) { return bar0 + 8u * (kB0 + 8 + buf); };
+    const uint32_t bar_o_free = bar0 + 8u * (kB0 + 10), bar_o_staged = bar0 + 8u * (kB0 + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
-    volatile uint32_t* slot_use = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc + 16);  // [kSlots] use number armed (20 bytes)
     const Ctl ctl{abort_flag, P.status};
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same value, but provably warp-uniform
 #ifdef LCBSA_TC_DEBUG
     int ts_n = 0;
 #endif
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < kSlots; ++s) slot_use[s] = 0xffffffffu;
-        for (int s = 0; s < kSlots; ++s) {
-            mbar_init(bar_slot_full(s), 1);
-            mbar_init(bar_slot_empty(s), 2);  // K slots: the two S issuers of a pair; V slots: the PV issuer, twice
+        for (int s = 0; s < kKSlots; ++s) {
+            mbar_init(bar_k_full(s), 1);
+            mbar_init(bar_k_empty(s), 1);
         }
-        for (int p = 0; p < 2; ++p) {
-            mbar_init(bar_q_full(p), 1);
-            mbar_init(bar_q_empty(p), 1);
-            mbar_init(bar_s_full(p, 0), 2);  // one commit per S issuer (tile) of the pair
-            mbar_init(bar_s_full(p, 1), 2);
-            for (int b = 0; b < 2; ++b) {
-                mbar_init(bar_p_full(p, b), 4);  // one elected arrival per softmax warp
-                mbar_init(bar_pv_done(p, b), 1);
-            }
-            mbar_init(bar_o_staged(p), 4);
-            mbar_init(bar_s_free(p, 0), 4);
-            mbar_init(bar_s_free(p, 1), 4);
+        for (int s = 0; s < kVSlots; ++s) {
+            mbar_init(bar_v_full(s), 1);
+            mbar_init(bar_v_empty(s), 1);
         }
+        mbar_init(bar_q_full, 1);
+        mbar_init(bar_q_empty, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_s_full(b), 1);
+            mbar_init(bar_s_free(b), 4);  // one elected arrival per softmax warp
+            mbar_init(bar_p_full(b), 4);
+            mbar_init(bar_pv_done(b), 1);
+        }
+        mbar_init(bar_o_free, 4);
+        mbar_init(bar_o_staged, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {  // TMEM: all 512 columns, allocated and freed by the MMA warp
+    if (warp == 5) {  // TMEM: all 512 columns, allocated and freed by the S issuer
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
     const int groups = (P.nq + kTilesPerWork - 1) / kTilesPerWork;
     const long long total_work = (long long)P.bh_total * groups;
     constexpr bool bf16 = kBf16;
 
-    // Register budgets are set inside each role's own branch: the compiler sizes a region by the
-    // setmaxnreg that dominates it.
-    if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-      if (warp == 8 || warp == 15) {
-        // ================================================================== TMA producers
-        // Two producer warps (8 and 15) share the ring: a ring slot is always filled by the same producer
-        // (slot index & 1), which keeps its parity wait on slot_empty exact.
-        // Each walks the whole event list (that is what numbers the slots) and keeps the block
-        // coordinates of every tile's pending iterations, but issues copies for its own slots only.
-        const int my_prod = warp == 8 ? 0 : 1;
-        unsigned slot_n = 0;  // slots of the event list passed so far
-        unsigned wk = 0;
+    // All roles walk the same list of work items and count the same global iteration number `gi`:
+    // iteration gi uses K slot gi % 3, V slot gi % 3, S and P buffer gi & 1.
+    if (warp == 4) {
+        // ================================================================== TMA producer
+        unsigned gk = 0, gv = 0, wk = 0, nq_issued = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
             const int b = bh / P.heads, h = bh % P.heads;
-            const int c0 = clamp_cnt(P, bh, g * kTilesPerWork + 0), c1 = clamp_cnt(P, bh, g * kTilesPerWork + 1);
-            const int c2 = clamp_cnt(P, bh, g * kTilesPerWork + 2), c3 = clamp_cnt(P, bh, g * kTilesPerWork + 3);
-            // Q tiles of both pairs (the previous work item's output has left the same shared memory)
-            for (int p = 0; p < 2 && ok && my_prod == 0; ++p) {
-                ok = mbar_wait_warp(bar_q_empty(p), (wk & 1) ^ 1, ctl, 10 + p, wk);
-                if (!ok) break;
-                if (lane == 0) {
-                    int ntile = 0;
-                    for (int hf = 0; hf < 2; ++hf) ntile += (g * kTilesPerWork + 2 * p + hf) < P.nq;
-                    mbar_arrive_tx(bar_q_full(p), ntile * kTileBytes);
-                    for (int hf = 0; hf < 2; ++hf) {
-                        const int t = 2 * p + hf, qt = g * kTilesPerWork + t;
-                        if (qt >= P.nq) continue;
-                        const Coord cc = block_coord(P.gq, qt, b, h, P.heads, P.merge_q, P.Tq);
-                        const uint32_t dst = sbase + kOffQ + t * kTileBytes;
-                        tma_load_5d(dst, &P.tm_q, bar_q_full(p), 0, cc.c1, cc.c2, cc.c3, cc.c4);
-                        tma_load_5d(dst + kHalfBytes, &P.tm_q, bar_q_full(p), 64, cc.c1, cc.c2, cc.c3, cc.c4);
-                    }
+            const int qa = g * kTilesPerWork, qb = qa + 1;
+            const int ca = clamp_cnt(P, bh, qa), cb = clamp_cnt(P, bh, qb);
+            const int n_iter = max(1, max(ca, cb));
+            // Q tiles: the buffer is free once the last S of the previous item has been computed
+            ok = mbar_wait_warp(bar_q_empty, (wk & 1) ^ 1, ctl, 10, wk);
+            if (!ok) break;
+            ++nq_issued;
+            if (lane == 0) {
+                const int ntile = (qa < P.nq) + (qb < P.nq);
+                mbar_arrive_tx(bar_q_full, ntile * kTileBytes);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int qt = qa + hf;
+                    if (qt >= P.nq) continue;
+                    const Coord cc = block_coord(P.gq, qt, b, h, P.heads, P.merge_q, P.Tq);
+                    const uint32_t dst = sbase + kOffQ + hf * kTileBytes;
+                    tma_load_5d(dst, &P.tm_q, bar_q_full, 0, cc.c1, cc.c2, cc.c3, cc.c4);
+                    tma_load_5d(dst + kHalfBytes, &P.tm_q, bar_q_full, 64, cc.c1, cc.c2, cc.c3, cc.c4);
                 }
             }
-            const int n0 = max(c0, c1), n1 = max(c2, c3);
-            const int nev = num_events(n0, n1);
-            // Block coordinates are prefetched and decoded by the whole warp: lane L holds, for tile
-            // (L & 3) and iteration win + (L >> 2), the block's first token packed as t << 20 | h << 10 | w;
-            // a second register holds the next window of eight iterations.
-            const int my_t = lane & 3, my_s = lane >> 2;
-            const int my_c = sel4(c0, c1, c2, c3, my_t);
-            const int32_t* my_l = P.idx + ((long long)bh * P.nq + min(g * kTilesPerWork + my_t, P.nq - 1)) * P.cap;
+            // Block coordinates are fetched and decoded by the whole warp: lane L holds, for tile (L & 1) and
+            // iteration win + (L >> 1), the block's first token packed as t << 20 | h << 10 | w.  `prv` and `nxt`
+            // hold the windows of sixteen iterations before and after (V trails K by two iterations).
+            const int my_t = lane & 1, my_s = lane >> 1;
+            const int my_c = my_t ? cb : ca;
+            const int32_t* my_l = P.idx + ((long long)bh * P.nq + min(qa + my_t, P.nq - 1)) * P.cap;
             auto fetch = [&](int it) {
                 if (it >= my_c) return 0;
                 int bt, bhh, bw;
                 block_coords(P.gk, my_l[it], bt, bhh, bw);
                 return ((bt * P.gk.ct) << 20) | ((bhh * P.gk.ch) << 10) | (bw * P.gk.cw);
             };
-            int win = 0;
+            int win = 0, prv = 0;
             int cur = fetch(my_s);
-            int nxt = fetch(8 + my_s);
-            // packed coordinates of the iterations whose K is queued and whose V is not yet: [tile][iteration parity]
-            int pe0 = 0, pe1 = 0, pe2 = 0, pe3 = 0, po0 = 0, po1 = 0, po2 = 0, po3 = 0;
-            for (int e = 0; e < nev && ok; ++e) {
-                const Event ev = event_at(e, n0, n1);
-                if (!ev.valid) continue;
-                const int ta = 2 * ev.pair, tb = ta + 1;
-                const bool act_a = ev.iter < sel4(c0, c1, c2, c3, ta), act_b = ev.iter < sel4(c0, c1, c2, c3, tb);
-                if (!ev.is_pv) {
-                    while (ev.iter >= win + 8) {
-                        win += 8;
+            int nxt = fetch(16 + my_s);
+            const int c3k = P.merge_k ? b * P.Tk : 0, c4k = P.merge_k ? h : b * P.heads + h;
+            const int c3v = P.merge_v ? b * P.Tk : 0, c4v = P.merge_v ? h : b * P.heads + h;
+            for (int j = 0; j < n_iter + 2 && ok; ++j) {
+                if (j < n_iter) {  // K(j)
+                    while (j >= win + 16) {
+                        win += 16;
+                        prv = cur;
                         cur = nxt;
-                        nxt = fetch(win + 8 + my_s);
+                        nxt = fetch(win + 16 + my_s);
                     }
-                    const int va = __shfl_sync(0xffffffffu, cur, ((ev.iter - win) << 2) | ta);
-                    const int vb = __shfl_sync(0xffffffffu, cur, ((ev.iter - win) << 2) | tb);
-                    if (ev.iter & 1) {
-                        if (ev.pair) { po2 = va; po3 = vb; } else { po0 = va; po1 = vb; }
-                    } else {
-                        if (ev.pair) { pe2 = va; pe3 = vb; } else { pe0 = va; pe1 = vb; }
+                    const int pa = __shfl_sync(0xffffffffu, cur, ((j - win) << 1) | 0);
+                    const int pb = __shfl_sync(0xffffffffu, cur, ((j - win) << 1) | 1);
+                    const bool act_a = j < ca, act_b = j < cb;
+                    const int slot = gk % kKSlots;
+                    ok = mbar_wait_warp(bar_k_empty(slot), ((gk / kKSlots) & 1) ^ 1, ctl, 20, gk);
+                    if (!ok) break;
+                    ++gk;
+                    if (lane == 0) {
+                        LCBSA_TS(3, 10000 + j);
+                        mbar_arrive_tx(bar_k_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            if (!(hf ? act_b : act_a)) continue;
+                            const int pk = hf ? pb : pa;
+                            const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3k;
+                            const uint32_t dst = sbase + kOffK + slot * kSlotBytes + hf * kTileBytes;
+                            tma_load_5d(dst, &P.tm_k, bar_k_full(slot), 0, cw, chh, ctt, c4k);
+                            tma_load_5d(dst + kHalfBytes, &P.tm_k, bar_k_full(slot), 64, cw, chh, ctt, c4k);
+                        }
                     }
                 }
-                const unsigned n = slot_n++;
-                const int slot = n % kSlots;
-                if ((slot & 1) != my_prod) continue;
-                ok = mbar_wait_warp(bar_slot_empty(slot), ((n / kSlots) & 1) ^ 1, ctl, 20, n);
-                if (!ok) break;
-                if (lane == 0) {
-                    if (warp == 15) LCBSA_TS(0, 100000 + ev.iter * 10 + ev.pair);
-                    const CUtensorMap* tm = ev.is_pv ? &P.tm_v : &P.tm_k;
-                    const int merge = ev.is_pv ? P.merge_v : P.merge_k;
-                    const int c3_add = merge ? b * P.Tk : 0, c4 = merge ? h : b * P.heads + h;
-                    slot_use[slot] = n / kSlots;  // this use of the slot is armed: its consumer may now wait on slot_full
-                    mbar_arrive_tx(bar_slot_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
+                if (j >= 2) {  // V(j - 2)
+                    const int jj = j - 2;
+                    const int src = jj >= win ? cur : prv;
+                    const int o = jj >= win ? jj - win : jj - (win - 16);
+                    const int pa = __shfl_sync(0xffffffffu, src, (o << 1) | 0);
+                    const int pb = __shfl_sync(0xffffffffu, src, (o << 1) | 1);
+                    const bool act_a = jj < ca, act_b = jj < cb;
+                    const int slot = gv % kVSlots;
+                    ok = mbar_wait_warp(bar_v_empty(slot), ((gv / kVSlots) & 1) ^ 1, ctl, 22, gv);
+                    if (!ok) break;
+                    ++gv;
+                    if (lane == 0) {
+                        LCBSA_TS(3, 20000 + jj);
+                        mbar_arrive_tx(bar_v_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
 #pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        if (!(hf ? act_b : act_a)) continue;
-                        const int pk = (ev.iter & 1) ? sel4(po0, po1, po2, po3, ta + hf) : sel4(pe0, pe1, pe2, pe3, ta + hf);
-                        const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3_add;
-                        const uint32_t dst = sbase + kOffKV + slot * kSlotBytes + hf * kTileBytes;
-                        tma_load_5d(dst, tm, bar_slot_full(slot), 0, cw, chh, ctt, c4);
-                        tma_load_5d(dst + kHalfBytes, tm, bar_slot_full(slot), 64, cw, chh, ctt, c4);
+                        for (int hf = 0; hf < 2; ++hf) {
+                            if (!(hf ? act_b : act_a)) continue;
+                            const int pk = hf ? pb : pa;
+                            const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3v;
+                            const uint32_t dst = sbase + kOffV + slot * kSlotBytes + hf * kTileBytes;
+                            tma_load_5d(dst, &P.tm_v, bar_v_full(slot), 0, cw, chh, ctt, c4v);
+                            tma_load_5d(dst + kHalfBytes, &P.tm_v, bar_v_full(slot), 64, cw, chh, ctt, c4v);
+                        }
                     }
                 }
             }
@@ -519,152 +484,134 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         if (!ok && lane == 0) {
             // drain: give the copies this warp issued a bounded time to land before the CTA exits
             const long long t0 = clock64();
-            for (unsigned r = slot_n > kSlots ? slot_n - kSlots : 0; r < slot_n; ++r)
-                while ((int)((r % kSlots) & 1) == my_prod && !mbar_try(bar_slot_full(r % kSlots), (r / kSlots) & 1) &&
-                       clock64() - t0 < 40000000ll) {
+            for (unsigned r = gk > kKSlots ? gk - kKSlots : 0; r < gk; ++r)
+                while (!mbar_try(bar_k_full(r % kKSlots), (r / kKSlots) & 1) && clock64() - t0 < 40000000ll) {
+                }
+            for (unsigned r = gv > kVSlots ? gv - kVSlots : 0; r < gv; ++r)
+                while (!mbar_try(bar_v_full(r % kVSlots), (r / kVSlots) & 1) && clock64() - t0 < 40000000ll) {
+                }
+            if (nq_issued > 0)
+                while (!mbar_try(bar_q_full, (nq_issued - 1) & 1) && clock64() - t0 < 40000000ll) {
                 }
         }
-      } else {
-        // ================================================================== MMA issuers
-        // warps 9-12: S of (pair, tile) = (0,0) (0,1) (1,0) (1,1).   warps 13 / 14: PV of pair 0 / 1.
-        // Every issuer walks the same event list as the producer (that fixes which ring slot belongs to
-        // which event) and acts on its own events only.
-        const bool my_pv = warp >= 13;
-        const int my_pair = my_pv ? warp - 13 : (warp - 9) >> 1;
-        const int my_hf = (warp - 9) & 1;  // S issuers: which tile of the pair
+    } else if (warp == 5) {
+        // ================================================================== S = Q K^T issuer
         const uint32_t idesc_s = instr_desc(bf16, 64, 64, 0);
-        const uint32_t idesc_pv = instr_desc(bf16, 64, 128, 1);
-        unsigned slot_n = 0, wk = 0;
-        unsigned n_own = 0;  // own events issued so far: S buffer = n_own & 1, phase of p_full = n_own & 1
+        unsigned gi = 0, wk = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
-            const int c0 = clamp_cnt(P, bh, g * kTilesPerWork + 0), c1 = clamp_cnt(P, bh, g * kTilesPerWork + 1);
-            const int c2 = clamp_cnt(P, bh, g * kTilesPerWork + 2), c3 = clamp_cnt(P, bh, g * kTilesPerWork + 3);
-            const int n0 = max(c0, c1), n1 = max(c2, c3);
-            const int nev = num_events(n0, n1);
-            const int ca = my_pair ? c2 : c0, cb = my_pair ? c3 : c1;
-            for (int e = 0; e < nev && ok; ++e) {
-                const Event ev = event_at(e, n0, n1);
-                if (!ev.valid) continue;
-                const unsigned slot = slot_n % kSlots, slot_phase = (slot_n / kSlots) & 1;
-                ++slot_n;
-                if (ev.pair != my_pair || (ev.is_pv != 0) != my_pv) continue;
-                const uint32_t slot_addr = sbase + kOffKV + slot * kSlotBytes;
-                const bool act_a = ev.iter < ca, act_b = ev.iter < cb;
-                // The slots of the ring are consumed by four different warps, so this warp may get here while the
-                // slot is still two uses back; a parity wait on slot_full would then be satisfied by the wrong
-                // phase.  The producer publishes the use number it has armed, which makes the parity wait exact.
-                const unsigned slot_use_no = (slot_n - 1) / kSlots;
-                ok = __all_sync(0xffffffffu, word_wait_thread(slot_use + slot, slot_use_no, ctl, 38, slot_n));
+            const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            const int n_iter = max(1, max(ca, cb));
+            ok = mbar_wait_warp(bar_q_full, wk & 1, ctl, 30, wk);
+            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
+                const int slot = gi % kKSlots, buf = gi & 1;
+                if (lane == 0) LCBSA_TS(1, 10000 + i);
+                ok = mbar_wait_warp(bar_k_full(slot), (gi / kKSlots) & 1, ctl, 40, gi);
+                if (lane == 0) LCBSA_TS(1, 20000 + i);
+                // the warpgroup has pulled S(gi - 2) out of this buffer
+                if (ok) ok = mbar_wait_warp(bar_s_free(buf), ((gi >> 1) & 1) ^ 1, ctl, 34, gi);
                 if (!ok) break;
-                if (!my_pv) {
-                    // ---- S(p, iter) = Q K^T, once the warpgroup has pulled the previous S into registers
-                    if (warp == 9 && lane == 0) LCBSA_TS(1, 10000 + ev.iter);
-                    if (ev.iter == 0) ok = mbar_wait_warp(bar_q_full(my_pair), wk & 1, ctl, 30 + my_pair, wk);
-                    if (ok) ok = mbar_wait_warp(bar_s_free(my_pair, 0), (n_own & 1) ^ 1, ctl, 34 + my_pair, n_own);
-                    if (warp == 9 && lane == 0) LCBSA_TS(1, 20000 + ev.iter);
-                    if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 40, slot_n);
-                    if (!ok) break;
-                    if (warp == 9 && lane == 0) LCBSA_TS(1, 30000 + ev.iter);
-                    tc_fence_after();
-                    if (lane == 0) {
-                        if (my_hf ? act_b : act_a) {
-                            const uint64_t qd = smem_desc(sbase + kOffQ + (2 * my_pair + my_hf) * kTileBytes, 16, 1024);
-                            const uint64_t kd = smem_desc(slot_addr + my_hf * kTileBytes, 16, 1024);
-                            const uint32_t d = tmem + 256u * my_pair + ((16u * my_hf) << 16);
+                if (lane == 0) LCBSA_TS(1, 30000 + i);
+                tc_fence_after();
 #pragma unroll
-                            for (int j = 0; j < kD / 16; ++j) {
-                                // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
-                                const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
-                                tc_mma(d, qd + off, kd + off, idesc_s, j > 0);
-                            }
-                        }
-                        tc_commit(bar_slot_empty(slot));  // this tile's K is free once these MMAs have read it
-                        tc_commit(bar_s_full(my_pair, 0));
-                        if (warp == 9) LCBSA_TS(1, 40000 + ev.iter);
-                    }
-                    __syncwarp();
-                } else {
-                    // ---- O(p) += P V
-                    ok = mbar_wait_warp(bar_p_full(my_pair, n_own & 1), (n_own >> 1) & 1, ctl, 50 + my_pair, n_own);
-                    if (ok) ok = mbar_wait_warp(bar_slot_full(slot), slot_phase, ctl, 60, slot_n);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) {
-                        // A: P in TMEM (buffer n_own & 1), 8 columns per 16-key step; the second tile of the pair
-                        // sits 16 lanes up, like its accumulators.
-                        // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
-                        const uint32_t pa = tmem + 256u * my_pair + 64u + 32u * (n_own & 1);
-                        const uint64_t va = smem_desc(slot_addr, kHalfBytes, 1024);
-                        const uint64_t vb = smem_desc(slot_addr + kTileBytes, kHalfBytes, 1024);
-                        const uint32_t d = tmem + 256u * my_pair + 128u;
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (!(i < (hf ? cb : ca))) continue;  // warp-uniform
+                    const uint64_t qd = smem_desc(sbase + kOffQ + hf * kTileBytes, 16, 1024);
+                    const uint64_t kd = smem_desc(sbase + kOffK + slot * kSlotBytes + hf * kTileBytes, 16, 1024);
+                    const uint32_t d = tmem + kTmS + 64u * buf + ((16u * hf) << 16);
 #pragma unroll
-                        for (int j = 0; j < kBlk / 16; ++j) {
-                            const uint32_t acc = (ev.iter > 0 || j > 0) ? 1u : 0u;
-                            if (act_a) tc_mma_ts(d, pa + 8u * j, va + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
-                            if (act_b) tc_mma_ts(d + (16u << 16), pa + 8u * j + (16u << 16), vb + (uint64_t)((j * 2048) >> 4), idesc_pv, acc);
-                        }
-                        tc_commit(bar_slot_empty(slot));
-                        tc_commit(bar_slot_empty(slot));  // the barrier counts two arrivals (see the K slots)
-                        tc_commit(bar_pv_done(my_pair, n_own & 1));
+                    for (int j = 0; j < kD / 16; ++j) {
+                        // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
+                        const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
+                        tc_mma(d, qd + off, kd + off, idesc_s, j > 0);
                     }
-                    __syncwarp();
                 }
-                ++n_own;
+                tc_commit(bar_k_empty(slot));  // K is free once these MMAs have read it
+                tc_commit(bar_s_full(buf));
+                if (i == n_iter - 1) tc_commit(bar_q_empty);  // and so is Q after the last S of the item
+                if (lane == 0) LCBSA_TS(1, 40000 + i);
             }
         }
-        __syncwarp();
-      }
-    } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        // ================================================================== softmax warpgroups
-        const int p = warp >> 2;          // pair
-        const int wq = warp & 3;          // TMEM quadrant of this warp
+    } else if (warp == 6) {
+        // ================================================================== O += P V issuer
+        const uint32_t idesc_pv = instr_desc(bf16, 64, 128, 1);
+        unsigned gi = 0, wk = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
+            const int bh = (int)(w / groups), g = (int)(w % groups);
+            const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            const int n_iter = max(1, max(ca, cb));
+            // the epilogue of the previous item has read O
+            ok = mbar_wait_warp(bar_o_free, (wk & 1) ^ 1, ctl, 36, wk);
+            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
+                const int slot = gi % kVSlots, buf = gi & 1;
+                if (lane == 0) LCBSA_TS(0, 10000 + i);
+                ok = mbar_wait_warp(bar_v_full(slot), (gi / kVSlots) & 1, ctl, 60, gi);
+                if (lane == 0) LCBSA_TS(0, 20000 + i);
+                if (ok) ok = mbar_wait_warp(bar_p_full(buf), (gi >> 1) & 1, ctl, 50, gi);
+                if (!ok) break;
+                if (lane == 0) LCBSA_TS(0, 30000 + i);
+                tc_fence_after();
+                // A: P in TMEM (buffer gi & 1), 8 columns per 16-key step; the second tile of the pair sits 16
+                // lanes up, like its accumulators.
+                // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (!(i < (hf ? cb : ca))) continue;  // warp-uniform
+                    const uint32_t pa = tmem + kTmP + 32u * buf + ((16u * hf) << 16);
+                    const uint64_t vd = smem_desc(sbase + kOffV + slot * kSlotBytes + hf * kTileBytes, kHalfBytes, 1024);
+                    const uint32_t d = tmem + kTmO + ((16u * hf) << 16);
+#pragma unroll
+                    for (int j = 0; j < kBlk / 16; ++j)
+                        tc_mma_ts(d, pa + 8u * j, vd + (uint64_t)((j * 2048) >> 4), idesc_pv, (i > 0 || j > 0) ? 1u : 0u);
+                }
+                // the V slot of the item's last block goes to the epilogue, which stages O in it and frees it
+                if (i < n_iter - 1) tc_commit(bar_v_empty(slot));
+                tc_commit(bar_pv_done(buf));
+                if (lane == 0) LCBSA_TS(0, 40000 + i);
+            }
+        }
+    } else if (warp < 4) {
+        // ================================================================== softmax warpgroup
+        const int wq = warp;              // TMEM quadrant of this warp
         const int hf = lane >> 4;         // tile of the pair this lane serves
         const int row = wq * 16 + (lane & 15);  // row of that tile
-        const int t = 2 * p + hf;
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
-        const uint32_t tm_s = tmem + 256u * p + t_lane;
-        const uint32_t tm_o = tm_s + 128u;
-        unsigned char* o_tile = smem + kOffQ + t * kTileBytes;
-        unsigned n_s = 0, wk = 0;      // S rounds done (= P buffers filled) over the whole kernel
-        unsigned n_pv0 = 0, n_pv1 = 0;  // pv_done phases consumed, per P buffer
+        const uint32_t tm_s = tmem + kTmS + t_lane, tm_p = tmem + kTmP + t_lane, tm_o = tmem + kTmO + t_lane;
+        unsigned gi = 0, wk = 0;
         bool ok = true;
 
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
-            const int b = bh / P.heads, h = bh % P.heads;
-            const int qt = g * kTilesPerWork + t;
+            const int qt = g * kTilesPerWork + hf;
             const bool tile_valid = qt < P.nq;
             const int my_cnt = clamp_cnt(P, bh, qt);
-            const int other_cnt = clamp_cnt(P, bh, g * kTilesPerWork + (t ^ 1));
-            const int n_iter = max(my_cnt, other_cnt);
+            const int other_cnt = clamp_cnt(P, bh, g * kTilesPerWork + (hf ^ 1));
+            const int n_iter = max(1, max(my_cnt, other_cnt));
             const int32_t* my_list = P.idx + ((long long)bh * P.nq + (tile_valid ? qt : 0)) * P.cap;
 
             float m_ref = -INFINITY, l_sum = 0.f;
 
-            ok = mbar_wait_warp(bar_q_full(p), wk & 1, ctl, 70 + p, wk);
-            if (!ok) break;
-
-            for (int i = 0; i < n_iter && ok; ++i) {
+            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
                 const bool active = i < my_cnt;
-                const unsigned round = n_s;  // index of this (pair, iteration) over the whole kernel
-                ok = mbar_wait_warp(bar_s_full(p, 0), n_s & 1, ctl, 80 + p, n_s);
+                const int buf = gi & 1;
+                const unsigned bph = (gi >> 1) & 1;
+                if (warp == 0 && lane == 0) LCBSA_TS(2, 10000 + i);
+                ok = mbar_wait_warp(bar_s_full(buf), bph, ctl, 80, gi);
                 if (!ok) break;
-                ++n_s;
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 10000 + i);
+                if (warp == 0 && lane == 0) LCBSA_TS(2, 20000 + i);
                 tc_fence_after();
                 uint32_t sr[64];
-                tc_ld64(tm_s, sr);
+                tc_ld64(tm_s + 64u * buf, sr);
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_s_free(p, 0));  // S may be overwritten by the next one
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 20000 + i);
+                if (lane == 0) mbar_arrive(bar_s_free(buf));  // the buffer may take S(gi + 2)
+                if (warp == 0 && lane == 0) LCBSA_TS(2, 30000 + i);
 #ifdef LCBSA_TC_DEBUG
                 if (P.dbg && w == 0 && i == 0)
-                    for (int j = 0; j < 64; ++j) P.dbg[(t * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
+                    for (int j = 0; j < 64; ++j) P.dbg[(hf * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
 #endif
                 float alpha = 1.f;
                 bool need = false;
@@ -724,28 +671,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                     l_sum = l_sum * alpha + rs;  // alpha is 1 unless this row's reference maximum moved
                 }
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 30000 + i);
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 40000 + i);
-                // P buffer (round & 1) was last read by the PV two rounds ago; O must be at rest (PV of the round
-                // before finished) before it is rescaled.  pv_done phases are consumed strictly in order.
+                if (warp == 0 && lane == 0) LCBSA_TS(2, 40000 + i);
                 const bool any_need = __any_sync(0xffffffffu, need);
-                // PV of round r signals pv_done[r & 1] (as that barrier's phase r >> 1).  Every PV up to round x must
-                // have finished, x = round - 2 (it read the P buffer about to be overwritten) or round - 1 when O is
-                // going to be rescaled.  Phases are consumed in order, per buffer.
-                {
-                    const int x = (int)round - (any_need ? 1 : 2);
-                    const unsigned need0 = x >= 0 ? (unsigned)(x >> 1) + 1u : 0u;   // even rounds <= x
-                    const unsigned need1 = x >= 1 ? (unsigned)((x + 1) >> 1) : 0u;  // odd rounds <= x
-                    while (n_pv0 < need0 && ok) {
-                        ok = mbar_wait_warp(bar_pv_done(p, 0), n_pv0 & 1, ctl, 90 + p, n_pv0);
-                        ++n_pv0;
-                    }
-                    while (n_pv1 < need1 && ok) {
-                        ok = mbar_wait_warp(bar_pv_done(p, 1), n_pv1 & 1, ctl, 92 + p, n_pv1);
-                        ++n_pv1;
-                    }
-                    if (!ok) break;
-                }
+                // P buffer gi & 1 was last read by PV(gi - 2); pv_done[buf] completes its phase (gi - 2) >> 1 then.
+                ok = mbar_wait_warp(bar_pv_done(buf), bph ^ 1, ctl, 90, gi);
+                // O is rescaled only at rest: PV(gi - 1) has to be finished as well (need implies i > 0, so gi > 0)
+                if (ok && any_need) ok = mbar_wait_warp(bar_pv_done(buf ^ 1), ((gi - 1) >> 1) & 1, ctl, 92, gi);
+                if (!ok) break;
                 {   // all 32 lanes take part in the store (a lane whose tile has run out of blocks writes don't-cares)
                     uint32_t pr[32];
 #pragma unroll
@@ -755,10 +687,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                         pr[4 * cch + 2] = pk[cch].z;
                         pr[4 * cch + 3] = pk[cch].w;
                     }
-                    tc_st32(tm_s + 64u + 32u * (round & 1), pr);
+                    tc_st32(tm_p + 32u * buf, pr);
                 }
-                // O is rescaled once PV(i-1) has finished with it (rare: only when a row maximum jumps)
-                if (any_need) {
+                if (any_need) {  // rare: only when a row maximum jumps
                     tc_fence_after();
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
@@ -771,36 +702,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                 }
                 tc_wait_st();
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 50000 + i);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_p_full(p, round & 1));
-                if ((warp & 3) == 0 && lane == 0) LCBSA_TS(2 + p, 60000 + i);
+                if (lane == 0) mbar_arrive(bar_p_full(buf));
+                if (warp == 0 && lane == 0) LCBSA_TS(2, 50000 + i);
             }
             if (!ok) break;
 
-            // ---- epilogue of this work item
-            while (n_pv0 < ((n_s + 1) >> 1) && ok) {  // every PV of this work item has finished
-                ok = mbar_wait_warp(bar_pv_done(p, 0), n_pv0 & 1, ctl, 100 + p, n_pv0);
-                ++n_pv0;
-            }
-            while (n_pv1 < (n_s >> 1) && ok) {
-                ok = mbar_wait_warp(bar_pv_done(p, 1), n_pv1 & 1, ctl, 102 + p, n_pv1);
-                ++n_pv1;
-            }
+            // ---- epilogue of this work item: every PV has finished once the last one has
+            const unsigned last = gi - 1;
+            ok = mbar_wait_warp(bar_pv_done(last & 1), (last >> 1) & 1, ctl, 100, last);
             if (!ok) break;
             tc_fence_after();
+            // O is staged (input dtype, 128B-swizzled halves) in the V slot that this last PV has just released
+            unsigned char* o_tile = smem + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
+            const bool any_pv = max(my_cnt, other_cnt) > 0;  // warp-uniform: O holds something
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
 #pragma unroll
             for (int cch = 0; cch < 4; ++cch) {
                 uint32_t orr[32];
-                if (n_iter > 0) {
+                if (any_pv) {
                     tc_ld32(tm_o + 32 * cch, orr);
                     tc_wait_ld();
                 }
 #ifdef LCBSA_TC_DEBUG
-                if (P.dbg && w == 0 && n_iter > 0)
-                    for (int j = 0; j < 32; ++j) P.dbg[4 * 64 * 64 + (t * 64 + row) * 128 + cch * 32 + j] = __uint_as_float(orr[j]);
+                if (P.dbg && w == 0 && any_pv)
+                    for (int j = 0; j < 32; ++j) P.dbg[2 * 64 * 64 + (hf * 64 + row) * 128 + cch * 32 + j] = __uint_as_float(orr[j]);
 #endif
                 if (tile_valid) {
                     unsigned char* half = o_tile + (cch >> 1) * kHalfBytes;
@@ -821,6 +748,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 }
             }
             tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_o_free);  // O may be overwritten by the next item's first PV
             if (P.lse != nullptr && tile_valid) {
                 int lt, lh, lw, bt, bhh, bw;
                 slot_coords(P.gq, row, lt, lh, lw);
@@ -834,32 +763,43 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_o_staged(p));
-            if (warp == 4 * p) {  // first warp of the warpgroup: wait for all 128 rows, then one lane stores
-                ok = mbar_wait_warp(bar_o_staged(p), wk & 1, ctl, 110 + p, wk);
-                if (ok && lane == 0) {
-                    for (int hh2 = 0; hh2 < 2; ++hh2) {
-                        const int tt2 = 2 * p + hh2, qq = g * kTilesPerWork + tt2;
-                        if (qq >= P.nq) continue;
-                        const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
-                        const uint32_t src = sbase + kOffQ + tt2 * kTileBytes;
-                        tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
-                        tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
-                    }
-                    tma_store_commit();
-                    tma_store_wait_read();
-                    mbar_arrive(bar_q_empty(p));
-                }
-                __syncwarp();
-            }
+            if (lane == 0) mbar_arrive(bar_o_staged);  // the store warp takes it from here
         }
-        if ((tid & 127) == 0) tma_store_wait_all();
+    } else {
+        // ================================================================== output store warp
+        // Waits for the 128 staged rows of a work item, sends them off by TMA and hands the V slot they were
+        // staged in back to the producer, so that the warpgroup does not wait for the store.
+        unsigned gi = 0, wk = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
+            const int bh = (int)(w / groups), g = (int)(w % groups);
+            const int b = bh / P.heads, h = bh % P.heads;
+            const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            gi += max(1, max(ca, cb));
+            const unsigned last = gi - 1;
+            ok = mbar_wait_warp(bar_o_staged, wk & 1, ctl, 110, wk);
+            if (ok && lane == 0) {
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int qq = g * kTilesPerWork + hf;
+                    if (qq >= P.nq) continue;
+                    const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
+                    const uint32_t src = sbase + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
+                    tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
+                    tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
+                }
+                tma_store_commit();
+                tma_store_wait_read();
+                mbar_arrive(bar_v_empty(last % kVSlots));
+            }
+            __syncwarp();
+        }
+        if (lane == 0) tma_store_wait_all();
     }
 
     // ---- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 5) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
