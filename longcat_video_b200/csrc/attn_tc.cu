@@ -10,18 +10,23 @@
 // One persistent CTA per SM.  A work item is a pair of consecutive query blocks of one head.  Each
 // query block is a 64-row tile, i.e. an M=64 tcgen05 MMA whose accumulator occupies 16 lanes of every
 // 32-lane TMEM quadrant; the two tiles of the pair sit in the lower and the upper 16 lanes of the same
-// columns, so that the softmax warpgroup (128 threads, one TMEM lane each) serves both with every lane busy.
+// columns, so that a softmax warpgroup (128 threads, one TMEM lane each) serves both with every lane busy.
 //
-//   warps 0-3 : softmax warpgroup           warp 4 : TMA producer (Q tiles, K ring, V ring)
-//   warp 5    : S = Q K^T issuer            warp 6 : O += P V issuer           warp 7 : output TMA stores
+// The selected K/V blocks of the pair are dealt alternately to two softmax warpgroups (even blocks to
+// warpgroup 0, odd blocks to warpgroup 1).  Each keeps its own running maximum, row sum and O accumulator,
+// and the two partial results are merged once at the end of the work item (as in split-KV decoding), so
+// the warpgroups never synchronise with each other inside the loop and one computes while the other waits.
 //
-// Per selected K/V block i and tile:  S(i) = Q K^T  (M64 N64 K128, fp32 in TMEM, double-buffered)  ->  the
-// warpgroup reads S(i) with tcgen05.ld (which frees the buffer for S(i+2)), exp2 online softmax in
-// registers, P(i) in the input dtype back into TMEM with tcgen05.st (double-buffered)  ->
-// O += P(i) V(i)  (M64 N128 K64, A operand from TMEM, fp32 accumulator in TMEM).
-// S runs two blocks ahead of the softmax and the softmax never waits for the PV of the block before, so
-// the three stages overlap; K and V have a ring of three slots each (a slot = the tiles of both query
-// blocks), filled in the order K0 K1 K2 V0 K3 V1 ..., which hides about two iterations of load latency.
+//   warps 0-3, 4-7 : softmax warpgroups 0 and 1     warp 8  : TMA producer (Q tiles, K ring, V ring)
+//   warp 9         : S = Q K^T issuer               warp 10 : O += P V issuer      warp 11 : output TMA stores
+//
+// Per block i (warpgroup g = i & 1, its round r = i >> 1):  S = Q K^T  (M64 N64 K128, fp32 in TMEM, buffer
+// r & 1 of the warpgroup)  ->  the warpgroup reads S with tcgen05.ld, exp2 online softmax in registers, P in the
+// input dtype written over the first half of the same S buffer with tcgen05.st  ->  O_g += P V  (M64 N128
+// K64, A operand from TMEM).  The S of round r + 2 is issued into the buffer once that PV has finished, which
+// leaves a whole round of the warpgroup for it; a round costs the warpgroup one barrier wait and one arrival.
+// K and V have a ring of three slots each (a slot = the tiles of both query blocks), filled in the order in
+// which they are used: K0 K1 K2 K3 V0 K4 V1 ...
 //
 // The MMAs are issued by whole converged warps with one elected lane (about 23 cycles per MMA for the
 // warp; a single lane inside a divergent branch needs 50 and more).
@@ -30,12 +35,14 @@
 // (the accumulated values stay finite and the result is unchanged after the final division), so O is
 // rarely rescaled in TMEM.
 //
-// TMEM columns: S[buf] at 64*buf, P[buf] at 128 + 32*buf (two 16-bit probabilities per column),
-// O at 192 (128 columns); the second tile of the pair 16 lanes up in each.
+// TMEM columns, per warpgroup g at 256*g: S/P[buf] at 64*buf (the probabilities, two 16-bit values per
+// column, occupy the first 32 columns of the buffer), O at 128 (128 columns); the second tile of the
+// pair 16 lanes up in each.
 //
-// The finished O tile is staged in the V slot that the last PV of the work item has just released and
-// leaves by TMA store; the Q tiles are released as soon as the last S of the item has been computed, so
-// the next item's Q, K and S are in flight while this one finishes.
+// At the end of a work item both warpgroups exchange (maximum, row sum) through shared memory, each merges
+// and normalises one 64-column half of O and stages it in the V slot that the last PV has released; it
+// leaves by TMA store.  The Q tiles are released as soon as the last S of the item has been computed, so the
+// next item's Q, K and S are in flight while this one finishes.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the CTA records where, raises an abort
 // flag that all roles poll, drains its outstanding bulk copies, frees its TMEM and returns.
@@ -54,22 +61,27 @@ constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128
 constexpr int kTilesPerWork = 2;            // the two query blocks of a pair
 constexpr int kSlotBytes = kTilesPerWork * kTileBytes;  // a ring slot holds the K (or V) tiles of both query blocks
 constexpr int kKSlots = 3, kVSlots = 3;
-constexpr int kThreads = 256;
+constexpr int kKLead = 4;                   // K blocks requested ahead of V: S runs two rounds of each warpgroup ahead
+constexpr int kThreads = 384;
+// setmaxnreg per warpgroup: (208 + 208 + 88) * 128 threads <= the 64 K registers of the SM
+constexpr int kRegsSoftmax = 208, kRegsOther = 88;
 constexpr unsigned kSpinsBeforeClock = 1u << 12;     // failed try_waits before the clock is consulted
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s
 
-// TMEM columns
-constexpr uint32_t kTmS = 0, kTmP = 128, kTmO = 192;
+// TMEM columns of warpgroup g: base 256 * g
+constexpr uint32_t kTmWg = 256, kTmS = 0, kTmO = 128;
 
-// shared memory map (offsets from a 1024-byte aligned base)
+// shared memory map (offsets from the 1024-byte aligned base of dynamic shared memory)
 constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kTilesPerWork * kTileBytes;
 constexpr int kOffV = kOffK + kKSlots * kSlotBytes;
 constexpr int kOffBar = kOffV + kVSlots * kSlotBytes;
-// barriers: k_full[3] k_empty[3] v_full[3] v_empty[3] q_full q_empty s_full[2] s_free[2] p_full[2] pv_done[2] o_free o_staged
-constexpr int kNumBars = 2 * kKSlots + 2 * kVSlots + 2 + 8 + 2;
-constexpr int kOffMisc = kOffBar + kNumBars * 8;
-constexpr int kSmemBytes = kOffMisc + 64 + 1024;  // + slack for the 1024-byte alignment
+// barriers: k_full[3] k_empty[3] v_full[3] v_empty[3] q_full q_empty s_full[2][2] p_full[2][2] pv_done[2][2]
+//           ml_ready o_free o_staged
+constexpr int kNumBars = 2 * kKSlots + 2 * kVSlots + 2 + 12 + 3;
+constexpr int kOffMisc = kOffBar + kNumBars * 8;      // abort flag, TMEM base
+constexpr int kOffMl = kOffMisc + 64;                 // [2 warpgroups][128 lanes] (maximum, row sum)
+constexpr int kSmemBytes = kOffMl + 2 * 128 * 8;
 
 struct TcParams {
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
@@ -87,8 +99,8 @@ struct TcParams {
     float scale2;   // sm_scale * log2(e)
     int is_bf16;
 #ifdef LCBSA_TC_DEBUG
-    float* dbg;     // [2 tiles][64 rows][64] raw S of the first work item's first iteration, then [2][64][128] raw O
-    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: PV issuer, S issuer, softmax warp 0, producer
+    float* dbg;     // [2 blocks][2 tiles][64 rows][64] raw S of the first work item's first two blocks
+    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: PV issuer, S issuer, softmax warps 0 and 4
 #endif
 };
 
@@ -114,6 +126,14 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// called by all lanes of a converged warp: one elected lane arrives (no divergent branch around it)
+__device__ __forceinline__ void mbar_arrive_elect(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+        ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -320,8 +340,7 @@ __device__ __forceinline__ int clamp_cnt(const TcParams& P, int bh, int qt) {
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_constant__ TcParams P) {
-    extern __shared__ unsigned char smem_dyn[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + kOffBar;
     auto bar_k_full = [&](int s) { return bar0 + 8u * s; };
@@ -330,13 +349,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     auto bar_v_empty = [&](int s) { return bar0 + 8u * (2 * kKSlots + kVSlots + s); };
     constexpr int kB0 = 2 * kKSlots + 2 * kVSlots;
     const uint32_t bar_q_full = bar0 + 8u * kB0, bar_q_empty = bar0 + 8u * (kB0 + 1);
-    auto bar_s_full = [&](int buf) { return bar0 + 8u * (kB0 + 2 + buf); };
-    auto bar_s_free = [&](int buf) { return bar0 + 8u * (kB0 + 4 + buf); };
-    auto bar_p_full = [&](int buf) { return bar0 + 8u * (kB0 + 6 + buf); };
-    auto bar_pv_done = [&](int buf) { return bar0 + 8u * (kB0 + 8 + buf); };
-    const uint32_t bar_o_free = bar0 + 8u * (kB0 + 10), bar_o_staged = bar0 + 8u * (kB0 + 11);
+    auto bar_s_full = [&](int wg, int buf) { return bar0 + 8u * (kB0 + 2 + 2 * wg + buf); };
+    auto bar_p_full = [&](int wg, int buf) { return bar0 + 8u * (kB0 + 6 + 2 * wg + buf); };
+    auto bar_pv_done = [&](int wg, int buf) { return bar0 + 8u * (kB0 + 10 + 2 * wg + buf); };
+    const uint32_t bar_ml_ready = bar0 + 8u * (kB0 + 14), bar_o_free = bar0 + 8u * (kB0 + 15), bar_o_staged = bar0 + 8u * (kB0 + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
+    float2* ml = reinterpret_cast<float2*>(smem + kOffMl);  // [2][128]
     const Ctl ctl{abort_flag, P.status};
 
     const int tid = threadIdx.x, lane = tid & 31;
@@ -357,17 +376,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
         }
         mbar_init(bar_q_full, 1);
         mbar_init(bar_q_empty, 1);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), 4);  // one elected arrival per softmax warp
-            mbar_init(bar_p_full(b), 4);
-            mbar_init(bar_pv_done(b), 1);
-        }
-        mbar_init(bar_o_free, 4);
-        mbar_init(bar_o_staged, 4);
+        for (int g = 0; g < 2; ++g)
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(bar_s_full(g, b), 1);
+                mbar_init(bar_p_full(g, b), 4);  // one elected arrival per softmax warp
+                mbar_init(bar_pv_done(g, b), 1);
+            }
+        mbar_init(bar_ml_ready, 8);
+        mbar_init(bar_o_free, 8);
+        mbar_init(bar_o_staged, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The tiles are 128B-swizzled, which ties their layout to address bits 7-9: without a 1024-byte aligned
+        // base nothing below is valid.  The declaration asks for it; refuse to run if it was not honoured.
+        if (sbase & 1023u) {
+            *abort_flag = 1;
+            if (atomicCAS(P.status, 0u, 1u) == 0u) {
+                P.status[1] = blockIdx.x;
+                P.status[2] = sbase;
+                P.status[3] = 0;
+            }
+        }
     }
-    if (warp == 5) {  // TMEM: all 512 columns, allocated and freed by the S issuer
+    if (warp == 9) {  // TMEM: all 512 columns, allocated and freed by the S issuer
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
@@ -375,14 +405,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    const bool start_ok = *abort_flag == 0;
 
     const int groups = (P.nq + kTilesPerWork - 1) / kTilesPerWork;
-    const long long total_work = (long long)P.bh_total * groups;
+    const long long total_work = start_ok ? (long long)P.bh_total * groups : 0;
     constexpr bool bf16 = kBf16;
 
-    // All roles walk the same list of work items and count the same global iteration number `gi`:
-    // iteration gi uses K slot gi % 3, V slot gi % 3, S and P buffer gi & 1.
-    if (warp == 4) {
+    // All roles walk the same list of work items and blocks.  Block number gb (counted over the whole kernel)
+    // uses K slot gb % 3 and V slot gb % 3; warpgroup g numbers its own rounds rr[g] over the whole kernel and
+    // round rr uses S/P buffer rr & 1.  Within an item block i belongs to warpgroup i & 1.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+      if (warp == 8) {
         // ================================================================== TMA producer
         unsigned gk = 0, gv = 0, wk = 0, nq_issued = 0;
         bool ok = true;
@@ -409,8 +443,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 }
             }
             // Block coordinates are fetched and decoded by the whole warp: lane L holds, for tile (L & 1) and
-            // iteration win + (L >> 1), the block's first token packed as t << 20 | h << 10 | w.  `prv` and `nxt`
-            // hold the windows of sixteen iterations before and after (V trails K by two iterations).
+            // block win + (L >> 1), the block's first token packed as t << 20 | h << 10 | w.  `prv` and `nxt`
+            // hold the windows of sixteen blocks before and after (V trails K by kKLead blocks).
             const int my_t = lane & 1, my_s = lane >> 1;
             const int my_c = my_t ? cb : ca;
             const int32_t* my_l = P.idx + ((long long)bh * P.nq + min(qa + my_t, P.nq - 1)) * P.cap;
@@ -425,7 +459,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             int nxt = fetch(16 + my_s);
             const int c3k = P.merge_k ? b * P.Tk : 0, c4k = P.merge_k ? h : b * P.heads + h;
             const int c3v = P.merge_v ? b * P.Tk : 0, c4v = P.merge_v ? h : b * P.heads + h;
-            for (int j = 0; j < n_iter + 2 && ok; ++j) {
+            for (int j = 0; j < n_iter + kKLead && ok; ++j) {
+                if (j >= kKLead) {  // V(j - kKLead)
+                    const int jj = j - kKLead;
+                    const int src = jj >= win ? cur : prv;
+                    const int o = jj >= win ? jj - win : jj - (win - 16);
+                    const int pa = __shfl_sync(0xffffffffu, src, (o << 1) | 0);
+                    const int pb = __shfl_sync(0xffffffffu, src, (o << 1) | 1);
+                    const bool act_a = jj < ca, act_b = jj < cb;
+                    const int slot = gv % kVSlots;
+                    ok = mbar_wait_warp(bar_v_empty(slot), ((gv / kVSlots) & 1) ^ 1, ctl, 22, gv);
+                    if (!ok) break;
+                    ++gv;
+                    if (lane == 0) {
+                        mbar_arrive_tx(bar_v_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            if (!(hf ? act_b : act_a)) continue;
+                            const int pk = hf ? pb : pa;
+                            const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3v;
+                            const uint32_t dst = sbase + kOffV + slot * kSlotBytes + hf * kTileBytes;
+                            tma_load_5d(dst, &P.tm_v, bar_v_full(slot), 0, cw, chh, ctt, c4v);
+                            tma_load_5d(dst + kHalfBytes, &P.tm_v, bar_v_full(slot), 64, cw, chh, ctt, c4v);
+                        }
+                    }
+                }
                 if (j < n_iter) {  // K(j)
                     while (j >= win + 16) {
                         win += 16;
@@ -441,7 +499,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     if (!ok) break;
                     ++gk;
                     if (lane == 0) {
-                        LCBSA_TS(3, 10000 + j);
                         mbar_arrive_tx(bar_k_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
 #pragma unroll
                         for (int hf = 0; hf < 2; ++hf) {
@@ -451,31 +508,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                             const uint32_t dst = sbase + kOffK + slot * kSlotBytes + hf * kTileBytes;
                             tma_load_5d(dst, &P.tm_k, bar_k_full(slot), 0, cw, chh, ctt, c4k);
                             tma_load_5d(dst + kHalfBytes, &P.tm_k, bar_k_full(slot), 64, cw, chh, ctt, c4k);
-                        }
-                    }
-                }
-                if (j >= 2) {  // V(j - 2)
-                    const int jj = j - 2;
-                    const int src = jj >= win ? cur : prv;
-                    const int o = jj >= win ? jj - win : jj - (win - 16);
-                    const int pa = __shfl_sync(0xffffffffu, src, (o << 1) | 0);
-                    const int pb = __shfl_sync(0xffffffffu, src, (o << 1) | 1);
-                    const bool act_a = jj < ca, act_b = jj < cb;
-                    const int slot = gv % kVSlots;
-                    ok = mbar_wait_warp(bar_v_empty(slot), ((gv / kVSlots) & 1) ^ 1, ctl, 22, gv);
-                    if (!ok) break;
-                    ++gv;
-                    if (lane == 0) {
-                        LCBSA_TS(3, 20000 + jj);
-                        mbar_arrive_tx(bar_v_full(slot), ((int)act_a + (int)act_b) * kTileBytes);
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            if (!(hf ? act_b : act_a)) continue;
-                            const int pk = hf ? pb : pa;
-                            const int cw = pk & 1023, chh = (pk >> 10) & 1023, ctt = (pk >> 20) + c3v;
-                            const uint32_t dst = sbase + kOffV + slot * kSlotBytes + hf * kTileBytes;
-                            tma_load_5d(dst, &P.tm_v, bar_v_full(slot), 0, cw, chh, ctt, c4v);
-                            tma_load_5d(dst + kHalfBytes, &P.tm_v, bar_v_full(slot), 64, cw, chh, ctt, c4v);
                         }
                     }
                 }
@@ -494,23 +526,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 while (!mbar_try(bar_q_full, (nq_issued - 1) & 1) && clock64() - t0 < 40000000ll) {
                 }
         }
-    } else if (warp == 5) {
+      } else if (warp == 9) {
         // ================================================================== S = Q K^T issuer
         const uint32_t idesc_s = instr_desc(bf16, 64, 64, 0);
-        unsigned gi = 0, wk = 0;
+        unsigned gb = 0, wk = 0, rr0 = 0, rr1 = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
             const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
             const int n_iter = max(1, max(ca, cb));
             ok = mbar_wait_warp(bar_q_full, wk & 1, ctl, 30, wk);
-            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
-                const int slot = gi % kKSlots, buf = gi & 1;
+            for (int i = 0; i < n_iter && ok; ++i, ++gb) {
+                const int wg = i & 1;
+                const unsigned rr = wg ? rr1 : rr0;
+                const int slot = gb % kKSlots, buf = rr & 1;
                 if (lane == 0) LCBSA_TS(1, 10000 + i);
-                ok = mbar_wait_warp(bar_k_full(slot), (gi / kKSlots) & 1, ctl, 40, gi);
+                ok = mbar_wait_warp(bar_k_full(slot), (gb / kKSlots) & 1, ctl, 40, gb);
                 if (lane == 0) LCBSA_TS(1, 20000 + i);
-                // the warpgroup has pulled S(gi - 2) out of this buffer
-                if (ok) ok = mbar_wait_warp(bar_s_free(buf), ((gi >> 1) & 1) ^ 1, ctl, 34, gi);
+                // the buffer held P of the warpgroup's round rr - 2: that PV has to be finished
+                if (ok) ok = mbar_wait_warp(bar_pv_done(wg, buf), ((rr >> 1) & 1) ^ 1, ctl, 34 + wg, rr);
                 if (!ok) break;
                 if (lane == 0) LCBSA_TS(1, 30000 + i);
                 tc_fence_after();
@@ -519,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     if (!(i < (hf ? cb : ca))) continue;  // warp-uniform
                     const uint64_t qd = smem_desc(sbase + kOffQ + hf * kTileBytes, 16, 1024);
                     const uint64_t kd = smem_desc(sbase + kOffK + slot * kSlotBytes + hf * kTileBytes, 16, 1024);
-                    const uint32_t d = tmem + kTmS + 64u * buf + ((16u * hf) << 16);
+                    const uint32_t d = tmem + kTmWg * wg + kTmS + 64u * buf + ((16u * hf) << 16);
 #pragma unroll
                     for (int j = 0; j < kD / 16; ++j) {
                         // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
@@ -528,58 +562,96 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                 }
                 tc_commit(bar_k_empty(slot));  // K is free once these MMAs have read it
-                tc_commit(bar_s_full(buf));
+                tc_commit(bar_s_full(wg, buf));
                 if (i == n_iter - 1) tc_commit(bar_q_empty);  // and so is Q after the last S of the item
                 if (lane == 0) LCBSA_TS(1, 40000 + i);
+                if (wg) ++rr1; else ++rr0;
             }
         }
-    } else if (warp == 6) {
+      } else if (warp == 10) {
         // ================================================================== O += P V issuer
         const uint32_t idesc_pv = instr_desc(bf16, 64, 128, 1);
-        unsigned gi = 0, wk = 0;
+        unsigned gb = 0, wk = 0, rr0 = 0, rr1 = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), g = (int)(w % groups);
             const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
             const int n_iter = max(1, max(ca, cb));
-            // the epilogue of the previous item has read O
+            // the epilogue of the previous item has read both O accumulators
             ok = mbar_wait_warp(bar_o_free, (wk & 1) ^ 1, ctl, 36, wk);
-            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
-                const int slot = gi % kVSlots, buf = gi & 1;
+            for (int i = 0; i < n_iter && ok; ++i, ++gb) {
+                const int wg = i & 1;
+                const unsigned rr = wg ? rr1 : rr0;
+                const int slot = gb % kVSlots, buf = rr & 1;
                 if (lane == 0) LCBSA_TS(0, 10000 + i);
-                ok = mbar_wait_warp(bar_v_full(slot), (gi / kVSlots) & 1, ctl, 60, gi);
+                ok = mbar_wait_warp(bar_v_full(slot), (gb / kVSlots) & 1, ctl, 60, gb);
                 if (lane == 0) LCBSA_TS(0, 20000 + i);
-                if (ok) ok = mbar_wait_warp(bar_p_full(buf), (gi >> 1) & 1, ctl, 50, gi);
+                if (ok) ok = mbar_wait_warp(bar_p_full(wg, buf), (rr >> 1) & 1, ctl, 50 + wg, rr);
                 if (!ok) break;
                 if (lane == 0) LCBSA_TS(0, 30000 + i);
                 tc_fence_after();
-                // A: P in TMEM (buffer gi & 1), 8 columns per 16-key step; the second tile of the pair sits 16
-                // lanes up, like its accumulators.
+                // A: P in TMEM (first 32 columns of the S buffer), 8 columns per 16-key step; the second tile of
+                // the pair sits 16 lanes up, like its accumulators.
                 // B: V tile, MN-major: 64-column halves 8 KiB apart (LBO), 8-key groups 1 KiB apart (SBO).
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     if (!(i < (hf ? cb : ca))) continue;  // warp-uniform
-                    const uint32_t pa = tmem + kTmP + 32u * buf + ((16u * hf) << 16);
+                    const uint32_t pa = tmem + kTmWg * wg + kTmS + 64u * buf + ((16u * hf) << 16);
                     const uint64_t vd = smem_desc(sbase + kOffV + slot * kSlotBytes + hf * kTileBytes, kHalfBytes, 1024);
-                    const uint32_t d = tmem + kTmO + ((16u * hf) << 16);
+                    const uint32_t d = tmem + kTmWg * wg + kTmO + ((16u * hf) << 16);
 #pragma unroll
                     for (int j = 0; j < kBlk / 16; ++j)
-                        tc_mma_ts(d, pa + 8u * j, vd + (uint64_t)((j * 2048) >> 4), idesc_pv, (i > 0 || j > 0) ? 1u : 0u);
+                        tc_mma_ts(d, pa + 8u * j, vd + (uint64_t)((j * 2048) >> 4), idesc_pv, (i > 1 || j > 0) ? 1u : 0u);
                 }
                 // the V slot of the item's last block goes to the epilogue, which stages O in it and frees it
                 if (i < n_iter - 1) tc_commit(bar_v_empty(slot));
-                tc_commit(bar_pv_done(buf));
+                tc_commit(bar_pv_done(wg, buf));
                 if (lane == 0) LCBSA_TS(0, 40000 + i);
+                if (wg) ++rr1; else ++rr0;
             }
         }
-    } else if (warp < 4) {
-        // ================================================================== softmax warpgroup
-        const int wq = warp;              // TMEM quadrant of this warp
+      } else {
+        // ================================================================== output store warp
+        // Waits for the staged rows of a work item, sends them off by TMA and hands the V slot they were staged
+        // in back to the producer, so that the warpgroups do not wait for the store.
+        unsigned gb = 0, wk = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
+            const int bh = (int)(w / groups), g = (int)(w % groups);
+            const int b = bh / P.heads, h = bh % P.heads;
+            const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
+            gb += max(1, max(ca, cb));
+            const unsigned last = gb - 1;
+            ok = mbar_wait_warp(bar_o_staged, wk & 1, ctl, 110, wk);
+            if (ok && lane == 0) {
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int qq = g * kTilesPerWork + hf;
+                    if (qq >= P.nq) continue;
+                    const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
+                    const uint32_t src = sbase + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
+                    tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
+                    tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
+                }
+                tma_store_commit();
+                tma_store_wait_read();
+                mbar_arrive(bar_v_empty(last % kVSlots));
+            }
+            __syncwarp();
+        }
+        if (lane == 0) tma_store_wait_all();
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+        // ================================================================== softmax warpgroups
+        const int wg = warp >> 2;         // warpgroup: takes blocks wg, wg + 2, ... of every work item
+        const int wq = warp & 3;          // TMEM quadrant of this warp
         const int hf = lane >> 4;         // tile of the pair this lane serves
         const int row = wq * 16 + (lane & 15);  // row of that tile
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
-        const uint32_t tm_s = tmem + kTmS + t_lane, tm_p = tmem + kTmP + t_lane, tm_o = tmem + kTmO + t_lane;
-        unsigned gi = 0, wk = 0;
+        const uint32_t tm_s = tmem + kTmWg * wg + kTmS + t_lane;
+        const uint32_t tm_o_mine = tmem + kTmWg * wg + kTmO + t_lane, tm_o_other = tmem + kTmWg * (wg ^ 1) + kTmO + t_lane;
+        const int ml_idx = wq * 32 + lane;
+        unsigned rr = 0, wk = 0, gb = 0;
         bool ok = true;
 
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
@@ -592,26 +664,23 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             const int32_t* my_list = P.idx + ((long long)bh * P.nq + (tile_valid ? qt : 0)) * P.cap;
 
             float m_ref = -INFINITY, l_sum = 0.f;
+            bool first = true;  // no block of this item seen yet by this warpgroup
 
-            for (int i = 0; i < n_iter && ok; ++i, ++gi) {
+            for (int i = wg; i < n_iter && ok; i += 2, ++rr) {
                 const bool active = i < my_cnt;
-                const int buf = gi & 1;
-                const unsigned bph = (gi >> 1) & 1;
-                if (warp == 0 && lane == 0) LCBSA_TS(2, 10000 + i);
-                ok = mbar_wait_warp(bar_s_full(buf), bph, ctl, 80, gi);
+                const int buf = rr & 1;
+                const unsigned bph = (rr >> 1) & 1;
+                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 10000 + i);
+                ok = mbar_wait_warp(bar_s_full(wg, buf), bph, ctl, 80 + wg, rr);
                 if (!ok) break;
-                if (warp == 0 && lane == 0) LCBSA_TS(2, 20000 + i);
                 tc_fence_after();
                 uint32_t sr[64];
                 tc_ld64(tm_s + 64u * buf, sr);
                 tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_s_free(buf));  // the buffer may take S(gi + 2)
-                if (warp == 0 && lane == 0) LCBSA_TS(2, 30000 + i);
+                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 20000 + i);
 #ifdef LCBSA_TC_DEBUG
-                if (P.dbg && w == 0 && i == 0)
-                    for (int j = 0; j < 64; ++j) P.dbg[(hf * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
+                if (P.dbg && w == 0 && i < 2)
+                    for (int j = 0; j < 64; ++j) P.dbg[((i * 2 + hf) * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
 #endif
                 float alpha = 1.f;
                 bool need = false;
@@ -633,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                     // One pass: the probabilities are computed against the current reference maximum while
                     // the row maximum is tracked on the side; only if the maximum has moved by more than 2^8
-                    // (or this is the first block) is the pass repeated with the new reference.
+                    // (or this is the warpgroup's first block) is the pass repeated with the new reference.
                     auto probs = [&](float mref, float& rsum) {
                         float r4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -652,7 +721,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                         rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
                     };
                     float rs = 0.f;
-                    if (i > 0) probs(m_ref, rs);
+                    if (!first) probs(m_ref, rs);
                     float mx8[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) mx8[j] = __uint_as_float(sr[j]);
@@ -661,8 +730,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                                            fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                     const float m_new = fmaxf(m_ref, mx * P.scale2);
-                    if (i == 0 || m_new - m_ref > 8.f) {
-                        if (i > 0) {
+                    if (first || m_new - m_ref > 8.f) {
+                        if (!first) {
                             need = true;
                             alpha = ex2(m_ref - m_new);
                         }
@@ -671,14 +740,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     }
                     l_sum = l_sum * alpha + rs;  // alpha is 1 unless this row's reference maximum moved
                 }
-                if (warp == 0 && lane == 0) LCBSA_TS(2, 40000 + i);
+                first = false;
+                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 30000 + i);
                 const bool any_need = __any_sync(0xffffffffu, need);
-                // P buffer gi & 1 was last read by PV(gi - 2); pv_done[buf] completes its phase (gi - 2) >> 1 then.
-                ok = mbar_wait_warp(bar_pv_done(buf), bph ^ 1, ctl, 90, gi);
-                // O is rescaled only at rest: PV(gi - 1) has to be finished as well (need implies i > 0, so gi > 0)
-                if (ok && any_need) ok = mbar_wait_warp(bar_pv_done(buf ^ 1), ((gi - 1) >> 1) & 1, ctl, 92, gi);
-                if (!ok) break;
-                {   // all 32 lanes take part in the store (a lane whose tile has run out of blocks writes don't-cares)
+                // O is rescaled only at rest: the warpgroup's PV of the round before has to be finished
+                // (need implies that this is not the warpgroup's first round of the item, so rr > 0)
+                if (any_need) {
+                    ok = mbar_wait_warp(bar_pv_done(wg, buf ^ 1), ((rr - 1) >> 1) & 1, ctl, 92 + wg, rr);
+                    if (!ok) break;
+                }
+                {   // P overwrites the first half of the S buffer just read; all 32 lanes take part in the store
+                    // (a lane whose tile has run out of blocks writes don't-cares)
                     uint32_t pr[32];
 #pragma unroll
                     for (int cch = 0; cch < 8; ++cch) {
@@ -687,70 +759,91 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                         pr[4 * cch + 2] = pk[cch].z;
                         pr[4 * cch + 3] = pk[cch].w;
                     }
-                    tc_st32(tm_p + 32u * buf, pr);
+                    tc_st32(tm_s + 64u * buf, pr);
                 }
                 if (any_need) {  // rare: only when a row maximum jumps
                     tc_fence_after();
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
                         uint32_t orr[32];
-                        tc_ld32(tm_o + 32 * cch, orr);
+                        tc_ld32(tm_o_mine + 32 * cch, orr);
                         tc_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
-                        tc_st32(tm_o + 32 * cch, orr);
+                        tc_st32(tm_o_mine + 32 * cch, orr);
                     }
                 }
                 tc_wait_st();
                 tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_p_full(buf));
-                if (warp == 0 && lane == 0) LCBSA_TS(2, 50000 + i);
+                mbar_arrive_elect(bar_p_full(wg, buf));
+                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 40000 + i);
             }
             if (!ok) break;
+            gb += n_iter;
 
-            // ---- epilogue of this work item: every PV has finished once the last one has
-            const unsigned last = gi - 1;
-            ok = mbar_wait_warp(bar_pv_done(last & 1), (last >> 1) & 1, ctl, 100, last);
+            // ---- epilogue of this work item.  The warpgroup's PVs are finished once its last one is; it then
+            // publishes (maximum, row sum) of its rows and waits for the other warpgroup to do the same.
+            const int my_rounds = (n_iter - wg + 1) >> 1;  // blocks wg, wg + 2, ... below n_iter
+            if (my_rounds > 0) {
+                const unsigned lr = rr - 1;
+                ok = mbar_wait_warp(bar_pv_done(wg, lr & 1), (lr >> 1) & 1, ctl, 100 + wg, lr);
+                if (!ok) break;
+            }
+            // the other warpgroup has read this warpgroup's entry of the previous item before it arrived on o_free
+            if (wk > 0) {
+                ok = mbar_wait_warp(bar_o_free, (wk - 1) & 1, ctl, 102 + wg, wk);
+                if (!ok) break;
+            }
+            ml[wg * 128 + ml_idx] = make_float2(m_ref, l_sum);
+            __syncwarp();
+            mbar_arrive_elect(bar_ml_ready);
+            ok = mbar_wait_warp(bar_ml_ready, wk & 1, ctl, 104 + wg, wk);
             if (!ok) break;
             tc_fence_after();
-            // O is staged (input dtype, 128B-swizzled halves) in the V slot that this last PV has just released
-            unsigned char* o_tile = smem + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
-            const bool any_pv = max(my_cnt, other_cnt) > 0;  // warp-uniform: O holds something
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            const float2 oth = ml[(wg ^ 1) * 128 + ml_idx];
+            // merged scale of both partial sums: everything relative to the larger reference maximum
+            const float m_all = fmaxf(m_ref, oth.x);
+            const float w_mine = l_sum > 0.f ? ex2(m_ref - m_all) : 0.f;
+            const float w_oth = oth.y > 0.f ? ex2(oth.x - m_all) : 0.f;
+            const float l_all = l_sum * w_mine + oth.y * w_oth;
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            const float f_mine = w_mine * inv, f_oth = w_oth * inv;
+            // This warpgroup merges and stages columns 64*wg .. 64*wg+63 of O (input dtype, one 128B-swizzled
+            // half-tile row per thread) in the V slot that the item's last PV has just released.
+            const unsigned last = gb - 1;
+            unsigned char* o_half = smem + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes + wg * kHalfBytes;
 #pragma unroll
-            for (int cch = 0; cch < 4; ++cch) {
-                uint32_t orr[32];
-                if (any_pv) {
-                    tc_ld32(tm_o + 32 * cch, orr);
-                    tc_wait_ld();
-                }
-#ifdef LCBSA_TC_DEBUG
-                if (P.dbg && w == 0 && any_pv)
-                    for (int j = 0; j < 32; ++j) P.dbg[2 * 64 * 64 + (hf * 64 + row) * 128 + cch * 32 + j] = __uint_as_float(orr[j]);
-#endif
+            for (int cch = 0; cch < 2; ++cch) {
+                uint32_t oa[32], ob[32];
+                // a warpgroup that saw no block has weight 0; its accumulator holds garbage and is not used
+                const bool rd_mine = __any_sync(0xffffffffu, w_mine > 0.f), rd_oth = __any_sync(0xffffffffu, w_oth > 0.f);
+                if (rd_mine) tc_ld32(tm_o_mine + 64 * wg + 32 * cch, oa);
+                if (rd_oth) tc_ld32(tm_o_other + 64 * wg + 32 * cch, ob);
+                tc_wait_ld();
                 if (tile_valid) {
-                    unsigned char* half = o_tile + (cch >> 1) * kHalfBytes;
 #pragma unroll
                     for (int q8 = 0; q8 < 4; ++q8) {
-                        uint4 pk;
-                        if (my_cnt > 0) {
-                            pk.x = pack2(bf16, __uint_as_float(orr[q8 * 8 + 0]) * inv, __uint_as_float(orr[q8 * 8 + 1]) * inv);
-                            pk.y = pack2(bf16, __uint_as_float(orr[q8 * 8 + 2]) * inv, __uint_as_float(orr[q8 * 8 + 3]) * inv);
-                            pk.z = pack2(bf16, __uint_as_float(orr[q8 * 8 + 4]) * inv, __uint_as_float(orr[q8 * 8 + 5]) * inv);
-                            pk.w = pack2(bf16, __uint_as_float(orr[q8 * 8 + 6]) * inv, __uint_as_float(orr[q8 * 8 + 7]) * inv);
-                        } else {
-                            pk = make_uint4(0u, 0u, 0u, 0u);
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float a = w_mine > 0.f ? __uint_as_float(oa[q8 * 8 + j]) * f_mine : 0.f;
+                            const float bb = w_oth > 0.f ? __uint_as_float(ob[q8 * 8 + j]) * f_oth : 0.f;
+                            v[j] = a + bb;
                         }
-                        const int chunk = (cch & 1) * 4 + q8;
-                        *reinterpret_cast<uint4*>(half + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
+                        uint4 pk;
+                        pk.x = pack2(bf16, v[0], v[1]);
+                        pk.y = pack2(bf16, v[2], v[3]);
+                        pk.z = pack2(bf16, v[4], v[5]);
+                        pk.w = pack2(bf16, v[6], v[7]);
+                        const int chunk = cch * 4 + q8;
+                        *reinterpret_cast<uint4*>(o_half + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_o_free);  // O may be overwritten by the next item's first PV
-            if (P.lse != nullptr && tile_valid) {
+            mbar_arrive_elect(bar_o_free);  // both O accumulators may be overwritten by the next item's first PVs
+            if (wg == 0 && P.lse != nullptr && tile_valid) {
                 int lt, lh, lw, bt, bhh, bw;
                 slot_coords(P.gq, row, lt, lh, lw);
                 block_coords(P.gq, qt, bt, bhh, bw);
@@ -758,48 +851,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 if (tt < P.gq.T && hh < P.gq.H && ww < P.gq.W) {
                     const long long Sq = (long long)P.gq.T * P.gq.H * P.gq.W;
                     const long long tok = ((long long)tt * P.gq.H + hh) * P.gq.W + ww;
-                    P.lse[(long long)bh * Sq + tok] = l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+                    P.lse[(long long)bh * Sq + tok] = l_all > 0.f ? (m_all + log2f(l_all)) * 0.6931471805599453f : -INFINITY;
                 }
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_o_staged);  // the store warp takes it from here
+            mbar_arrive_elect(bar_o_staged);  // the store warp takes it from here
         }
-    } else {
-        // ================================================================== output store warp
-        // Waits for the 128 staged rows of a work item, sends them off by TMA and hands the V slot they were
-        // staged in back to the producer, so that the warpgroup does not wait for the store.
-        unsigned gi = 0, wk = 0;
-        bool ok = true;
-        for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
-            const int bh = (int)(w / groups), g = (int)(w % groups);
-            const int b = bh / P.heads, h = bh % P.heads;
-            const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
-            gi += max(1, max(ca, cb));
-            const unsigned last = gi - 1;
-            ok = mbar_wait_warp(bar_o_staged, wk & 1, ctl, 110, wk);
-            if (ok && lane == 0) {
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int qq = g * kTilesPerWork + hf;
-                    if (qq >= P.nq) continue;
-                    const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
-                    const uint32_t src = sbase + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
-                    tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
-                    tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
-                }
-                tma_store_commit();
-                tma_store_wait_read();
-                mbar_arrive(bar_v_empty(last % kVSlots));
-            }
-            __syncwarp();
-        }
-        if (lane == 0) tma_store_wait_all();
     }
 
     // ---- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
