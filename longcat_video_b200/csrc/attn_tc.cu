@@ -150,6 +150,19 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// non-blocking probe of a phase (used to look ahead while other work is being issued)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 struct Ctl {
     volatile int* abort;    // shared flag
     unsigned int* status;   // global status words
@@ -536,17 +549,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             const int ca = clamp_cnt(P, bh, g * kTilesPerWork), cb = clamp_cnt(P, bh, g * kTilesPerWork + 1);
             const int n_iter = max(1, max(ca, cb));
             ok = mbar_wait_warp(bar_q_full, wk & 1, ctl, 30, wk);
+            bool pre = false;
             for (int i = 0; i < n_iter && ok; ++i, ++gb) {
                 const int wg = i & 1;
                 const unsigned rr = wg ? rr1 : rr0;
                 const int slot = gb % kKSlots, buf = rr & 1;
                 if (lane == 0) LCBSA_TS(1, 10000 + i);
-                ok = mbar_wait_warp(bar_k_full(slot), (gb / kKSlots) & 1, ctl, 40, gb);
-                if (lane == 0) LCBSA_TS(1, 20000 + i);
-                // the buffer held P of the warpgroup's round rr - 2: that PV has to be finished
-                if (ok) ok = mbar_wait_warp(bar_pv_done(wg, buf), ((rr >> 1) & 1) ^ 1, ctl, 34 + wg, rr);
-                if (!ok) break;
+                if (!pre) {  // not already seen ready by the look-ahead of the block before
+                    ok = mbar_wait_warp(bar_k_full(slot), (gb / kKSlots) & 1, ctl, 40, gb);
+                    if (lane == 0) LCBSA_TS(1, 20000 + i);
+                    // the buffer held P of the warpgroup's round rr - 2: that PV has to be finished
+                    if (ok) ok = mbar_wait_warp(bar_pv_done(wg, buf), ((rr >> 1) & 1) ^ 1, ctl, 34 + wg, rr);
+                    if (!ok) break;
+                }
                 if (lane == 0) LCBSA_TS(1, 30000 + i);
+                // look ahead: probe the two barriers of the item's next block now, read the answer after the MMAs
+                bool nk = false, np = false;
+                if (i + 1 < n_iter) {
+                    const int wg2 = wg ^ 1;
+                    const unsigned rr2 = wg2 ? rr1 : rr0;  // that warpgroup's next round
+                    nk = mbar_test(bar_k_full((gb + 1) % kKSlots), ((gb + 1) / kKSlots) & 1);
+                    np = mbar_test(bar_pv_done(wg2, rr2 & 1), ((rr2 >> 1) & 1) ^ 1);
+                }
                 tc_fence_after();
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
@@ -566,6 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 if (i == n_iter - 1) tc_commit(bar_q_empty);  // and so is Q after the last S of the item
                 if (lane == 0) LCBSA_TS(1, 40000 + i);
                 if (wg) ++rr1; else ++rr0;
+                pre = __all_sync(0xffffffffu, nk && np);
             }
         }
       } else if (warp == 10) {
@@ -579,16 +604,26 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             const int n_iter = max(1, max(ca, cb));
             // the epilogue of the previous item has read both O accumulators
             ok = mbar_wait_warp(bar_o_free, (wk & 1) ^ 1, ctl, 36, wk);
+            bool pre = false;
             for (int i = 0; i < n_iter && ok; ++i, ++gb) {
                 const int wg = i & 1;
                 const unsigned rr = wg ? rr1 : rr0;
                 const int slot = gb % kVSlots, buf = rr & 1;
                 if (lane == 0) LCBSA_TS(0, 10000 + i);
-                ok = mbar_wait_warp(bar_v_full(slot), (gb / kVSlots) & 1, ctl, 60, gb);
-                if (lane == 0) LCBSA_TS(0, 20000 + i);
-                if (ok) ok = mbar_wait_warp(bar_p_full(wg, buf), (rr >> 1) & 1, ctl, 50 + wg, rr);
-                if (!ok) break;
+                if (!pre) {
+                    ok = mbar_wait_warp(bar_v_full(slot), (gb / kVSlots) & 1, ctl, 60, gb);
+                    if (lane == 0) LCBSA_TS(0, 20000 + i);
+                    if (ok) ok = mbar_wait_warp(bar_p_full(wg, buf), (rr >> 1) & 1, ctl, 50 + wg, rr);
+                    if (!ok) break;
+                }
                 if (lane == 0) LCBSA_TS(0, 30000 + i);
+                bool nv = false, np = false;  // look ahead to the item's next block
+                if (i + 1 < n_iter) {
+                    const int wg2 = wg ^ 1;
+                    const unsigned rr2 = wg2 ? rr1 : rr0;
+                    nv = mbar_test(bar_v_full((gb + 1) % kVSlots), ((gb + 1) / kVSlots) & 1);
+                    np = mbar_test(bar_p_full(wg2, rr2 & 1), (rr2 >> 1) & 1);
+                }
                 tc_fence_after();
                 // A: P in TMEM (first 32 columns of the S buffer), 8 columns per 16-key step; the second tile of
                 // the pair sits 16 lanes up, like its accumulators.
@@ -608,6 +643,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 tc_commit(bar_pv_done(wg, buf));
                 if (lane == 0) LCBSA_TS(0, 40000 + i);
                 if (wg) ++rr1; else ++rr0;
+                pre = __all_sync(0xffffffffu, nv && np);
             }
         }
       } else {
