@@ -133,6 +133,24 @@ int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const 
                               int nsel, int cap, int32_t* idx, int32_t* cnt, void* stream);
 
 /*
+ * Number of SMs that lcbsa_attn_fwd leaves idle (0..64, default 0; process-wide).  The attention kernel is
+ * persistent with one CTA per SM and all of an SM's shared memory, so nothing else can start beside it; a caller
+ * that overlaps it with communication kernels on another stream (the all-to-all of
+ * longcat_video/context_parallel/ulysses_wrapper.py:7-83) reserves a few SMs for them.  No counterpart in the
+ * reference.  Returns the previous value, or LCBSA_EINVAL.
+ */
+int lcbsa_set_attn_sm_reserve(int n_sms);
+
+/*
+ * Enqueue `count` device-to-device copies of `nbytes` each on `stream`: dst[i] <- src[i], one cudaMemcpyAsync per
+ * slab, so the copy engines move them; a destination may be another GPU's memory mapped into this process
+ * (symmetric memory, CUDA IPC).  The pointer arrays are host memory and are read before the call returns.
+ * This is how the Ulysses exchange (longcat_video/context_parallel/ulysses_wrapper.py:7-83, NCCL all_to_all there)
+ * moves its [S/N, D] slabs without taking an SM from the attention kernel.  No counterpart in the reference.
+ */
+int lcbsa_copy_slabs(void* const* dst, const void* const* src, size_t nbytes, int count, void* stream);
+
+/*
  * Synchronise the current device and report whether any kernel of this library flagged a
  * bounded wait that ran out since the last call (LCBSA_EDEVICE), clearing the flag.
  * Debug aid for tests; not part of the hot path.

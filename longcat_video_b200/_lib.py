@@ -58,6 +58,8 @@ SIGNATURES = {
     "lcbsa_static_scratch_bytes": (ctypes.c_size_t, []),
     "lcbsa_block_select_static": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_int,
                                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "lcbsa_set_attn_sm_reserve": (ctypes.c_int, [ctypes.c_int]),
+    "lcbsa_copy_slabs": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]),
     "lcbsa_check_device_status": (ctypes.c_int, []),
 }
 

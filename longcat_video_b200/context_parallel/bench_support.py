@@ -9,6 +9,7 @@ back.  The total work is that of one layer whatever N is ("strong" scaling).
 from __future__ import annotations
 
 import json
+import os
 import statistics
 
 import torch
@@ -24,7 +25,12 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
     from .ulysses_wrapper import ulysses_wrapper
 
     dev = torch.device("cuda", local_rank)
+    # The attention kernel fills every SM it is given; the exchange runs on the copy engines, but its barrier is a
+    # one-CTA kernel that must be able to start beside the attention: keep two SMs free.
+    reserve = int(os.environ.get("LCBSA_ATTN_SM_RESERVE", "2"))
     dist.init_process_group("nccl", device_id=dev)
+    if L.lib().lcbsa_set_attn_sm_reserve(reserve) < 0:
+        L.check(-1)
     cpu_.init_context_parallel(world, rank, world)
     if heads % world:
         raise SystemExit(f"{heads} heads do not split over {world} ranks")
@@ -127,9 +133,9 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
                 "config": {"workload": wl.name, "grid": list(wl.grid_k), "rank_major_grid": list(bsa_grid), "heads": heads,
                            "heads_per_gpu": heads // world, "head_dim": wl.head_dim, "block": list(wl.chunk),
                            "sparsity": wl.sparsity, "selected_blocks": nsel, "algorithmic_tflop": flops / 1e12,
-                           "ms_attention_kernels": ms_attn, "cp_split_hw": [sh, sw],
+                           "ms_attention_kernels": ms_attn, "cp_split_hw": [sh, sw], "attn_sm_reserve": reserve,
                            "l2": "inputs exceed the 126 MB L2; no flush between iterations",
-                           "parallelism": f"ulysses{world} (NCCL all-to-all in/out, pipelined by head group)"},
+                           "parallelism": f"ulysses{world} (all-to-all in/out by peer DMA copies over NVLink, pipelined by head group)"},
                 "roofline": {"bound": "tensor", "kernel": "attn_tc_kernel", "achieved": attn_tf, "peak": peak, "unit": "TFLOP/s",
                              "frac": attn_tf / peak, "peak_source": f"{peak_src} (burst cuBLAS bf16 x {world} GPUs)",
                              "ms_per_step_in_kernel": ms_attn, "traffic": None},

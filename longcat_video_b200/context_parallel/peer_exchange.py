@@ -1,0 +1,172 @@
+"""Ulysses exchange by peer DMA copies over NVLink instead of NCCL send/recv kernels.
+
+Every rank of the context-parallel group owns one symmetric buffer (``torch.distributed._symmetric_memory``:
+the same allocation on every GPU, mapped into every process) that holds its receive side of the exchange:
+``q, k, v`` as ``[H/N, S, D]`` each and the attention result as ``[H, S/N, D]``.  A rank *pushes*: it copies each
+``[S/N, D]`` slab it owes a peer straight into that peer's buffer with a device-to-device ``cudaMemcpyAsync``
+(``lcbsa_copy_slabs``), which the driver executes on the copy engines over NVLink, and then joins a barrier of the
+group on the same stream.  When a
+rank leaves the barrier, every slab pushed to it before the barrier has landed.
+
+Why not NCCL here: the attention kernel is persistent and takes every SM it is given, so NCCL's send/recv
+kernels cannot run beside it and the exchange does not overlap; the copy engines need no SM.  (Measured on two
+B200: 203 GB/s per direction for the exchange through NCCL against 465 GB/s for pushes of the same size
+including the barrier.)  The barrier is a one-CTA kernel; ``lcbsa_set_attn_sm_reserve`` keeps an SM free for it.
+
+The three functions of the reference's hooks (``longcat_video/context_parallel/ulysses_wrapper.py:86-116``) keep
+their meaning; this module only moves the bytes.  No kernel of this library reads or writes peer memory.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+_ARENAS: Dict[Tuple[int, int, torch.dtype], "PeerArena"] = {}
+
+
+def available(t: torch.Tensor, group) -> bool:
+    """True when the exchange of ``t`` over ``group`` can take the peer-copy path."""
+    if os.environ.get("LCBSA_ULYSSES_EXCHANGE", "peer") != "peer":
+        return False
+    if not t.is_cuda or dist.get_backend(group) != "nccl":
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception:
+        return False
+    return True
+
+
+class PeerArena:
+    """The symmetric receive buffer of one (group, device, dtype) and the views of it in every peer."""
+
+    def __init__(self, group, device: torch.device, dtype: torch.dtype):
+        self.group, self.device, self.dtype = group, device, dtype
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.numel = 0
+        self.buf: Optional[torch.Tensor] = None
+        self.hdl = None
+
+    def ensure(self, numel: int) -> None:
+        """Collective: every rank asks for the same size (the exchange shapes are the same on all ranks)."""
+        if numel <= self.numel:
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if self.buf is not None:  # growing: nobody may still be pushing into the old buffer
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+        self.buf = symm_mem.empty(numel, dtype=self.dtype, device=self.device)
+        self.hdl = symm_mem.rendezvous(self.buf, self.group)
+        self.numel = numel
+
+    def view(self, rank: int, offset: int, shape) -> torch.Tensor:
+        """``shape`` elements at ``offset`` of rank ``rank``'s buffer, as a tensor on this device."""
+        if rank == self.rank:
+            n = 1
+            for s in shape:
+                n *= s
+            return self.buf[offset:offset + n].view(shape)
+        return self.hdl.get_buffer(rank, tuple(shape), self.dtype, offset)
+
+    def barrier(self) -> None:
+        self.hdl.barrier(channel=0)
+
+
+def arena(group, device: torch.device, dtype: torch.dtype) -> PeerArena:
+    key = (id(group), torch.device(device).index or 0, dtype)
+    if key not in _ARENAS:
+        _ARENAS[key] = PeerArena(group, device, dtype)
+    return _ARENAS[key]
+
+
+def reset() -> None:
+    _ARENAS.clear()
+
+
+class PeerExchange:
+    """One forward call's worth of exchange for ``[1, H, S/N, D]`` inputs: receive views and the push operations.
+
+    All pushes and barriers are issued on ``side`` in the same order on every rank (the barrier is a collective of
+    the group); ``main`` is the stream the attention kernels run on.  A push is one call of ``lcbsa_copy_slabs``
+    (a loop of ``cudaMemcpyAsync`` in C: the Python cost of the hundred-odd slabs of a step would otherwise rival
+    the attention itself on eight GPUs)."""
+
+    def __init__(self, group, query: torch.Tensor, main: torch.cuda.Stream, side: torch.cuda.Stream):
+        from .. import _lib as L
+
+        self._L = L
+        B, H, Sl, D = query.shape
+        self.n = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.H, self.Sl, self.D = H, Sl, D
+        self.hn = H // self.n
+        self.S = self.n * Sl
+        self.es = query.element_size()
+        self.main, self.side = main, side
+        self.ar = arena(group, query.device, query.dtype)
+        self.in_elems = self.hn * self.S * D
+        out_elems = H * Sl * D
+        # two output regions, used alternately, so that the result of one call may still be read while the next
+        # call's exchange is already writing
+        self.ar.ensure(3 * self.in_elems + 2 * out_elems)
+        calls = getattr(self.ar, "_calls", 0)
+        self.ar._calls = calls + 1
+        self.out_off = 3 * self.in_elems + (calls & 1) * out_elems
+        # my receive side
+        self.local_in = [self.ar.view(self.rank, t * self.in_elems, (1, self.hn, self.S, D)) for t in range(3)]
+        self.local_out = self.ar.view(self.rank, self.out_off, (1, H, Sl, D))
+        # base address of every rank's buffer as seen from this process
+        if getattr(self.ar, "_bases", None) is None or self.ar._bases_numel != self.ar.numel:
+            self.ar._bases = [self.ar.view(r, 0, (1,)).data_ptr() for r in range(self.n)]
+            self.ar._bases_numel = self.ar.numel
+        self.bases = self.ar._bases
+
+    def _copy(self, dst: List[int], src: List[int]) -> None:
+        n = len(dst)
+        arr = (ctypes.c_void_p * (2 * n))(*dst, *src)
+        base = ctypes.addressof(arr)
+        self._L.check(self._L.lib().lcbsa_copy_slabs(base, base + n * ctypes.sizeof(ctypes.c_void_p), self.Sl * self.D * self.es, n,
+                                                   self.side.cuda_stream))
+
+    def push_in(self, tensors, lo: int, hi: int) -> torch.cuda.Event:
+        """Send heads ``lo:hi`` (of every rank's share) of q, k, v to their owners; the event fires when this
+        rank's own receive views of those heads are complete."""
+        slab = self.Sl * self.D
+        dst, src = [], []
+        for t, x in enumerate(tensors):
+            xp, xs = x.data_ptr(), x.stride(1)
+            for r in range(self.n):
+                b = self.bases[r] + t * self.in_elems * self.es
+                for j in range(lo, hi):
+                    dst.append(b + (j * self.n + self.rank) * slab * self.es)  # [head j][source rank][S/N][D] of rank r
+                    src.append(xp + (r * self.hn + j) * xs * self.es)          # x[0, r * hn + j]
+        with torch.cuda.stream(self.side):
+            self._copy(dst, src)
+            self.ar.barrier()
+            return self.side.record_event()
+
+    def received(self, lo: int, hi: int) -> List[torch.Tensor]:
+        return [v[:, lo:hi] for v in self.local_in]
+
+    def push_out(self, o: torch.Tensor, lo: int) -> torch.cuda.Event:
+        """Return the attention result ``o [1, h, S, D]`` of local heads ``lo:lo+h``: token chunk r goes to rank r."""
+        done = self.main.record_event()
+        o.record_stream(self.side)
+        slab = self.Sl * self.D
+        op = o.data_ptr()
+        dst, src = [], []
+        for r in range(self.n):
+            b = self.bases[r] + self.out_off * self.es
+            for j in range(o.shape[1]):
+                dst.append(b + (self.rank * self.hn + lo + j) * slab * self.es)  # out[head rank*hn+lo+j] of rank r
+                src.append(op + (j * self.S + r * self.Sl) * self.D * self.es)   # o[0, j, r*Sl:(r+1)*Sl]
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(done)
+            self._copy(dst, src)
+            self.ar.barrier()
+            return self.side.record_event()

@@ -197,6 +197,21 @@ int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor
     return LCBSA_OK;
 }
 
+int lcbsa_set_attn_sm_reserve(int n_sms) {
+    if (n_sms < 0 || n_sms > 64) return fail(LCBSA_EINVAL, "sm reserve %d outside 0..64", n_sms);
+    return lcbsa::set_attn_sm_reserve(n_sms);
+}
+
+int lcbsa_copy_slabs(void* const* dst, const void* const* src, size_t nbytes, int count, void* stream) {
+    if (count < 0 || (count > 0 && (!dst || !src))) return fail(LCBSA_EINVAL, "copy_slabs: null pointer array");
+    for (int i = 0; i < count; ++i) {
+        if (!dst[i] || !src[i]) return fail(LCBSA_EINVAL, "copy_slabs: null slab %d", i);
+        cudaError_t e = cudaMemcpyAsync(dst[i], src[i], nbytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail(LCBSA_ECUDA, "copy_slabs: slab %d: %s", i, cudaGetErrorString(e));
+    }
+    return LCBSA_OK;
+}
+
 int lcbsa_check_device_status(void) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return fail(LCBSA_ECUDA, "device synchronize: %s", cudaGetErrorString(e));

@@ -48,6 +48,8 @@
 // flag that all roles poll, drains its outstanding bulk copies, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace lcbsa {
@@ -960,6 +962,9 @@ extern "C" void lcbsa_debug_set_buffer(float* p) { g_tc_debug = p; }
 extern "C" void lcbsa_debug_set_timeline(long long* p) { g_tc_ts = p; }
 #endif
 
+static std::atomic<int> g_sm_reserve{0};
+int set_attn_sm_reserve(int n_sms) { return g_sm_reserve.exchange(n_sms); }
+
 bool attn_tc_supported(const AttnArgs& a, const char** why) {
     if (a.dtype != LCBSA_BF16 && a.dtype != LCBSA_FP16) { *why = "needs bf16 or fp16"; return false; }
     if (a.D != kD) { *why = "needs head_dim 128"; return false; }
@@ -1013,7 +1018,8 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
     if (e != cudaSuccess) return e;
     const long long groups = (a.gq.nblk + kTilesPerWork - 1) / kTilesPerWork;
     const long long work = groups * a.B * a.H;
-    const int grid = (int)(work < sm_count ? work : sm_count);
+    const int usable = sm_count - g_sm_reserve.load() > 0 ? sm_count - g_sm_reserve.load() : 1;
+    const int grid = (int)(work < usable ? work : usable);
     kern<<<grid, kThreads, kSmemBytes, st>>>(P);
     return cudaGetLastError();
 }

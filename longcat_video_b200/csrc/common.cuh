@@ -96,5 +96,6 @@ struct AttnArgs {
 cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why);
 bool attn_tc_supported(const AttnArgs& a, const char** why);
+int set_attn_sm_reserve(int n_sms);  // SMs the tcgen05 attention kernel leaves idle; returns the previous value
 
 }  // namespace lcbsa
