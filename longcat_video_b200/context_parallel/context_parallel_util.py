@@ -35,6 +35,15 @@ def init_context_parallel(context_parallel_size: int = 1, global_rank: int = 0, 
             dp_group, dp_ranks = grp, ranks
     dp_rank = dist.get_rank(group=dp_group)
     cp_rank = dist.get_rank(group=cp_group)
+    if cp_size > 1:
+        # The attention kernel owns every SM it is given; the barrier kernel of the overlapped exchange
+        # (peer_exchange) needs one to start on.  LCBSA_ATTN_SM_RESERVE overrides the two SMs kept free.
+        import os
+
+        from .. import _lib
+
+        if _lib.lib().lcbsa_set_attn_sm_reserve(int(os.environ.get("LCBSA_ATTN_SM_RESERVE", "2"))) < 0:
+            _lib.check(-1)
 
 
 def reset_context_parallel():
