@@ -90,6 +90,7 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
     end.record()
     sync()
     clocks = sampler.stop() if sampler else None
+    timed_launches = launches["n"]
     L.check(L.lib().lcbsa_check_device_status())
     ms_local = start.elapsed_time(end) / args.steps
     ms_attn_local = sum(a.elapsed_time(b) for a, b in attn_events) / args.steps
@@ -139,7 +140,7 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
                 "roofline": {"bound": "tensor", "kernel": "attn_tc_kernel", "achieved": attn_tf, "peak": peak, "unit": "TFLOP/s",
                              "frac": attn_tf / peak, "peak_source": f"{peak_src} (burst cuBLAS bf16 x {world} GPUs)",
                              "ms_per_step_in_kernel": ms_attn, "traffic": None},
-                "cpu_baseline": None, "e2e": e2e, "clocks": clocks, "gpu_launches": launches["n"]}
+                "cpu_baseline": None, "e2e": e2e, "clocks": clocks, "gpu_launches": timed_launches}
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
