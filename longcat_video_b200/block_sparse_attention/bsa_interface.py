@@ -168,3 +168,68 @@ def flash_attn_bsa_3d(
                                   chunk_3d_shape_q, chunk_3d_shape_k)
     return attn_fwd_bsa_varlen(q, k, v, 1 / head_dim ** 0.5, idx, cnt, latent_shape_q, latent_shape_k,
                                chunk_3d_shape_q, chunk_3d_shape_k)
+
+
+_HOST_STATE = {}
+
+
+def flash_attn_bsa_3d_host(q, k, v, latent_shape_q, latent_shape_k, out=None, heads_per_chunk=4, device=None, **bsa_params):
+    """``flash_attn_bsa_3d`` for tensors that live in (pinned) host memory: q, k, v ``[B, H, S, D]`` on the host in,
+    the result on the host out (``out`` is filled and returned if given, else a pinned tensor is allocated).
+
+    An extension without counterpart in the reference (whose op only takes device tensors).  The heads are
+    independent, so the call is pipelined by chunks of ``heads_per_chunk`` heads over three streams: while the
+    kernels work on chunk c, the copy engines bring in chunk c+1 and take the result of chunk c-1 back, through two
+    device staging buffers per tensor.  End to end the call then costs about what moving the bytes over PCIe costs.
+    """
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise RuntimeError("flash_attn_bsa_3d_host takes host tensors; use flash_attn_bsa_3d for device tensors")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B_, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    hc = max(1, min(int(heads_per_chunk), H))
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    key = (dev.index, B_, hc, Sq, Sk, D, q.dtype)
+    st = _HOST_STATE.get(key)
+    if st is None:
+        _HOST_STATE.clear()  # one shape at a time: the staging buffers of another shape are dropped
+        st = {"q": [torch.empty(B_, hc, Sq, D, dtype=q.dtype, device=dev) for _ in range(2)],
+              "k": [torch.empty(B_, hc, Sk, D, dtype=q.dtype, device=dev) for _ in range(2)],
+              "v": [torch.empty(B_, hc, Sk, D, dtype=q.dtype, device=dev) for _ in range(2)],
+              "h2d": torch.cuda.Stream(device=dev), "d2h": torch.cuda.Stream(device=dev)}
+        _HOST_STATE[key] = st
+    main = torch.cuda.current_stream(dev)
+    h2d, d2h = st["h2d"], st["d2h"]
+    h2d.wait_stream(main)
+    d2h.wait_stream(main)
+    chunks = [(lo, min(lo + hc, H)) for lo in range(0, H, hc)]
+    done = []
+
+    def bring(c):
+        lo, hi = chunks[c]
+        slot = c & 1
+        with torch.cuda.stream(h2d):
+            if c >= 2:
+                h2d.wait_event(done[c - 2])  # the kernels of chunk c-2 are through with this staging buffer
+            for name, src in (("q", q), ("k", k), ("v", v)):
+                st[name][slot][:, :hi - lo].copy_(src[:, lo:hi], non_blocking=True)
+            return h2d.record_event()
+
+    arrived = [bring(0)]
+    for c, (lo, hi) in enumerate(chunks):
+        if c + 1 < len(chunks):
+            # chunk c-1's kernels are already queued, so its `done` event exists when chunk c+1 wants its buffer
+            arrived.append(bring(c + 1))
+        slot = c & 1
+        main.wait_event(arrived[c])
+        o = flash_attn_bsa_3d(st["q"][slot][:, :hi - lo], st["k"][slot][:, :hi - lo], st["v"][slot][:, :hi - lo],
+                              latent_shape_q, latent_shape_k, **bsa_params)
+        done.append(main.record_event())
+        o.record_stream(d2h)
+        with torch.cuda.stream(d2h):
+            d2h.wait_event(done[c])
+            out[:, lo:hi].copy_(o, non_blocking=True)
+    main.wait_stream(d2h)
+    main.wait_stream(h2d)
+    return out

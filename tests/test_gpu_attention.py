@@ -151,3 +151,50 @@ def test_tc_matches_generic_kernel_at_size():
     assert torch.equal(a, a2)
     assert rel_l2(a.float().cpu(), b.float().cpu()) <= REL_L2_TOL
     assert max_abs(a.float().cpu(), b.float().cpu()) <= MAX_ABS_TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,chunk_heads", [(6, 4), (5, 2), (3, 8)])
+def test_host_entry_point_matches_device_call(heads, chunk_heads):
+    """flash_attn_bsa_3d_host (pinned host tensors in and out, pipelined by head chunks) returns exactly what
+    flash_attn_bsa_3d returns for the same tensors on the device; repeated calls reuse its staging buffers."""
+    grid, chunk = (8, 8, 16), (4, 4, 4)
+    S = grid[0] * grid[1] * grid[2]
+    g = torch.Generator().manual_seed(11)
+    q, k, v = ((torch.randn(1, heads, S, 128, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(3))
+    kw = dict(sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
+    want = B.flash_attn_bsa_3d(q.cuda(), k.cuda(), v.cuda(), grid, grid, **kw).cpu()
+    out = torch.empty_like(want).pin_memory()
+    for _ in range(3):
+        out.zero_()
+        got = B.flash_attn_bsa_3d_host(q, k, v, grid, grid, out=out, heads_per_chunk=chunk_heads, **kw)
+        torch.cuda.synchronize()
+        assert got is out
+        assert torch.equal(out, want)
+    L.check(L.lib().lcbsa_check_device_status())
+    with pytest.raises(RuntimeError):
+        B.flash_attn_bsa_3d_host(q.cuda(), k, v, grid, grid, **kw)
+
+
+@pytest.mark.gpu
+def test_copy_slabs_and_sm_reserve():
+    """lcbsa_copy_slabs moves every slab; lcbsa_set_attn_sm_reserve validates its range and returns the old value."""
+    import ctypes
+
+    src = torch.arange(8 * 1024, dtype=torch.int32, device="cuda").view(8, 1024)
+    dst = torch.zeros_like(src)
+    order = [3, 0, 7, 1, 6, 2, 5, 4]
+    n = len(order)
+    arr = (ctypes.c_void_p * (2 * n))(*[dst[i].data_ptr() for i in range(n)], *[src[j].data_ptr() for j in order])
+    base = ctypes.addressof(arr)
+    L.check(L.lib().lcbsa_copy_slabs(base, base + n * ctypes.sizeof(ctypes.c_void_p), 1024 * 4, n,
+                                     torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src[order])
+    assert L.lib().lcbsa_copy_slabs(None, None, 16, 1, None) == -1
+    lib = L.lib()
+    old = lib.lcbsa_set_attn_sm_reserve(4)
+    assert old >= 0
+    assert lib.lcbsa_set_attn_sm_reserve(old) == 4
+    assert lib.lcbsa_set_attn_sm_reserve(-1) == -1 and lib.lcbsa_set_attn_sm_reserve(1000) == -1
+    assert lib.lcbsa_set_attn_sm_reserve(old) == old
