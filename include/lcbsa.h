@@ -90,6 +90,15 @@ int lcbsa_pool(const LcbsaTensor* x, const LcbsaGrid* g, void* out, void* stream
 int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D,
                      int nsel, int cap, int32_t* idx, int32_t* cnt, void* stream);
 
+/*
+ * Bytes of workspace with which lcbsa_block_select takes its faster form: pooled Q and K plus one 16-bit key per
+ * block score (B*H*Nq*Nk_padded*2 bytes), which lets the scores be computed by a register-tiled GEMM kernel and the
+ * rows be selected by a second kernel.  Results are identical to the fused form.  Equal to
+ * lcbsa_select_workspace_bytes when that form does not apply (fp32 inputs, head_dim other than 64 or 128).
+ */
+size_t lcbsa_select_workspace_bytes_fast(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq,
+                                         const LcbsaGrid* gk);
+
 /* Bytes of workspace lcbsa_block_select needs (pooled Q and pooled K). */
 size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq,
                                     const LcbsaGrid* gk);

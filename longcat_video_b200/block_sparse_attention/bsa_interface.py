@@ -91,7 +91,7 @@ def get_select_indices(q: torch.Tensor, k: torch.Tensor, latent_shape_q, latent_
     nsel = num_selected(sparsity, nk)
     cap = max(nsel, 1)
     qd, kd = L.tensor_desc(q), L.tensor_desc(k)
-    ws_bytes = L.lib().lcbsa_select_workspace_bytes(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk))
+    ws_bytes = L.lib().lcbsa_select_workspace_bytes_fast(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk))
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
     idx = torch.empty(B, H, nq, cap, dtype=torch.int32, device=q.device)
     cnt = torch.empty(B, H, nq, dtype=torch.int32, device=q.device)

@@ -131,6 +131,14 @@ size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, 
     return up(bhd * nq) + up(bhd * nk);
 }
 
+size_t lcbsa_select_workspace_bytes_fast(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk) {
+    const size_t base = lcbsa_select_workspace_bytes(q, k, gq, gk);
+    if (base == 0) return 0;
+    const size_t keys = lcbsa::score_keys_bytes(q->dtype, (int)(q->size[0] * q->size[1]), lcbsa::make_geom(*gq).nblk,
+                                                lcbsa::make_geom(*gk).nblk, (int)q->size[3]);
+    return base + (keys + 255) / 256 * 256;
+}
+
 int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel,
                        int cap, int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream) {
     if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "block_select: bad grid");
@@ -150,6 +158,19 @@ int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGr
     unsigned char* kc = qc + (bhd * ggq.nblk + 255) / 256 * 256;
     if (int rc = lcbsa_pool(q, gq, qc, stream)) return rc;
     if (int rc = lcbsa_pool(k, gk, kc, stream)) return rc;
+    // With room for the score keys the scores are computed by the register-tiled GEMM kernel and selected by a second
+    // kernel; otherwise by the fused kernel that keeps them in shared memory.
+    const size_t fast = lcbsa_select_workspace_bytes_fast(q, k, gq, gk);
+    if (fast > need && workspace_bytes >= fast) {
+        if (nsel < 0 || cap < 1 || nsel > cap || nsel > ggk.nblk || !idx || !cnt)
+            return fail(LCBSA_EINVAL, "block_select: bad nsel/cap (%d/%d for %d key blocks) or null outputs", nsel, cap, ggk.nblk);
+        const char* why = "";
+        cudaError_t e = lcbsa::launch_score_gemm_topk(q->dtype, qc, kc, (int)(q->size[0] * q->size[1]), ggq.nblk, ggk.nblk,
+                                                      (int)q->size[3], nsel, cap, idx, cnt,
+                                                      static_cast<unsigned char*>(workspace) + need, static_cast<cudaStream_t>(stream), &why);
+        if (e != cudaSuccess) return cuda_fail(e, "score_gemm_topk", why);
+        return LCBSA_OK;
+    }
     return lcbsa_score_topk(qc, kc, q->dtype, (int)(q->size[0] * q->size[1]), ggq.nblk, ggk.nblk, (int)q->size[3], nsel, cap,
                             idx, cnt, stream);
 }

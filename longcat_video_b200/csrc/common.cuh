@@ -77,6 +77,10 @@ void set_last_error(const char* msg);
 // Launchers implemented in the .cu files (host side). All return a cudaError_t from the launch.
 cudaError_t launch_pool(int dtype, const View& x, int B, int H, int D, const Geom& g, void* out, cudaStream_t st);
 
+// two-kernel form of the same stage (select_gemm.cu): bytes of key workspace it needs (0: does not apply) and launch
+size_t score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D);
+cudaError_t launch_score_gemm_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel, int cap,
+                                   int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why);
 cudaError_t launch_score_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel,
                               int cap, int32_t* idx, int32_t* cnt, cudaStream_t st, const char** why);
 

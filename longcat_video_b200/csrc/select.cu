@@ -12,7 +12,7 @@
 // selects, for its rows, the nsel largest keys: the threshold key is found by bisection over the key
 // bits, ties at the threshold are broken towards the lower block index, and the selected block
 // indices are emitted in ascending order with warp ballots.  No atomics: the result is deterministic.
-#include "common.cuh"
+#include "select_common.cuh"
 
 namespace lcbsa {
 
@@ -22,54 +22,7 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kChunk = 64;  // pooled K rows per shared-memory chunk
 
-template <typename T> struct KeyOf { using type = uint16_t; };
-template <> struct KeyOf<float> { using type = uint32_t; };
-
-// Order-preserving key: a larger key is a larger score; -0 equals +0; NaN ranks above +inf.
-__device__ __forceinline__ uint16_t make_key(__nv_bfloat16 v) {
-    uint16_t u = __bfloat16_as_ushort(v);
-    if ((u & 0x7fffu) > 0x7f80u) return 0xffffu;
-    if (u == 0x8000u) u = 0;
-    return (u & 0x8000u) ? (uint16_t)~u : (uint16_t)(u | 0x8000u);
-}
-__device__ __forceinline__ uint16_t make_key(__half v) {
-    uint16_t u = __half_as_ushort(v);
-    if ((u & 0x7fffu) > 0x7c00u) return 0xffffu;
-    if (u == 0x8000u) u = 0;
-    return (u & 0x8000u) ? (uint16_t)~u : (uint16_t)(u | 0x8000u);
-}
-__device__ __forceinline__ uint32_t make_key(float v) {
-    uint32_t u = __float_as_uint(v);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return 0xffffffffu;
-    if (u == 0x80000000u) u = 0;
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-__device__ __forceinline__ int warp_sum(int v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// Number of keys of a row that are >= cand (gt == false) or > cand (gt == true).
-__device__ __forceinline__ int count_row(const uint16_t* row, int nk_pad, uint32_t cand, bool gt, int lane) {
-    const uint32_t* r32 = reinterpret_cast<const uint32_t*>(row);
-    const uint32_t c = gt ? cand + 1u : cand;  // cand + 1 may be 0x10000: no 16-bit key reaches it
-    int n = 0;
-    for (int p = lane; p < nk_pad / 2; p += 32) {
-        const uint32_t kk = r32[p];
-        n += ((kk & 0xffffu) >= c) + ((kk >> 16) >= c);
-    }
-    return warp_sum(n);
-}
-__device__ __forceinline__ int count_row(const uint32_t* row, int nk_pad, uint32_t cand, bool gt, int lane) {
-    int n = 0;
-    for (int p = lane; p < nk_pad; p += 32) {
-        const uint32_t kk = row[p];
-        n += gt ? (kk > cand) : (kk >= cand);
-    }
-    return warp_sum(n);
-}
+using namespace sel;
 
 template <typename T, int D, int QPW>
 __global__ void __launch_bounds__(kThreads) score_topk_kernel(const T* __restrict__ qc, const T* __restrict__ kc,
@@ -170,37 +123,11 @@ __global__ void __launch_bounds__(kThreads) score_topk_kernel(const T* __restric
     }
 
     // ---- per-row selection: each warp owns its QPW rows
-    constexpr int kKeyBits = sizeof(Key) * 8;
     for (int i = 0; i < QPW; ++i) {
         const int qrow = q0 + warp * QPW + i;
         if (qrow >= Nq) break;
-        const Key* row = keys + (long long)(warp * QPW + i) * nk_pad;
-        int32_t* out = idx + ((long long)bh * Nq + qrow) * cap;
-        if (lane == 0) cnt[(long long)bh * Nq + qrow] = nsel;
-        if (nsel > 0) {
-            uint32_t thr = 0;
-            for (int bit = kKeyBits - 1; bit >= 0; --bit) {
-                const uint32_t cand = thr | (1u << bit);
-                if (count_row(row, nk_pad, cand, false, lane) >= nsel) thr = cand;
-            }
-            const int above = count_row(row, nk_pad, thr, true, lane);
-            const int take_eq = nsel - above;  // ties at the threshold to keep, lowest block index first
-            int n_out = 0, n_eq = 0;
-            const unsigned lt_mask = (1u << lane) - 1u;
-            for (int j0 = 0; j0 < Nk; j0 += 32) {
-                const int j = j0 + lane;
-                const uint32_t key = (j < Nk) ? (uint32_t)row[j] : 0u;
-                const bool gt = key > thr;
-                const bool eq = (key == thr) && (j < Nk);
-                const unsigned eq_mask = __ballot_sync(0xffffffffu, eq);
-                const bool take = gt || (eq && (n_eq + __popc(eq_mask & lt_mask) < take_eq));
-                const unsigned take_mask = __ballot_sync(0xffffffffu, take);
-                if (take) out[n_out + __popc(take_mask & lt_mask)] = j;
-                n_out += __popc(take_mask);
-                n_eq += __popc(eq_mask);
-            }
-        }
-        for (int j = nsel + lane; j < cap; j += 32) out[j] = -1;
+        select_row<Key>(keys + (long long)(warp * QPW + i) * nk_pad, Nk, nk_pad, nsel, cap, idx + ((long long)bh * Nq + qrow) * cap,
+                        cnt + (long long)bh * Nq + qrow, lane);
     }
 }
 
