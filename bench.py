@@ -39,9 +39,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # the ncu capture summarised in profiles/attn_tc_kernel_480p_16heads.md (599.2 MB against 654.3 MB).  K and V of a
 # head are re-read from L2, so the traffic of a launch grows with the tensors, not with the selected blocks.
 NCU_ATTN_DRAM_PER_IO_BYTE = 599.2 / 654.3
-# the same for the block-select stage (profiles/score_topk_kernel_480p_16heads.md): two pool launches read q and k
-# once (163.6 + 4.1 MB each against 163.6 algorithmic), the score/top-k launch adds 5.1 MB.
-NCU_SELECT_DRAM_PER_IO_BYTE = (2 * 167.7 + 5.1) / (2 * 163.6)
+# the same for the block-select stage (profiles/select_kernels_480p_16heads.md): two pool launches read q and k
+# once (163.6 + 4.1 MB each against 163.6 algorithmic), the score and top-k launches add 5.2 + 12.8 MB.
+NCU_SELECT_DRAM_PER_IO_BYTE = (2 * 167.7 + 5.2 + 12.8) / (2 * 163.6)
 
 
 def load_peaks():
@@ -166,7 +166,7 @@ def main():
         out = B.attn_fwd_bsa_varlen(q, k, v, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk, impl=attn_impl)
         if events:
             events[2].record()
-        launches["n"] += 4  # pool(q), pool(k), score+top-k, attention
+        launches["n"] += 5  # pool(q), pool(k), score GEMM, top-k, attention
         return idx, cnt, out
 
     for _ in range(args.warmup):
@@ -207,7 +207,7 @@ def main():
                 "traffic": (NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes) if attn_impl != L.ATTN_MMA else None,
                 "traffic_source": "ncu capture of 480p_legal/16 heads scaled by the bytes of q,k,v,out"}
     sel_gbs = select_bytes / ms_select / 1e6
-    roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_topk_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
+    roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_gemm_kernel + topk_rows_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
                        "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"], "peak_source": peak_src, "ms_per_stage": ms_select,
                        "traffic": NCU_SELECT_DRAM_PER_IO_BYTE * select_bytes}
 

@@ -57,7 +57,7 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
             o = B.attn_fwd_bsa_varlen(q_, k_, v_, scale, idx, cnt, shape, shape, wl.chunk, wl.chunk, impl=attn_impl)
             e1.record()
             attn_events.append((e0, e1))
-            launches["n"] += 4
+            launches["n"] += 5  # pool(q), pool(k), score GEMM, top-k, attention
             return o
 
     layer = Layer()
