@@ -14,10 +14,10 @@ namespace lcbsa {
 
 namespace {
 
-constexpr int kBatch = 16;  // independent 16-byte loads in flight per lane
+constexpr int kBatch = 8;  // independent 16-byte loads in flight per lane (64 registers: four CTAs per SM; measured 5.1 TB/s against 4.5 with 16)
 
 template <typename T, int VEC>
-__global__ void __launch_bounds__(256) pool_kernel(View x, int H, int D, Geom g, T* __restrict__ out, int lpr,
+__global__ void __launch_bounds__(256, 4) pool_kernel(View x, int H, int D, Geom g, T* __restrict__ out, int lpr,
                                                     long long total_groups) {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long group = gtid / lpr;
