@@ -86,6 +86,32 @@ def arena(group, device: torch.device, dtype: torch.dtype) -> PeerArena:
 
 def reset() -> None:
     _ARENAS.clear()
+    _SIDE.clear()
+    _FAILED.clear()
+
+
+_SIDE: Dict[int, torch.cuda.Stream] = {}
+_FAILED: Dict[int, str] = {}
+
+
+def open_exchange(group, query: torch.Tensor) -> Optional["PeerExchange"]:
+    """The exchange object for one call, or None when the symmetric buffer cannot be set up for this group (the
+    failure is remembered and reported once; the caller then takes the NCCL path).  Setting it up is a collective
+    of the group, so every rank gets the same answer."""
+    gid = id(group)
+    if gid in _FAILED:
+        return None
+    idx = query.device.index if query.device.index is not None else torch.cuda.current_device()
+    if idx not in _SIDE:
+        _SIDE[idx] = torch.cuda.Stream(device=query.device)
+    try:
+        return PeerExchange(group, query, torch.cuda.current_stream(query.device), _SIDE[idx])
+    except Exception as e:  # noqa: BLE001 - any failure of the symmetric-memory setup means "use NCCL"
+        _FAILED[gid] = repr(e)
+        import warnings
+
+        warnings.warn(f"peer-copy exchange unavailable ({e!r}); using the NCCL exchange")
+        return None
 
 
 class PeerExchange:

@@ -223,15 +223,13 @@ def ulysses_a2a_out(output):
     return seq_scatter_heads_gather(output, context_parallel_util.get_cp_group())
 
 
-def _peer_pipeline(func, self, query, key, value, shape, group, stages):
+def _peer_pipeline(func, self, query, key, value, shape, ex, stages):
     """The pipeline of ``ulysses_wrapper`` with the exchanges done by peer DMA copies (``peer_exchange``): the
     push of stage g+1 and the return of stage g-1 run on the copy engines while attention works on stage g."""
-    main = torch.cuda.current_stream()
-    side = _side_stream(query.device)
+    main, side = ex.main, ex.side
     side.wait_stream(main)
     for t in (query, key, value):
         t.record_stream(side)
-    ex = peer_exchange.PeerExchange(group, query, main, side)
     ev = ex.push_in((query, key, value), *stages[0])
     ev_out = None
     for g, (lo, hi) in enumerate(stages):
@@ -312,7 +310,9 @@ def ulysses_wrapper(func):
         stages = _stages(hn, hg)
         if (B == 1 and peer_exchange.available(query, group)
                 and all(t[0, 0].is_contiguous() and t.shape == query.shape and t.dtype == query.dtype for t in (query, key, value))):
-            return _peer_pipeline(func, self, query, key, value, shape, group, stages)
+            ex = peer_exchange.open_exchange(group, query)  # None if symmetric memory cannot be set up here
+            if ex is not None:
+                return _peer_pipeline(func, self, query, key, value, shape, ex, stages)
         if hg == hn:
             q, k, v = ulysses_a2a_in(query, key, value)
             return ulysses_a2a_out(func(self, q, k, v, shape))
