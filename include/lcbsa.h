@@ -91,6 +91,16 @@ int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, in
                      int nsel, int cap, int32_t* idx, int32_t* cnt, void* stream);
 
 /*
+ * lcbsa_score_topk with a workspace for the scores: with keys_bytes >= lcbsa_score_keys_bytes(...) (one 16-bit key
+ * per score; 0 when the form does not apply: fp32, head_dim other than 64 or 128) the scores are computed by a
+ * register-tiled GEMM kernel into the workspace and a second kernel selects per row; otherwise this is
+ * lcbsa_score_topk.  Same results either way.
+ */
+size_t lcbsa_score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D);
+int lcbsa_score_topk_ws(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, int nsel, int cap,
+                        int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream);
+
+/*
  * Bytes of workspace with which lcbsa_block_select takes its faster form: pooled Q and K plus one 16-bit key per
  * block score (B*H*Nq*Nk_padded*2 bytes), which lets the scores be computed by a register-tiled GEMM kernel and the
  * rows be selected by a second kernel.  Results are identical to the fused form.  Equal to

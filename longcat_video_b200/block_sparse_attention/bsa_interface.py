@@ -70,9 +70,13 @@ def get_select_indices_from_pooled(q_cmp: torch.Tensor, k_cmp: torch.Tensor, spa
     cap = max(nsel, 1)
     idx = torch.empty(B, H, Nq, cap, dtype=torch.int32, device=q_cmp.device)
     cnt = torch.empty(B, H, Nq, dtype=torch.int32, device=q_cmp.device)
+    dt = L.dtype_code(q_cmp.dtype)
+    keys_bytes = L.lib().lcbsa_score_keys_bytes(dt, B * H, Nq, Nk, D)  # 0: only the fused kernel applies
+    ws = torch.empty(max(keys_bytes, 16), dtype=torch.uint8, device=q_cmp.device)
     with torch.cuda.device(q_cmp.device):
-        L.check(L.lib().lcbsa_score_topk(q_cmp.data_ptr(), k_cmp.data_ptr(), L.dtype_code(q_cmp.dtype), B * H, Nq, Nk, D,
-                                         nsel, cap, idx.data_ptr(), cnt.data_ptr(), L.current_stream(q_cmp.device)))
+        L.check(L.lib().lcbsa_score_topk_ws(q_cmp.data_ptr(), k_cmp.data_ptr(), dt, B * H, Nq, Nk, D, nsel, cap,
+                                            idx.data_ptr(), cnt.data_ptr(), ws.data_ptr(), keys_bytes,
+                                            L.current_stream(q_cmp.device)))
     return idx, cnt
 
 

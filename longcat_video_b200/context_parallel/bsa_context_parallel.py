@@ -1,0 +1,97 @@
+"""Block-sparse attention under Ulysses context parallelism as ONE op.
+
+``Attention._process_attn`` of the reference (``longcat_video/modules/attention.py:49-67``) is
+``ulysses_wrapper(flash_attn_bsa_3d)``: all-to-all, then pool + score + top-k + attention on the gathered tensors,
+then all-to-all back.  ``flash_attn_bsa_3d_ulysses`` computes the same result (bit for bit) in a different order:
+
+  1. every rank mean-pools the 3-D blocks of ITS tokens for all heads (blocks never straddle ranks: the gathered
+     sequence is rank-major and the grid is split along T), and only the pooled rows -- 1/64 of the bytes --
+     are exchanged first;
+  2. the block lists of all the rank's heads are selected in one launch while the first q, k, v slabs are still on
+     their way;
+  3. the attention runs stage by stage over head groups, each stage's q, k, v arriving by peer DMA during the stage
+     before and its result leaving during the stage after (``peer_exchange``).
+
+Against the generic wrapper this takes the block-select off the critical path and out of the small per-stage
+launches.  It falls back to ``ulysses_wrapper(flash_attn_bsa_3d)`` whenever its preconditions do not hold.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..block_sparse_attention import bsa_interface as B
+from . import context_parallel_util, peer_exchange
+from . import ulysses_wrapper as U
+
+
+def _generic(q, k, v, latent_shape, params):
+    class _Layer:
+        @U.ulysses_wrapper
+        def attn(self, q_, k_, v_, shape):
+            return B.flash_attn_bsa_3d(q_, k_, v_, shape, shape, **params)
+
+    return _Layer().attn(q, k, v, latent_shape)
+
+
+@torch.compiler.disable
+def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_threshold=None, chunk_3d_shape_q=[4, 4, 8],
+                              chunk_3d_shape_k=[4, 4, 8]):
+    """``q, k, v``: this rank's ``[B, H, S/N, D]`` slices (all heads, its tokens); ``latent_shape``: the rank-major
+    grid ``(N*T, H', W')`` of the gathered sequence, as ``_process_attn`` receives it.  Returns ``[B, H, S/N, D]``."""
+    n = context_parallel_util.get_cp_size()
+    params = dict(sparsity=sparsity, cdf_threshold=cdf_threshold, chunk_3d_shape_q=list(chunk_3d_shape_q),
+                  chunk_3d_shape_k=list(chunk_3d_shape_k))
+    if n == 1:
+        return B.flash_attn_bsa_3d(q, k, v, latent_shape, latent_shape, **params)
+    group = context_parallel_util.get_cp_group()
+    Bsz, H, Sl, D = q.shape
+    T, Hh, Ww = latent_shape
+    chunk = tuple(chunk_3d_shape_q)
+    fast = (Bsz == 1 and cdf_threshold is None and sparsity is not None and tuple(chunk_3d_shape_k) == chunk and H % n == 0
+            and T % n == 0 and (T // n) % chunk[0] == 0 and Hh % chunk[1] == 0 and Ww % chunk[2] == 0
+            and (T // n) * Hh * Ww == Sl and q.dtype in (torch.bfloat16, torch.float16)
+            and peer_exchange.available(q, group)
+            and all(t[0, 0].is_contiguous() and t.shape == q.shape and t.dtype == q.dtype for t in (q, k, v)))
+    if not fast:
+        return _generic(q, k, v, latent_shape, params)
+    hn = H // n
+    local_grid = (T // n, Hh, Ww)
+    nblk_l = B.num_blocks(local_grid, chunk)
+    ex = peer_exchange.open_exchange(group, q, extra_elems=2 * hn * n * nblk_l * D)
+    if ex is None:
+        return _generic(q, k, v, latent_shape, params)
+    main, side = ex.main, ex.side
+
+    # 1. pooled rows of this rank's tokens, all heads -> their owners
+    qc_l = B.mean_pooling_compression_3d(q, local_grid, chunk)  # [1, H, nblk_l, D]
+    kc_l = B.mean_pooling_compression_3d(k, local_grid, chunk)
+    pooled = main.record_event()
+    side.wait_stream(main)
+    for t in (q, k, v):
+        t.record_stream(side)
+    ev_pooled = ex.push_rows((qc_l, kc_l), nblk_l, pooled)
+    stages = U._stages(hn, U._heads_per_group(hn))
+    ev = ex.push_in((q, k, v), *stages[0])
+
+    # 2. block lists of all local heads while the first slabs travel
+    main.wait_event(ev_pooled)
+    qc, kc = ex.rows_received(2, nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
+    idx, cnt = B.get_select_indices_from_pooled(qc, kc, sparsity, None)
+    scale = 1 / D ** 0.5
+
+    # 3. attention by head group
+    ev_out = None
+    for g, (lo, hi) in enumerate(stages):
+        main.wait_event(ev)
+        q_, k_, v_ = ex.received(lo, hi)
+        o = B.attn_fwd_bsa_varlen(q_, k_, v_, scale, idx[:, lo:hi], cnt[:, lo:hi], latent_shape, latent_shape, chunk, chunk)
+        ev_next = ex.push_in((q, k, v), *stages[g + 1]) if g + 1 < len(stages) else None
+        ev_out = ex.push_out(o, lo)
+        ev = ev_next
+    main.wait_event(ev_out)
+    import os
+
+    if os.environ.get("LCBSA_ULYSSES_ALIAS_OUT", "0") == "1":
+        return ex.local_out
+    return ex.local_out.clone()

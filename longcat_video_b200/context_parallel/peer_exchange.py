@@ -90,11 +90,23 @@ def reset() -> None:
     _FAILED.clear()
 
 
+_AUX_STREAMS = int(os.environ.get("LCBSA_ULYSSES_COPY_STREAMS", "4"))  # streams the slab copies of one push are spread over
+_AUX: Dict[int, List[torch.cuda.Stream]] = {}
+
+
+def _aux_streams(device, count: int) -> List[torch.cuda.Stream]:
+    idx = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    have = _AUX.setdefault(idx, [])
+    while len(have) < count:
+        have.append(torch.cuda.Stream(device=device))
+    return have[:count]
+
+
 _SIDE: Dict[int, torch.cuda.Stream] = {}
 _FAILED: Dict[int, str] = {}
 
 
-def open_exchange(group, query: torch.Tensor) -> Optional["PeerExchange"]:
+def open_exchange(group, query: torch.Tensor, extra_elems: int = 0) -> Optional["PeerExchange"]:
     """The exchange object for one call, or None when the symmetric buffer cannot be set up for this group (the
     failure is remembered and reported once; the caller then takes the NCCL path).  Setting it up is a collective
     of the group, so every rank gets the same answer."""
@@ -105,7 +117,7 @@ def open_exchange(group, query: torch.Tensor) -> Optional["PeerExchange"]:
     if idx not in _SIDE:
         _SIDE[idx] = torch.cuda.Stream(device=query.device)
     try:
-        return PeerExchange(group, query, torch.cuda.current_stream(query.device), _SIDE[idx])
+        return PeerExchange(group, query, torch.cuda.current_stream(query.device), _SIDE[idx], extra_elems)
     except Exception as e:  # noqa: BLE001 - any failure of the symmetric-memory setup means "use NCCL"
         _FAILED[gid] = repr(e)
         import warnings
@@ -122,7 +134,7 @@ class PeerExchange:
     (a loop of ``cudaMemcpyAsync`` in C: the Python cost of the hundred-odd slabs of a step would otherwise rival
     the attention itself on eight GPUs)."""
 
-    def __init__(self, group, query: torch.Tensor, main: torch.cuda.Stream, side: torch.cuda.Stream):
+    def __init__(self, group, query: torch.Tensor, main: torch.cuda.Stream, side: torch.cuda.Stream, extra_elems: int = 0):
         from .. import _lib as L
 
         self._L = L
@@ -139,7 +151,8 @@ class PeerExchange:
         out_elems = H * Sl * D
         # two output regions, used alternately, so that the result of one call may still be read while the next
         # call's exchange is already writing
-        self.ar.ensure(3 * self.in_elems + 2 * out_elems)
+        self.extra_off = 3 * self.in_elems + 2 * out_elems  # `extra_elems` more for the caller (pooled rows)
+        self.ar.ensure(self.extra_off + extra_elems)
         calls = getattr(self.ar, "_calls", 0)
         self.ar._calls = calls + 1
         self.out_off = 3 * self.in_elems + (calls & 1) * out_elems
@@ -152,18 +165,68 @@ class PeerExchange:
             self.ar._bases_numel = self.ar.numel
         self.bases = self.ar._bases
 
-    def _copy(self, dst: List[int], src: List[int]) -> None:
-        n = len(dst)
-        arr = (ctypes.c_void_p * (2 * n))(*dst, *src)
-        base = ctypes.addressof(arr)
-        self._L.check(self._L.lib().lcbsa_copy_slabs(base, base + n * ctypes.sizeof(ctypes.c_void_p), self.Sl * self.D * self.es, n,
-                                                   self.side.cuda_stream))
+    def _copy(self, dst: List[int], src: List[int], nbytes: Optional[int] = None, lanes: Optional[List[int]] = None) -> None:
+        """Enqueue the slab copies.  Called with ``side`` current.  ``lanes[i]`` (the destination rank of slab i)
+        spreads them over a few auxiliary streams, so that copies to different peers use different copy engines
+        and links at the same time; ``side`` continues when all of them are done."""
+        nbytes = self.Sl * self.D * self.es if nbytes is None else nbytes
+        aux = _aux_streams(self.side.device, min(_AUX_STREAMS, self.n) - 1) if lanes is not None else []
+        groups: List[Tuple[List[int], List[int]]] = [([], []) for _ in range(len(aux) + 1)]
+        for i in range(len(dst)):
+            g = (lanes[i] % len(groups)) if lanes is not None else 0
+            groups[g][0].append(dst[i])
+            groups[g][1].append(src[i])
+        start = self.side.record_event() if aux else None
+        for g, (d, s_) in enumerate(groups):
+            if not d:
+                continue
+            stream = self.side if g == 0 else aux[g - 1]
+            if g > 0:
+                stream.wait_event(start)
+            m = len(d)
+            arr = (ctypes.c_void_p * (2 * m))(*d, *s_)
+            base = ctypes.addressof(arr)
+            self._L.check(self._L.lib().lcbsa_copy_slabs(base, base + m * ctypes.sizeof(ctypes.c_void_p), nbytes, m, stream.cuda_stream))
+            if g > 0:
+                self.side.wait_event(stream.record_event())
+
+    def push_rows(self, tensors, rows: int, after: torch.cuda.Event) -> torch.cuda.Event:
+        """Heads-scatter of small per-block tensors ``[1, H, rows, D]`` (the pooled Q and K of this rank's tokens)
+        into the extra region of the owners of the heads: one contiguous copy per tensor and peer, received as
+        ``[tensor][source rank][H/N][rows][D]``.  ``after`` is the event that marks them computed.  The event
+        returned fires when this rank's own region is complete."""
+        part = self.hn * rows * self.D  # what one rank sends another per tensor
+        dst, src, lanes = [], [], []
+        for t, x in enumerate(tensors):
+            if not x.is_contiguous():
+                raise ValueError("push_rows takes contiguous tensors")
+            x.record_stream(self.side)
+            xp = x.data_ptr()
+            for r in range(self.n):
+                dst.append(self.bases[r] + (self.extra_off + (t * self.n + self.rank) * part) * self.es)
+                src.append(xp + r * part * self.es)  # x[0, r*hn:(r+1)*hn]
+                lanes.append(r)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(after)
+            self._copy(dst, src, part * self.es, lanes=lanes)
+            self.ar.barrier()
+            return self.side.record_event()
+
+    def rows_received(self, n_tensors: int, rows: int) -> List[torch.Tensor]:
+        """The tensors of ``push_rows`` as ``[1, H/N, N * rows, D]`` (source-rank-major row order): a small permuting
+        copy on the current stream out of the receive layout."""
+        part = self.hn * rows * self.D
+        out = []
+        for t in range(n_tensors):
+            v = self.ar.view(self.rank, self.extra_off + t * self.n * part, (self.n, self.hn, rows, self.D))
+            out.append(v.permute(1, 0, 2, 3).reshape(1, self.hn, self.n * rows, self.D))
+        return out
 
     def push_in(self, tensors, lo: int, hi: int) -> torch.cuda.Event:
         """Send heads ``lo:hi`` (of every rank's share) of q, k, v to their owners; the event fires when this
         rank's own receive views of those heads are complete."""
         slab = self.Sl * self.D
-        dst, src = [], []
+        dst, src, lanes = [], [], []
         for t, x in enumerate(tensors):
             xp, xs = x.data_ptr(), x.stride(1)
             for r in range(self.n):
@@ -171,8 +234,9 @@ class PeerExchange:
                 for j in range(lo, hi):
                     dst.append(b + (j * self.n + self.rank) * slab * self.es)  # [head j][source rank][S/N][D] of rank r
                     src.append(xp + (r * self.hn + j) * xs * self.es)          # x[0, r * hn + j]
+                    lanes.append(r)
         with torch.cuda.stream(self.side):
-            self._copy(dst, src)
+            self._copy(dst, src, lanes=lanes)
             self.ar.barrier()
             return self.side.record_event()
 
@@ -185,14 +249,15 @@ class PeerExchange:
         o.record_stream(self.side)
         slab = self.Sl * self.D
         op = o.data_ptr()
-        dst, src = [], []
+        dst, src, lanes = [], [], []
         for r in range(self.n):
             b = self.bases[r] + self.out_off * self.es
             for j in range(o.shape[1]):
                 dst.append(b + (self.rank * self.hn + lo + j) * slab * self.es)  # out[head rank*hn+lo+j] of rank r
                 src.append(op + (j * self.S + r * self.Sl) * self.D * self.es)   # o[0, j, r*Sl:(r+1)*Sl]
+                lanes.append(r)
         with torch.cuda.stream(self.side):
             self.side.wait_event(done)
-            self._copy(dst, src)
+            self._copy(dst, src, lanes=lanes)
             self.ar.barrier()
             return self.side.record_event()

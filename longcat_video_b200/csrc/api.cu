@@ -122,6 +122,26 @@ int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, in
     return LCBSA_OK;
 }
 
+size_t lcbsa_score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D) { return lcbsa::score_keys_bytes(dtype, BH, Nq, Nk, D); }
+
+int lcbsa_score_topk_ws(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, int nsel, int cap,
+                        int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream) {
+    const size_t need = lcbsa::score_keys_bytes(dtype, BH, Nq, Nk, D);
+    if (need == 0 || !keys_ws || keys_bytes < need)  // the two-kernel form does not apply or has no room: fused form
+        return lcbsa_score_topk(q_cmp, k_cmp, dtype, BH, Nq, Nk, D, nsel, cap, idx, cnt, stream);
+    if (!q_cmp || !k_cmp || !idx || !cnt) return fail(LCBSA_EINVAL, "score_topk: null pointer");
+    if (BH < 0 || Nq < 0 || Nk <= 0) return fail(LCBSA_EINVAL, "score_topk: bad sizes");
+    if (nsel < 0 || nsel > Nk) return fail(LCBSA_EINVAL, "score_topk: nsel %d outside [0, %d]", nsel, Nk);
+    if (cap < nsel || cap < 1) return fail(LCBSA_EINVAL, "score_topk: list capacity %d below nsel %d", cap, nsel);
+    if (reinterpret_cast<uintptr_t>(q_cmp) % 16 || reinterpret_cast<uintptr_t>(k_cmp) % 16 || reinterpret_cast<uintptr_t>(keys_ws) % 16)
+        return fail(LCBSA_EINVAL, "score_topk: pooled tensors and workspace must be 16-byte aligned");
+    const char* why = "";
+    cudaError_t e = lcbsa::launch_score_gemm_topk(dtype, q_cmp, k_cmp, BH, Nq, Nk, D, nsel, cap, idx, cnt, keys_ws,
+                                                  static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) return cuda_fail(e, "score_gemm_topk", why);
+    return LCBSA_OK;
+}
+
 size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk) {
     if (!q || !k || !grid_ok(gq) || !grid_ok(gk)) return 0;
     const size_t es = elem_size(q->dtype);

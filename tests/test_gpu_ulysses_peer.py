@@ -1,6 +1,6 @@
 """Two-GPU check of the Ulysses pipeline with the peer-DMA exchange (symmetric buffers, copy engines) against the
-NCCL exchange without pipelining, around the real block-sparse attention op: the results must be identical bit for
-bit (same kernels, same data, different transport).  Skipped on a box with fewer than two GPUs.  Layout rules as in
+NCCL exchange without pipelining, around the real block-sparse attention op, and of the context-parallel op
+`flash_attn_bsa_3d_ulysses`: the results must be identical bit for bit (same arithmetic, different transport and order).  Skipped on a box with fewer than two GPUs.  Layout rules as in
 longcat_video/context_parallel/ulysses_wrapper.py:54-79 and longcat_video/modules/attention.py:60-66."""
 import os
 import socket
@@ -58,6 +58,16 @@ def _worker(rank, world, port, heads):
         assert float(want.float().abs().max()) > 0
         for o in got:
             assert torch.equal(o, want)
+        # the context-parallel op (local pooling, pooled rows exchanged first, one block-select for all local heads)
+        from longcat_video_b200.context_parallel.bsa_context_parallel import flash_attn_bsa_3d_ulysses
+
+        os.environ["LCBSA_ULYSSES_EXCHANGE"] = "peer"
+        del os.environ["LCBSA_ULYSSES_GROUP_HEADS"]
+        for _ in range(2):
+            fused = flash_attn_bsa_3d_ulysses(q, k, v, grid, sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
+            torch.cuda.synchronize()
+            assert torch.equal(fused, want)
+        L.check(L.lib().lcbsa_check_device_status())
     finally:
         dist.barrier()
         dist.destroy_process_group()
