@@ -74,6 +74,33 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
     nsel = int((1 - wl.sparsity) * ((bsa_grid[0] // wl.chunk[0]) * (bsa_grid[1] // wl.chunk[1]) * (bsa_grid[2] // wl.chunk[2])))
     flops = 4.0 * heads * (wl.sq) * nsel * (wl.chunk[0] * wl.chunk[1] * wl.chunk[2]) * wl.head_dim  # whole job
 
+    # One layer of a fixed shape is what a DiT repeats dozens of times per step: the whole call (pooling, copies,
+    # barriers, block-select, attention stages) is captured once in a CUDA graph and replayed, which takes the host out
+    # of the loop (at 8 GPUs the eager call costs the host about as much time as it costs the GPU).
+    # LCBSA_BENCH_CUDA_GRAPH=0 times the eager call instead.
+    graph, graph_note = None, "off"
+    if os.environ.get("LCBSA_BENCH_CUDA_GRAPH", "1") == "1":
+        try:
+            cap = torch.cuda.Stream()
+            cap.wait_stream(torch.cuda.current_stream())
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=cap):
+                out_graph = layer.attn(q, k, v, bsa_grid)
+            torch.cuda.current_stream().wait_stream(cap)
+            g_.replay()
+            sync()
+            if not torch.equal(out_graph, out):
+                raise RuntimeError("the replayed graph does not reproduce the eager result")
+            graph, graph_note = g_, "on"
+        except Exception as e:  # noqa: BLE001 - capture is an optimisation: fall back to the eager call
+            graph_note = f"capture failed, eager: {e!r}"[:200]
+            torch.cuda.synchronize()
+    ok_all = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)  # every rank replays, or every rank runs eagerly
+    if int(ok_all) == 0:
+        graph = None
+    stage_launches = 2 + 2 + len(_stage_list)
+
     sampler = None
     if rank == 0:
         from ..clocks import ClockSampler
@@ -84,7 +111,11 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
     sync()
     start.record()
     for _ in range(args.steps):
-        layer.attn(q, k, v, bsa_grid)
+        if graph is not None:
+            graph.replay()
+            launches["n"] += stage_launches
+        else:
+            layer.attn(q, k, v, bsa_grid)
     end.record()
     sync()
     clocks = sampler.stop() if sampler else None
@@ -145,7 +176,7 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, att
                 "config": {"workload": wl.name, "grid": list(wl.grid_k), "rank_major_grid": list(bsa_grid), "heads": heads,
                            "heads_per_gpu": heads // world, "head_dim": wl.head_dim, "block": list(wl.chunk),
                            "sparsity": wl.sparsity, "selected_blocks": nsel, "algorithmic_tflop": flops / 1e12,
-                           "ms_attention_kernels": ms_attn, "cp_split_hw": [sh, sw], "attn_sm_reserve": reserve,
+                           "ms_attention_kernels": ms_attn, "cp_split_hw": [sh, sw], "attn_sm_reserve": reserve, "cuda_graph": graph_note if graph is None else "on",
                            "l2": "inputs exceed the 126 MB L2; no flush between iterations",
                            "parallelism": f"ulysses{world} (flash_attn_bsa_3d_ulysses: pooled rows exchanged first, all-to-all in/out by peer DMA copies over NVLink, pipelined by head group)"},
                 "roofline": {"bound": "tensor", "kernel": "attn_tc_kernel", "achieved": attn_tf, "peak": peak, "unit": "TFLOP/s",

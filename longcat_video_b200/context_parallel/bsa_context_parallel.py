@@ -68,8 +68,9 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
     kc_l = B.mean_pooling_compression_3d(k, local_grid, chunk)
     pooled = main.record_event()
     side.wait_stream(main)
-    for t in (q, k, v):
-        t.record_stream(side)
+    if not torch.cuda.is_current_stream_capturing():
+        for t in (q, k, v):
+            t.record_stream(side)
     ev_pooled = ex.push_rows((qc_l, kc_l), nblk_l, pooled)
     stages = U._stages(hn, U._heads_per_group(hn))
     ev = ex.push_in((q, k, v), *stages[0])

@@ -200,7 +200,8 @@ class PeerExchange:
         for t, x in enumerate(tensors):
             if not x.is_contiguous():
                 raise ValueError("push_rows takes contiguous tensors")
-            x.record_stream(self.side)
+            if not torch.cuda.is_current_stream_capturing():
+                x.record_stream(self.side)
             xp = x.data_ptr()
             for r in range(self.n):
                 dst.append(self.bases[r] + (self.extra_off + (t * self.n + self.rank) * part) * self.es)
@@ -246,7 +247,8 @@ class PeerExchange:
     def push_out(self, o: torch.Tensor, lo: int) -> torch.cuda.Event:
         """Return the attention result ``o [1, h, S, D]`` of local heads ``lo:lo+h``: token chunk r goes to rank r."""
         done = self.main.record_event()
-        o.record_stream(self.side)
+        if not torch.cuda.is_current_stream_capturing():
+            o.record_stream(self.side)
         slab = self.Sl * self.D
         op = o.data_ptr()
         dst, src, lanes = [], [], []

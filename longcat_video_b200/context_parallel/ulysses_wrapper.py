@@ -228,8 +228,9 @@ def _peer_pipeline(func, self, query, key, value, shape, ex, stages):
     push of stage g+1 and the return of stage g-1 run on the copy engines while attention works on stage g."""
     main, side = ex.main, ex.side
     side.wait_stream(main)
-    for t in (query, key, value):
-        t.record_stream(side)
+    if not torch.cuda.is_current_stream_capturing():
+        for t in (query, key, value):
+            t.record_stream(side)
     ev = ex.push_in((query, key, value), *stages[0])
     ev_out = None
     for g, (lo, hi) in enumerate(stages):

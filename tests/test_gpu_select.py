@@ -2,8 +2,9 @@
 import pytest
 import torch
 
+from longcat_video_b200 import _lib as L
 from longcat_video_b200.block_sparse_attention import bsa_interface as B
-from longcat_video_b200.synthetic import Workload, make_qkv
+from longcat_video_b200.synthetic import WORKLOADS, Workload, make_qkv
 from oracle import bsa_oracle as O
 from tests.golden.cases import CASES
 from tests.helpers import from_bits, load_golden
@@ -141,3 +142,42 @@ def test_rejects_bad_arguments():
         B.mean_pooling_compression_3d(x[..., :100].contiguous(), (4, 4, 4), (4, 4, 4))  # 200-byte rows
     with pytest.raises(ValueError):
         B.get_select_indices(x, x, (4, 4, 4), (4, 4, 4), None, None, (4, 4, 4), (4, 4, 4))
+
+
+def _block_select(q, k, grid, chunk, nsel, ws_bytes):
+    import ctypes
+
+    qd, kd = L.tensor_desc(q), L.tensor_desc(k)
+    g = L.grid_desc(grid, chunk)
+    Nq = B.num_blocks(grid, chunk)
+    idx = torch.empty(q.shape[0], q.shape[1], Nq, max(nsel, 1), dtype=torch.int32, device=q.device)
+    cnt = torch.empty(q.shape[0], q.shape[1], Nq, dtype=torch.int32, device=q.device)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    L.check(L.lib().lcbsa_block_select(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(g), ctypes.byref(g), nsel, max(nsel, 1),
+                                       idx.data_ptr(), cnt.data_ptr(), ws.data_ptr(), ws_bytes, L.current_stream(q.device)))
+    return idx, cnt
+
+
+def test_two_kernel_form_equals_fused_form_at_full_size():
+    """At the size of the 720p configuration (1440 blocks a side; two heads) the register-tiled GEMM + row-selection
+    kernels and the fused kernel return the same lists bit for bit, and both are deterministic.  The form is chosen by
+    the size of the workspace handed to lcbsa_block_select."""
+    import ctypes
+
+    wl = WORKLOADS["720p_legal"]
+    q, k, _ = (t.cuda() for t in make_qkv(wl, heads=2))
+    nsel = B.num_selected(wl.sparsity, B.num_blocks(wl.grid_k, wl.chunk))
+    qd, kd = L.tensor_desc(q), L.tensor_desc(k)
+    g = L.grid_desc(wl.grid_k, wl.chunk)
+    small = L.lib().lcbsa_select_workspace_bytes(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(g), ctypes.byref(g))
+    big = L.lib().lcbsa_select_workspace_bytes_fast(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(g), ctypes.byref(g))
+    assert big > small > 0
+    fused = _block_select(q, k, wl.grid_k, wl.chunk, nsel, small)
+    gemm = _block_select(q, k, wl.grid_k, wl.chunk, nsel, big)
+    again = _block_select(q, k, wl.grid_k, wl.chunk, nsel, big)
+    torch.cuda.synchronize()
+    assert torch.equal(fused[0], gemm[0]) and torch.equal(fused[1], gemm[1])
+    assert torch.equal(gemm[0], again[0])
+    lists = gemm[0]
+    assert int(gemm[1].min()) == nsel == int(gemm[1].max())
+    assert bool((lists[..., 1:] > lists[..., :-1]).all()) and int(lists.min()) >= 0 and int(lists.max()) < 1440
