@@ -6,8 +6,11 @@ on more than one GPU) on synthetic tensors of the named workload.
 One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 prints ONE JSON line.
   value      effective TFLOP/s of the whole job (algorithmic flops of the selected blocks / step time),
              inputs resident in HBM;  ms_per_step is ms/layer.
-  e2e        the same metric through ``flash_attn_bsa_3d`` with HOST (pinned) inputs and output: the
-             host->device copies of q,k,v and the device->host copy of the result are inside the timing.
+  e2e        the same metric through ``flash_attn_bsa_3d_host`` with HOST (pinned) inputs and output: the
+             host->device copies of q,k,v and the device->host copy of the result are inside the timing
+             (pipelined with the kernels by chunks of four heads).
+  N > 1      ``flash_attn_bsa_3d_ulysses`` on every rank's [1, H, S/N, D] slices (longcat_video_b200/
+             context_parallel/bench_support.py), replayed from a CUDA graph captured after the warm-up.
   roofline   the attention kernel against the measured bf16 tensor peak (events around that launch);
              roofline_select does the same for the block-select stage against the measured HBM copy rate.
   cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
