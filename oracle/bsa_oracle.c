@@ -341,3 +341,54 @@ void lco_attn(const void* q, const void* k, const void* v, int dtype, int BH, co
 void lco_round_through(float* x, int64_t n, int dtype) {
     for (int64_t i = 0; i < n; ++i) x[i] = round_to(dtype, x[i]);
 }
+
+/* ---- the step before the path: q/k RMSNorm (fp32) + 3-D rotary embedding --------------------------------
+ * Restates, per row x[D] of q or k (longcat_video/modules/attention.py:116,121):
+ *   RMSNorm_FP32.forward (longcat_video/modules/blocks.py:42-53):
+ *       y = T( float(x) * rsqrt(mean(float(x)^2) + eps) );   z = T( y * weight )
+ *   RotaryPositionalEmbedding.forward (longcat_video/modules/rope_3d.py:99-120):
+ *       o = T( float(z) * cos + rotate_half(float(z)) * sin ),  rotate_half: (x1, x2) -> (-x2, x1) per pair
+ * cos/sin are the fp32 tables [S, D] the caller built from precompute_freqs_cis_3d (rope_3d.py:60-97).
+ * What the reference leaves to the library is fixed here:
+ *   the sum of squares is taken as 32 partial sums (element d goes to partial (d / (D/32)) ... i.e. partial p owns the
+ *   D/32 consecutive elements p*(D/32) .., accumulated in ascending order with fmaf) combined by the butterfly
+ *   p[i] += p[i ^ o] for o = 16, 8, 4, 2, 1; mean = sum * (1/D); rsqrt(v) = 1 / sqrtf(v) (both correctly rounded);
+ *   the two products of the rotation are rounded separately before the addition (no fused multiply-add).
+ * x: [rows, D] with row stride xs elements; cos, sin: row index = row % S; out: dense [rows, D]. */
+void lco_norm_rope(const void* x, int64_t xs, int dtype, int64_t rows, int D, int64_t S, const void* weight,
+                   const float* cos_tab, const float* sin_tab, float eps, void* out) {
+    const int per = D / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float part[32];
+        for (int p = 0; p < 32; ++p) {
+            float s = 0.f;
+            for (int e = 0; e < per; ++e) {
+                const float v = load_elem(x, dtype, r * xs + p * per + e);
+                s = fmaf(v, v, s);
+            }
+            part[p] = s;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float nxt[32];
+            for (int i = 0; i < 32; ++i) nxt[i] = part[i] + part[i ^ o];
+            memcpy(part, nxt, sizeof(part));
+        }
+        const float mean = part[0] * (1.0f / (float)D);
+        const float rinv = 1.0f / sqrtf(mean + eps);
+        const int64_t pos = r % S;
+        for (int d = 0; d < D; d += 2) {
+            float z[2];
+            for (int e = 0; e < 2; ++e) {
+                const float y = round_to(dtype, load_elem(x, dtype, r * xs + d + e) * rinv);
+                z[e] = round_to(dtype, y * load_elem(weight, dtype, d + e));
+            }
+            const float c0 = cos_tab[pos * D + d], c1 = cos_tab[pos * D + d + 1];
+            const float s0 = sin_tab[pos * D + d], s1 = sin_tab[pos * D + d + 1];
+            const float a0 = z[0] * c0, b0 = (-z[1]) * s0;
+            const float a1 = z[1] * c1, b1 = z[0] * s1;
+            store_elem(out, dtype, r * D + d, a0 + b0);
+            store_elem(out, dtype, r * D + d + 1, a1 + b1);
+        }
+    }
+}

@@ -170,3 +170,36 @@ def flash_attn_bsa_3d(q, k, v, latent_shape_q, latent_shape_k, sparsity=0.875, c
 
 if __name__ == "__main__":
     print(build(force=True))
+
+
+def rope_tables(grid_size, head_dim: int, base: float = 10000.0):
+    """fp32 ``cos, sin [T*H*W, head_dim]`` of the reference's 3-D rotary embedding
+    (``longcat_video/modules/rope_3d.py:60-97, 113-115``): the head dimension is split into a T part of
+    ``D - 4*(D//6)`` and H and W parts of ``2*(D//6)`` elements; within a part, pair i of the elements turns by
+    ``position / base**(2i/part)``; every angle is repeated for the two elements of its pair."""
+    T, H, W = grid_size
+    d_h = d_w = 2 * (head_dim // 6)
+    d_t = head_dim - d_h - d_w
+
+    def angles(n, part):
+        inv = 1.0 / (base ** (torch.arange(0, part, 2)[: part // 2].float() / part))
+        pos = torch.arange(n, dtype=torch.float32)
+        return torch.repeat_interleave(pos[:, None] * inv[None, :], 2, dim=1)  # [n, part]
+
+    at, ah, aw = angles(T, d_t), angles(H, d_h), angles(W, d_w)
+    full = torch.cat([at[:, None, None, :].expand(T, H, W, d_t), ah[None, :, None, :].expand(T, H, W, d_h),
+                      aw[None, None, :, :].expand(T, H, W, d_w)], dim=-1).reshape(T * H * W, head_dim)
+    return full.cos().contiguous(), full.sin().contiguous()
+
+
+def norm_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm (fp32) + weight + 3-D rotary embedding of ``x [B, H, S, D]`` (any strides, D contiguous); dense result."""
+    B, H, S, D = x.shape
+    assert D % 32 == 0 and x.stride(3) == 1 and cos.shape == (S, D) and sin.shape == (S, D)
+    xc = x.contiguous()
+    out = torch.empty(B, H, S, D, dtype=x.dtype)
+    w = weight.to(x.dtype).contiguous()
+    lib().lco_norm_rope(ctypes.c_void_p(xc.data_ptr()), ctypes.c_int64(D), _DTYPE_CODE[x.dtype], ctypes.c_int64(B * H * S), D,
+                        ctypes.c_int64(S), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(cos.float().contiguous().data_ptr()),
+                        ctypes.c_void_p(sin.float().contiguous().data_ptr()), ctypes.c_float(eps), ctypes.c_void_p(out.data_ptr()))
+    return out
