@@ -161,6 +161,24 @@ int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const 
 int lcbsa_set_attn_sm_reserve(int n_sms);
 
 /*
+ * The step in front of the BSA path, for q and for k (one call each): RMSNorm in fp32 over head_dim times the
+ * learned weight, then the 3-D rotary embedding, in one pass from the strided [B, H, S, D] view of the fused qkv
+ * projection into `out` (any B/H/S strides, e.g. the layout the attention or the Ulysses exchange reads).  Stands in
+ * for q_norm / k_norm followed by rope_3d in Attention.forward (longcat_video/modules/attention.py:113-121), i.e.
+ * RMSNorm_FP32.forward (longcat_video/modules/blocks.py:42-53) and RotaryPositionalEmbedding.forward
+ * (longcat_video/modules/rope_3d.py:99-120).  bf16 / fp16, head_dim 64 or 128; weight: [D] in the tensor dtype.
+ * Only T, H, W of the grid are read (the chunk fields must still be positive).
+ *
+ * rope_tab is the reference's [S, D] cos / sin tables (rope_3d.py:62-97) in the separable form they are built
+ * from, fp32, lcbsa_rope_table_floats(grid, D) floats (0 for a bad grid or odd D), with dh = 2 * (D / 6) and
+ * dt = D - 2 * dh:  cos_t [T, dt]  sin_t [T, dt]  cos_h [H, dh]  sin_h [H, dh]  cos_w [W, dh]  sin_w [W, dh],
+ * each entry repeated for the two elements of a rotation pair as in the reference's tables.
+ */
+size_t lcbsa_rope_table_floats(const LcbsaGrid* grid, int D);
+int lcbsa_norm_rope(const LcbsaTensor* x, const void* weight, const LcbsaGrid* grid, const float* rope_tab, float eps,
+                    const LcbsaTensor* out, void* stream);
+
+/*
  * Enqueue `count` device-to-device copies of `nbytes` each on `stream`: dst[i] <- src[i], one cudaMemcpyAsync per
  * slab, so the copy engines move them; a destination may be another GPU's memory mapped into this process
  * (symmetric memory, CUDA IPC).  The pointer arrays are host memory and are read before the call returns.

@@ -59,6 +59,28 @@ def test_validation_happens_before_any_launch():
     assert lib.lcbsa_score_topk(4096, 4096, L.LCBSA_BF16, 1, 4, 4, 128, 5, 5, 4096, 4096, None) == -1
 
 
+def test_norm_rope_host_side():
+    """Table size and argument checks of the q/k RMSNorm + rotary entry point run on the host."""
+    lib = L.lib()
+    g = L.grid_desc((24, 48, 80), (1, 1, 1))
+    assert lib.lcbsa_rope_table_floats(ctypes.byref(g), 128) == 2 * (24 * 44 + 48 * 42 + 80 * 42)
+    assert lib.lcbsa_rope_table_floats(ctypes.byref(g), 64) == 2 * (24 * 24 + 48 * 20 + 80 * 20)
+    assert lib.lcbsa_rope_table_floats(ctypes.byref(g), 127) == 0
+    t = L.LcbsaTensor()
+    t.data, t.dtype = 4096, L.LCBSA_BF16
+    for i, (n, s) in enumerate(zip((1, 2, 64, 128), (2 * 64 * 128, 64 * 128, 128, 1))):
+        t.size[i], t.stride[i] = n, s
+    g = L.grid_desc((4, 4, 4), (1, 1, 1))
+    assert lib.lcbsa_norm_rope(ctypes.byref(t), None, ctypes.byref(g), 4096, 1e-6, ctypes.byref(t), None) == -1
+    assert b"null weight" in lib.lcbsa_last_error()
+    bad = L.grid_desc((4, 4, 5), (1, 1, 1))
+    assert lib.lcbsa_norm_rope(ctypes.byref(t), 4096, ctypes.byref(bad), 4096, 1e-6, ctypes.byref(t), None) == -1
+    assert b"does not match the latent grid" in lib.lcbsa_last_error()
+    from longcat_video_b200.modules import norm_rope
+    with pytest.raises(RuntimeError):
+        norm_rope(torch.zeros(1, 1, 64, 128, dtype=torch.bfloat16), torch.ones(128), (4, 4, 4))
+
+
 def test_python_wrapper_refuses_cpu_tensors():
     from longcat_video_b200.block_sparse_attention import flash_attn_bsa_3d
     q = torch.zeros(1, 1, 64, 128, dtype=torch.bfloat16)
