@@ -166,7 +166,7 @@ int lcbsa_set_attn_sm_reserve(int n_sms);
  * projection into `out` (any B/H/S strides, e.g. the layout the attention or the Ulysses exchange reads).  Stands in
  * for q_norm / k_norm followed by rope_3d in Attention.forward (longcat_video/modules/attention.py:113-121), i.e.
  * RMSNorm_FP32.forward (longcat_video/modules/blocks.py:42-53) and RotaryPositionalEmbedding.forward
- * (longcat_video/modules/rope_3d.py:99-120).  bf16 / fp16, head_dim 64 or 128; weight: [D] in the tensor dtype.
+ * (longcat_video/modules/rope_3d.py:99-120).  bf16 / fp16, head_dim 64 or 128; weight: [D] in the tensor dtype, 16-byte aligned.
  * Only T, H, W of the grid are read (the chunk fields must still be positive).
  *
  * rope_tab is the reference's [S, D] cos / sin tables (rope_3d.py:62-97) in the separable form they are built

@@ -254,7 +254,8 @@ int lcbsa_norm_rope(const LcbsaTensor* x, const void* weight, const LcbsaGrid* g
     if (int rc = check_tensor("norm_rope input", x, g)) return rc;
     if (int rc = check_tensor("norm_rope output", out, g)) return rc;
     if (!weight || !rope_tab) return fail(LCBSA_EINVAL, "norm_rope: null weight or rope table");
-    if (reinterpret_cast<uintptr_t>(rope_tab) % 16 != 0) return fail(LCBSA_EINVAL, "norm_rope: rope table not 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(rope_tab) % 16 != 0 || reinterpret_cast<uintptr_t>(weight) % 16 != 0)
+        return fail(LCBSA_EINVAL, "norm_rope: weight and rope table must be 16-byte aligned");
     if (x->dtype != out->dtype) return fail(LCBSA_EINVAL, "norm_rope: input and output dtypes differ");
     for (int i = 0; i < 4; ++i)
         if (x->size[i] != out->size[i]) return fail(LCBSA_EINVAL, "norm_rope: input and output shapes differ");

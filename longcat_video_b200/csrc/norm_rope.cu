@@ -9,55 +9,77 @@
 // every input element is read once from the strided view of the fused qkv projection and every output element
 // written once.  HBM-bound: 2 bytes in + 2 bytes out per element.
 //
-// One warp per (batch, head, token) row; a lane owns D/32 consecutive elements, i.e. whole rotation pairs.
+// Half a warp per token: a lane owns D/16 consecutive elements (whole rotation pairs, one 16-byte load at
+// head_dim 128), a warp works on two neighbouring tokens and walks over a group of heads, so that the position
+// arithmetic, the angles and the weights are set up once and stay in registers, and every warp instruction of the
+// row arithmetic serves two rows (the kernel is bound by instruction issue as much as by HBM: at the HBM rate an SM
+// has about 90 issue slots per 256-byte row).
 // Arithmetic, in the order the CPU oracle fixes it: per-lane sum of squares with fmaf in ascending order, butterfly
-// over the lanes (xor 16, 8, 4, 2, 1), mean = sum / D, 1 / sqrtf(mean + eps) correctly rounded, y = T(x * r),
+// over the 16 lanes (xor 8, 4, 2, 1), mean = sum / D, 1 / sqrtf(mean + eps) correctly rounded, y = T(x * r),
 // z = T(y * w), out = T(z * cos + rot(z) * sin) with the two products rounded separately.
 //
 // The rotary angles depend on t for the first D - 4*(D/6) elements of the head dimension, on h for the next
 // 2*(D/6) and on w for the last 2*(D/6) (rope_3d.py:62-84), so the [S, D] cos/sin tables of the reference factor
-// into three small ones, [T, dt], [H, dh], [W, dw], that stay in L1.
+// into three small ones, [T, dt], [H, dh], [W, dw]; both elements of a pair have the same angle (rope_3d.py:113-115).
 #include "common.cuh"
 
 namespace lcbsa {
 
 namespace {
 
-constexpr int kRowsPerCta = 8;  // one warp per row
+constexpr int kWarps = 8;        // warps per CTA, two tokens each
+constexpr int kHeadsPerCta = 8;  // heads one warp walks over
+
+// Two values of the storage type in one 32-bit word: rounding two floats costs one packed conversion.
+template <typename T>
+struct Pair;
+template <>
+struct Pair<__nv_bfloat16> {
+    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ void unpack(uint32_t u, float& lo, float& hi) {
+        lo = __uint_as_float(u << 16);
+        hi = __uint_as_float(u & 0xffff0000u);
+    }
+};
+template <>
+struct Pair<__half> {
+    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+        const __half2 t = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ void unpack(uint32_t u, float& lo, float& hi) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+        lo = f.x;
+        hi = f.y;
+    }
+};
+
+template <int N>
+struct Vec;
+template <>
+struct Vec<8> { using type = uint4; };
+template <>
+struct Vec<4> { using type = uint2; };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kRowsPerCta * 32) norm_rope_kernel(View x, int H, int S, int Tg, int Hg, int Wg, const T* __restrict__ weight,
-                                                                    const float* __restrict__ tab, float eps, T* __restrict__ out,
-                                                                    long long osb, long long osh, long long oss, long long rows) {
-    constexpr int PER = D / 32;
-    static_assert(PER >= 2 && PER % 2 == 0, "a lane owns whole rotation pairs");
+__global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, int S, int Tg, int Hg, int Wg, const T* __restrict__ weight,
+                                                               const float* __restrict__ tab, float eps, T* out, long long osb,
+                                                               long long osh, long long oss) {
+    constexpr int PER = D / 16;
+    static_assert(PER == 4 || PER == 8, "a lane owns 8 or 16 bytes");
+    using V = typename Vec<PER>::type;
     constexpr int DH = 2 * (D / 6), DW = DH, DT = D - DH - DW;
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int s = (int)(row % S);
-    const long long bh = row / S;
-    const int h = (int)(bh % H), b = (int)(bh / H);
+    const int lane = threadIdx.x & 31, sub = lane & 15;
+    const long long first = ((long long)blockIdx.x * kWarps + (threadIdx.x >> 5)) * 2;  // the warp's first token
+    if (first >= S) return;
+    const bool live = first + (lane >> 4) < S;  // an odd S leaves the last warp's upper half without a token
+    const int s = live ? (int)(first + (lane >> 4)) : S - 1;
+    const int b = blockIdx.z;
+    const int h0 = blockIdx.y * kHeadsPerCta, h1 = min(H, h0 + kHeadsPerCta);
     const int w_pos = s % Wg, h_pos = (s / Wg) % Hg, t_pos = s / (Wg * Hg);
-
-    const T* src = reinterpret_cast<const T*>(x.data) + (long long)b * x.sb + (long long)h * x.sh + (long long)s * x.ss + lane * PER;
-    float v[PER];
-    if (PER == 4) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src));
-        const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-        for (int i = 0; i < PER; ++i) v[i] = DType<T>::to_f32(e[i]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < PER; ++i) v[i] = DType<T>::to_f32(src[i]);
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
-    const float mean = __fmul_rn(ss, 1.0f / (float)D);
-    const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 
     // table layout: cos_t [T, DT] sin_t [T, DT] cos_h [H, DH] sin_h [H, DH] cos_w [W, DW] sin_w [W, DW]
     const float* cos_t = tab;
@@ -66,46 +88,69 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) norm_rope_kernel(View x, int
     const float* sin_h = cos_h + (long long)Hg * DH;
     const float* cos_w = sin_h + (long long)Hg * DH;
     const float* sin_w = cos_w + (long long)Wg * DW;
-
-    T res[PER];
+    float cs[PER / 2], sn[PER / 2], wt[PER];
 #pragma unroll
-    for (int i = 0; i < PER; i += 2) {
-        const int d = lane * PER + i;  // even: d and d + 1 are one rotation pair and lie in the same part
-        float c0, c1, s0, s1;
+    for (int p = 0; p < PER / 2; ++p) {
+        const int d = sub * PER + 2 * p;  // even: d and d + 1 are one rotation pair and lie in the same part
+        const float *c, *n;
         if (d < DT) {
-            c0 = cos_t[t_pos * DT + d]; c1 = cos_t[t_pos * DT + d + 1];
-            s0 = sin_t[t_pos * DT + d]; s1 = sin_t[t_pos * DT + d + 1];
+            c = cos_t + t_pos * DT + d; n = sin_t + t_pos * DT + d;
         } else if (d < DT + DH) {
-            c0 = cos_h[h_pos * DH + d - DT]; c1 = cos_h[h_pos * DH + d - DT + 1];
-            s0 = sin_h[h_pos * DH + d - DT]; s1 = sin_h[h_pos * DH + d - DT + 1];
+            c = cos_h + h_pos * DH + (d - DT); n = sin_h + h_pos * DH + (d - DT);
         } else {
-            c0 = cos_w[w_pos * DW + d - DT - DH]; c1 = cos_w[w_pos * DW + d - DT - DH + 1];
-            s0 = sin_w[w_pos * DW + d - DT - DH]; s1 = sin_w[w_pos * DW + d - DT - DH + 1];
+            c = cos_w + w_pos * DW + (d - DT - DH); n = sin_w + w_pos * DW + (d - DT - DH);
         }
-        const float y0 = DType<T>::to_f32(DType<T>::from_f32(__fmul_rn(v[i], rinv)));
-        const float y1 = DType<T>::to_f32(DType<T>::from_f32(__fmul_rn(v[i + 1], rinv)));
-        const float z0 = DType<T>::to_f32(DType<T>::from_f32(__fmul_rn(y0, DType<T>::to_f32(weight[d]))));
-        const float z1 = DType<T>::to_f32(DType<T>::from_f32(__fmul_rn(y1, DType<T>::to_f32(weight[d + 1]))));
-        res[i] = DType<T>::from_f32(__fadd_rn(__fmul_rn(z0, c0), __fmul_rn(-z1, s0)));
-        res[i + 1] = DType<T>::from_f32(__fadd_rn(__fmul_rn(z1, c1), __fmul_rn(z0, s1)));
+        cs[p] = __ldg(c);
+        sn[p] = __ldg(n);
     }
-    T* dst = out + (long long)b * osb + (long long)h * osh + (long long)s * oss + lane * PER;
-    if (PER == 4) {
-        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(res);
-    } else {
+    {
+        const V raw = __ldg(reinterpret_cast<const V*>(weight + sub * PER));
+        const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-        for (int i = 0; i < PER; ++i) dst[i] = res[i];
+        for (int i = 0; i < PER; ++i) wt[i] = DType<T>::to_f32(e[i]);
+    }
+
+    const T* src = reinterpret_cast<const T*>(x.data) + (long long)b * x.sb + (long long)s * x.ss + sub * PER;
+    T* dst = out + (long long)b * osb + (long long)s * oss + sub * PER;
+    V cur = *reinterpret_cast<const V*>(src + (long long)h0 * x.sh);
+#pragma unroll 1
+    for (int h = h0; h < h1; ++h) {
+        V nxt = cur;
+        if (h + 1 < h1) nxt = *reinterpret_cast<const V*>(src + (long long)(h + 1) * x.sh);  // in flight during the arithmetic
+        const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cur);
+        float v[PER];
+#pragma unroll
+        for (int p = 0; p < PER / 2; ++p) Pair<T>::unpack(cw[p], v[2 * p], v[2 * p + 1]);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        const float mean = __fmul_rn(ss, 1.0f / (float)D);
+        const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+        V res;
+        uint32_t* rw = reinterpret_cast<uint32_t*>(&res);
+#pragma unroll
+        for (int p = 0; p < PER / 2; ++p) {
+            const int i = 2 * p;
+            float y0, y1, z0, z1;
+            Pair<T>::unpack(Pair<T>::pack(__fmul_rn(v[i], rinv), __fmul_rn(v[i + 1], rinv)), y0, y1);
+            Pair<T>::unpack(Pair<T>::pack(__fmul_rn(y0, wt[i]), __fmul_rn(y1, wt[i + 1])), z0, z1);
+            rw[p] = Pair<T>::pack(__fadd_rn(__fmul_rn(z0, cs[p]), __fmul_rn(-z1, sn[p])),
+                                  __fadd_rn(__fmul_rn(z1, cs[p]), __fmul_rn(z0, sn[p])));
+        }
+        if (live) *reinterpret_cast<V*>(dst + (long long)h * osh) = res;
+        cur = nxt;
     }
 }
 
 template <typename T, int D>
 cudaError_t run(const View& x, int B, int H, int S, int Tg, int Hg, int Wg, const void* weight, const float* tab, float eps, void* out,
                 long long osb, long long osh, long long oss, cudaStream_t st) {
-    const long long rows = (long long)B * H * S;
-    if (rows == 0) return cudaSuccess;
-    const long long grid = (rows + kRowsPerCta - 1) / kRowsPerCta;
-    norm_rope_kernel<T, D><<<(unsigned)grid, kRowsPerCta * 32, 0, st>>>(x, H, S, Tg, Hg, Wg, reinterpret_cast<const T*>(weight), tab, eps,
-                                                                       reinterpret_cast<T*>(out), osb, osh, oss, rows);
+    if ((long long)B * H * S == 0) return cudaSuccess;
+    dim3 grid((unsigned)((S + 2 * kWarps - 1) / (2 * kWarps)), (unsigned)((H + kHeadsPerCta - 1) / kHeadsPerCta), (unsigned)B);
+    norm_rope_kernel<T, D><<<grid, kWarps * 32, 0, st>>>(x, H, S, Tg, Hg, Wg, reinterpret_cast<const T*>(weight), tab, eps,
+                                                        reinterpret_cast<T*>(out), osb, osh, oss);
     return cudaGetLastError();
 }
 
@@ -121,6 +166,10 @@ cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int 
                              const char** why) {
     if (dtype == LCBSA_FP32 || (D != 64 && D != 128)) {
         *why = "norm_rope takes bf16 or fp16 with head_dim 64 or 128";
+        return cudaErrorInvalidValue;
+    }
+    if (B > 65535) {
+        *why = "norm_rope: batch above 65535";
         return cudaErrorInvalidValue;
     }
     if (dtype == LCBSA_BF16)

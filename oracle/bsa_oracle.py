@@ -195,7 +195,7 @@ def rope_tables(grid_size, head_dim: int, base: float = 10000.0):
 def norm_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     """RMSNorm (fp32) + weight + 3-D rotary embedding of ``x [B, H, S, D]`` (any strides, D contiguous); dense result."""
     B, H, S, D = x.shape
-    assert D % 32 == 0 and x.stride(3) == 1 and cos.shape == (S, D) and sin.shape == (S, D)
+    assert D % 16 == 0 and x.stride(3) == 1 and cos.shape == (S, D) and sin.shape == (S, D)
     xc = x.contiguous()
     out = torch.empty(B, H, S, D, dtype=x.dtype)
     w = weight.to(x.dtype).contiguous()
