@@ -9,14 +9,16 @@
 // every input element is read once from the strided view of the fused qkv projection and every output element
 // written once.  HBM-bound: 2 bytes in + 2 bytes out per element.
 //
-// Half a warp per token: a lane owns D/16 consecutive elements (whole rotation pairs, one 16-byte load at
-// head_dim 128), a warp works on two neighbouring tokens and walks over a group of heads, so that the position
+// Eight lanes per token: a lane owns D/8 consecutive elements (whole rotation pairs, two 16-byte loads at
+// head_dim 128), a warp works on four neighbouring tokens and walks over a group of heads, so that the position
 // arithmetic, the angles and the weights are set up once and stay in registers, and every warp instruction of the
-// row arithmetic serves two rows (the kernel is bound by instruction issue as much as by HBM: at the HBM rate an SM
-// has about 90 issue slots per 256-byte row).
+// row arithmetic serves four rows (the kernel is bound by instruction issue as much as by HBM: at the HBM rate an
+// SM has about 90 issue slots per 256-byte row).
 // Arithmetic, in the order the CPU oracle fixes it: per-lane sum of squares with fmaf in ascending order, butterfly
-// over the 16 lanes (xor 8, 4, 2, 1), mean = sum / D, 1 / sqrtf(mean + eps) correctly rounded, y = T(x * r),
-// z = T(y * w), out = T(z * cos + rot(z) * sin) with the two products rounded separately.
+// over the 8 lanes (xor 4, 2, 1), mean = sum / D, 1 / sqrtf(mean + eps) correctly rounded, y = T(x * r),
+// z = T(y * w) (one packed multiply in the storage type: the product of two 8- or 11-bit significands is exact in
+// fp32, so rounding it once is the same thing), out = T(z * cos + rot(z) * sin) with the two products rounded
+// separately.
 //
 // The rotary angles depend on t for the first D - 4*(D/6) elements of the head dimension, on h for the next
 // 2*(D/6) and on w for the last 2*(D/6) (rope_3d.py:62-84), so the [S, D] cos/sin tables of the reference factor
@@ -27,8 +29,9 @@ namespace lcbsa {
 
 namespace {
 
-constexpr int kWarps = 8;        // warps per CTA, two tokens each
-constexpr int kHeadsPerCta = 8;  // heads one warp walks over
+constexpr int kWarps = 8;         // warps per CTA, four tokens each
+constexpr int kTokens = 4;        // tokens per warp: eight lanes each
+constexpr int kHeadsPerCta = 16;  // heads one warp walks over
 
 // Two values of the storage type in one 32-bit word: rounding two floats costs one packed conversion.
 template <typename T>
@@ -43,6 +46,10 @@ struct Pair<__nv_bfloat16> {
         lo = __uint_as_float(u << 16);
         hi = __uint_as_float(u & 0xffff0000u);
     }
+    __device__ static __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {  // round(a * b) per half, one rounding
+        const __nv_bfloat162 t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
 };
 template <>
 struct Pair<__half> {
@@ -55,28 +62,26 @@ struct Pair<__half> {
         lo = f.x;
         hi = f.y;
     }
+    __device__ static __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+        const __half2 t = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
 };
-
-template <int N>
-struct Vec;
-template <>
-struct Vec<8> { using type = uint4; };
-template <>
-struct Vec<4> { using type = uint2; };
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, int S, int Tg, int Hg, int Wg, const T* __restrict__ weight,
                                                                const float* __restrict__ tab, float eps, T* out, long long osb,
                                                                long long osh, long long oss) {
-    constexpr int PER = D / 16;
-    static_assert(PER == 4 || PER == 8, "a lane owns 8 or 16 bytes");
-    using V = typename Vec<PER>::type;
+    constexpr int PER = D / 8;   // elements per lane: 16 or 8
+    constexpr int NV = PER / 8;  // 16-byte vectors per lane
+    constexpr int NP = PER / 2;  // rotation pairs per lane
+    static_assert(PER == 8 || PER == 16, "a lane owns one or two 16-byte vectors");
     constexpr int DH = 2 * (D / 6), DW = DH, DT = D - DH - DW;
-    const int lane = threadIdx.x & 31, sub = lane & 15;
-    const long long first = ((long long)blockIdx.x * kWarps + (threadIdx.x >> 5)) * 2;  // the warp's first token
+    const int lane = threadIdx.x & 31, sub = lane & 7, tok = lane >> 3;
+    const long long first = ((long long)blockIdx.x * kWarps + (threadIdx.x >> 5)) * kTokens;  // the warp's first token
     if (first >= S) return;
-    const bool live = first + (lane >> 4) < S;  // an odd S leaves the last warp's upper half without a token
-    const int s = live ? (int)(first + (lane >> 4)) : S - 1;
+    const bool live = first + tok < S;  // the last warp may have fewer than four tokens
+    const int s = live ? (int)(first + tok) : S - 1;
     const int b = blockIdx.z;
     const int h0 = blockIdx.y * kHeadsPerCta, h1 = min(H, h0 + kHeadsPerCta);
     const int w_pos = s % Wg, h_pos = (s / Wg) % Hg, t_pos = s / (Wg * Hg);
@@ -88,9 +93,9 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
     const float* sin_h = cos_h + (long long)Hg * DH;
     const float* cos_w = sin_h + (long long)Hg * DH;
     const float* sin_w = cos_w + (long long)Wg * DW;
-    float cs[PER / 2], sn[PER / 2], wt[PER];
+    float cs[NP], sn[NP];
 #pragma unroll
-    for (int p = 0; p < PER / 2; ++p) {
+    for (int p = 0; p < NP; ++p) {
         const int d = sub * PER + 2 * p;  // even: d and d + 1 are one rotation pair and lie in the same part
         const float *c, *n;
         if (d < DT) {
@@ -103,44 +108,51 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
         cs[p] = __ldg(c);
         sn[p] = __ldg(n);
     }
-    {
-        const V raw = __ldg(reinterpret_cast<const V*>(weight + sub * PER));
-        const T* e = reinterpret_cast<const T*>(&raw);
+    uint4 wv[NV];  // the lane's weights, packed as they are stored
 #pragma unroll
-        for (int i = 0; i < PER; ++i) wt[i] = DType<T>::to_f32(e[i]);
-    }
+    for (int j = 0; j < NV; ++j) wv[j] = __ldg(reinterpret_cast<const uint4*>(weight + sub * PER) + j);
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(wv);
 
-    const T* src = reinterpret_cast<const T*>(x.data) + (long long)b * x.sb + (long long)s * x.ss + sub * PER;
-    T* dst = out + (long long)b * osb + (long long)s * oss + sub * PER;
-    V cur = *reinterpret_cast<const V*>(src + (long long)h0 * x.sh);
+    const T* sp = reinterpret_cast<const T*>(x.data) + (long long)b * x.sb + (long long)s * x.ss + (long long)h0 * x.sh + sub * PER;
+    T* dp = out + (long long)b * osb + (long long)s * oss + (long long)h0 * osh + sub * PER;
+    uint4 cur[NV], nxt[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) cur[j] = reinterpret_cast<const uint4*>(sp)[j];
 #pragma unroll 1
     for (int h = h0; h < h1; ++h) {
-        V nxt = cur;
-        if (h + 1 < h1) nxt = *reinterpret_cast<const V*>(src + (long long)(h + 1) * x.sh);  // in flight during the arithmetic
-        const uint32_t* cw = reinterpret_cast<const uint32_t*>(&cur);
+        sp += x.sh;
+        if (h + 1 < h1) {  // the next head's row is in flight during the arithmetic
+#pragma unroll
+            for (int j = 0; j < NV; ++j) nxt[j] = reinterpret_cast<const uint4*>(sp)[j];
+        }
+        const uint32_t* cw = reinterpret_cast<const uint32_t*>(cur);
         float v[PER];
 #pragma unroll
-        for (int p = 0; p < PER / 2; ++p) Pair<T>::unpack(cw[p], v[2 * p], v[2 * p + 1]);
+        for (int p = 0; p < NP; ++p) Pair<T>::unpack(cw[p], v[2 * p], v[2 * p + 1]);
         float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        for (int o = 4; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
         const float mean = __fmul_rn(ss, 1.0f / (float)D);
         const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-        V res;
-        uint32_t* rw = reinterpret_cast<uint32_t*>(&res);
+        uint4 res[NV];
+        uint32_t* rw = reinterpret_cast<uint32_t*>(res);
 #pragma unroll
-        for (int p = 0; p < PER / 2; ++p) {
-            const int i = 2 * p;
-            float y0, y1, z0, z1;
-            Pair<T>::unpack(Pair<T>::pack(__fmul_rn(v[i], rinv), __fmul_rn(v[i + 1], rinv)), y0, y1);
-            Pair<T>::unpack(Pair<T>::pack(__fmul_rn(y0, wt[i]), __fmul_rn(y1, wt[i + 1])), z0, z1);
+        for (int p = 0; p < NP; ++p) {
+            const uint32_t y = Pair<T>::pack(__fmul_rn(v[2 * p], rinv), __fmul_rn(v[2 * p + 1], rinv));
+            float z0, z1;
+            Pair<T>::unpack(Pair<T>::mul(y, wp[p]), z0, z1);
             rw[p] = Pair<T>::pack(__fadd_rn(__fmul_rn(z0, cs[p]), __fmul_rn(-z1, sn[p])),
                                   __fadd_rn(__fmul_rn(z1, cs[p]), __fmul_rn(z0, sn[p])));
         }
-        if (live) *reinterpret_cast<V*>(dst + (long long)h * osh) = res;
-        cur = nxt;
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) reinterpret_cast<uint4*>(dp)[j] = res[j];
+        }
+        dp += osh;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) cur[j] = nxt[j];
     }
 }
 
@@ -148,7 +160,7 @@ template <typename T, int D>
 cudaError_t run(const View& x, int B, int H, int S, int Tg, int Hg, int Wg, const void* weight, const float* tab, float eps, void* out,
                 long long osb, long long osh, long long oss, cudaStream_t st) {
     if ((long long)B * H * S == 0) return cudaSuccess;
-    dim3 grid((unsigned)((S + 2 * kWarps - 1) / (2 * kWarps)), (unsigned)((H + kHeadsPerCta - 1) / kHeadsPerCta), (unsigned)B);
+    dim3 grid((unsigned)((S + kTokens * kWarps - 1) / (kTokens * kWarps)), (unsigned)((H + kHeadsPerCta - 1) / kHeadsPerCta), (unsigned)B);
     norm_rope_kernel<T, D><<<grid, kWarps * 32, 0, st>>>(x, H, S, Tg, Hg, Wg, reinterpret_cast<const T*>(weight), tab, eps,
                                                         reinterpret_cast<T*>(out), osb, osh, oss);
     return cudaGetLastError();

@@ -350,18 +350,18 @@ void lco_round_through(float* x, int64_t n, int dtype) {
  *       o = T( float(z) * cos + rotate_half(float(z)) * sin ),  rotate_half: (x1, x2) -> (-x2, x1) per pair
  * cos/sin are the fp32 tables [S, D] the caller built from precompute_freqs_cis_3d (rope_3d.py:60-97).
  * What the reference leaves to the library is fixed here:
- *   the sum of squares is taken as 16 partial sums (partial p owns the D/16 consecutive elements p*(D/16) ..,
+ *   the sum of squares is taken as 8 partial sums (partial p owns the D/8 consecutive elements p*(D/8) ..,
  *   accumulated in ascending order with fmaf) combined by the butterfly
- *   p[i] += p[i ^ o] for o = 8, 4, 2, 1; mean = sum * (1/D); rsqrt(v) = 1 / sqrtf(v) (both correctly rounded);
+ *   p[i] += p[i ^ o] for o = 4, 2, 1; mean = sum * (1/D); rsqrt(v) = 1 / sqrtf(v) (both correctly rounded);
  *   the two products of the rotation are rounded separately before the addition (no fused multiply-add).
  * x: [rows, D] with row stride xs elements; cos, sin: row index = row % S; out: dense [rows, D]. */
 void lco_norm_rope(const void* x, int64_t xs, int dtype, int64_t rows, int D, int64_t S, const void* weight,
                    const float* cos_tab, const float* sin_tab, float eps, void* out) {
-    const int per = D / 16;
+    const int per = D / 8;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; ++r) {
-        float part[16];
-        for (int p = 0; p < 16; ++p) {
+        float part[8];
+        for (int p = 0; p < 8; ++p) {
             float s = 0.f;
             for (int e = 0; e < per; ++e) {
                 const float v = load_elem(x, dtype, r * xs + p * per + e);
@@ -369,9 +369,9 @@ void lco_norm_rope(const void* x, int64_t xs, int dtype, int64_t rows, int D, in
             }
             part[p] = s;
         }
-        for (int o = 8; o > 0; o >>= 1) {
-            float nxt[16];
-            for (int i = 0; i < 16; ++i) nxt[i] = part[i] + part[i ^ o];
+        for (int o = 4; o > 0; o >>= 1) {
+            float nxt[8];
+            for (int i = 0; i < 8; ++i) nxt[i] = part[i] + part[i ^ o];
             memcpy(part, nxt, sizeof(part));
         }
         const float mean = part[0] * (1.0f / (float)D);
