@@ -268,6 +268,100 @@ void lco_topk(const void* score, int dtype, int BH, int Nq, int Nk, int nsel, in
     }
 }
 
+/* ---------------------------------------------------------------- CDF-threshold selection */
+
+/* exp(t) for t <= 0 from fp32 operations whose results do not depend on the machine (fmaf, rintf, one scaling by a
+ * power of two), so that a GPU kernel written with the same operations returns the same bits: n = rint(t * log2 e),
+ * r = t - n ln 2 in two fmaf steps, the degree-7 Taylor polynomial in Horner form, times 2^n.  Below -87: 0. */
+static inline float lco_exp(float t) {
+    if (!(t >= -87.0f)) return 0.0f;
+    const float n = rintf(t * 1.44269504f);
+    float r = fmaf(-n, 0.693145751953125f, t);
+    r = fmaf(-n, 1.42860677e-6f, r);
+    float p = 1.0f / 5040.0f;
+    p = fmaf(p, r, 1.0f / 720.0f);
+    p = fmaf(p, r, 1.0f / 120.0f);
+    p = fmaf(p, r, 1.0f / 24.0f);
+    p = fmaf(p, r, 1.0f / 6.0f);
+    p = fmaf(p, r, 0.5f);
+    p = fmaf(p, r, 1.0f);
+    p = fmaf(p, r, 1.0f);
+    const uint32_t bits = (uint32_t)((int)n + 127) << 23; /* 2^n, n in [-126, 0] */
+    float scale;
+    memcpy(&scale, &bits, 4);
+    return p * scale;
+}
+
+static int cmp_u32_desc(const void* a, const void* b) {
+    const uint32_t x = *(const uint32_t*)a, y = *(const uint32_t*)b;
+    return x > y ? -1 : (x < y ? 1 : 0);
+}
+
+/*
+ * The cdf_threshold selectors (longcat_video/block_sparse_attention/bsa_interface.py:234-244 and :253-266):
+ *   weights = softmax(score * sm_scale) in the score dtype (fp32 inside), sorted in descending order,
+ *   cdf = cumsum(sorted weights) (fp32 running sum, every entry rounded to the dtype),
+ *   count = number of entries with cdf <= threshold (searchsorted, right=True), raised to nsel_min for the combined
+ *   "max(cdf, topk)" selector; the list is the whole sorted index row, of which the first `count` entries are used.
+ * What the reference leaves to the library is fixed here: exp is lco_exp; the softmax denominator is summed as 256
+ * partial sums (partial t takes entries t, t + 256, ... in ascending order) combined by a butterfly over each group
+ * of 32 (xor 16, 8, 4, 2, 1) and then over the 8 group sums (xor 4, 2, 1); equal weights are ordered by ascending
+ * index (torch.sort leaves the order of ties open); the comparison with the threshold is done in fp32.
+ * score: [rows, Nk] in dtype (bf16 / fp16); idx: [rows, Nk]; cnt: [rows].
+ */
+void lco_cdf_select(const void* score, int dtype, int64_t rows, int Nk, float sm_scale, float threshold, int nsel_min,
+                    int32_t* idx, int32_t* cnt) {
+#pragma omp parallel
+    {
+        float* e = (float*)malloc(sizeof(float) * (size_t)(Nk > 0 ? Nk : 1));
+        uint32_t* key = (uint32_t*)malloc(sizeof(uint32_t) * (size_t)(Nk > 0 ? Nk : 1));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            float m = -INFINITY;
+            for (int j = 0; j < Nk; ++j) {
+                e[j] = round_to(dtype, load_elem(score, dtype, r * Nk + j) * sm_scale);
+                if (e[j] > m) m = e[j];
+            }
+            float part[256];
+            for (int t = 0; t < 256; ++t) part[t] = 0.0f;
+            for (int j = 0; j < Nk; ++j) {
+                e[j] = lco_exp(e[j] - m);
+                part[j & 255] += e[j];
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                float nxt[256];
+                for (int t = 0; t < 256; ++t) nxt[t] = part[t] + part[t ^ o];
+                memcpy(part, nxt, sizeof(part));
+            }
+            float grp[8];
+            for (int g = 0; g < 8; ++g) grp[g] = part[32 * g];
+            for (int o = 4; o > 0; o >>= 1) {
+                float nxt[8];
+                for (int g = 0; g < 8; ++g) nxt[g] = grp[g] + grp[g ^ o];
+                memcpy(grp, nxt, sizeof(grp));
+            }
+            const float sum = grp[0];
+            for (int j = 0; j < Nk; ++j) {
+                const float w = e[j] / sum;
+                uint32_t wb = dtype == LCO_BF16 ? f32_to_bf16(w) : f32_to_fp16(w);
+                key[j] = (wb << 16) | (uint32_t)(0xffff - j);
+            }
+            qsort(key, (size_t)Nk, sizeof(uint32_t), cmp_u32_desc);
+            float acc = 0.0f;
+            int n = 0, open = 1;
+            for (int j = 0; j < Nk; ++j) {
+                idx[r * Nk + j] = (int32_t)(0xffff - (key[j] & 0xffffu));
+                const uint16_t wb = (uint16_t)(key[j] >> 16);
+                acc += dtype == LCO_BF16 ? bf16_to_f32(wb) : fp16_to_f32(wb);
+                if (open && round_to(dtype, acc) <= threshold) ++n; else open = 0;
+            }
+            cnt[r] = n > nsel_min ? n : nsel_min;
+        }
+        free(e);
+        free(key);
+    }
+}
+
 /* ---------------------------------------------------------------- attention */
 
 /*

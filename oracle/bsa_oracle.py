@@ -125,6 +125,21 @@ def topk(score_: torch.Tensor, nsel: int, cap: Optional[int] = None
     return idx, cnt, ties
 
 
+def cdf_select(score_: torch.Tensor, cdf_threshold: float, sm_scale: float, nsel_min: int = 0
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The cdf_threshold selectors of bsa_interface.py:234-266 on bf16 / fp16 scores ``[B,H,Nq,Nk]``: returns the whole
+    index row sorted by descending softmax weight (int32 ``[B,H,Nq,Nk]``; ties by ascending index) and the number of
+    leading entries to use (int32 ``[B,H,Nq]``), at least ``nsel_min`` (the combined "max(cdf, topk)" selector)."""
+    B, H, Nq, Nk = score_.shape
+    assert score_.dtype in (torch.bfloat16, torch.float16) and 0 < Nk < 65535
+    score_ = score_.contiguous()
+    idx = torch.empty(B, H, Nq, Nk, dtype=torch.int32)
+    cnt = torch.empty(B, H, Nq, dtype=torch.int32)
+    lib().lco_cdf_select(_ptr(score_), _DTYPE_CODE[score_.dtype], ctypes.c_int64(B * H * Nq), Nk, ctypes.c_float(sm_scale),
+                         ctypes.c_float(cdf_threshold), int(nsel_min), _ptr(idx), _ptr(cnt))
+    return idx, cnt
+
+
 def block_select(q, k, latent_shape_q, latent_shape_k, sparsity, chunk_q, chunk_k, cap=None):
     """pool -> score -> top-k (the ``sparsity``-only branch of bsa_interface.py:268-277)."""
     qc = pool(q, latent_shape_q, chunk_q)
