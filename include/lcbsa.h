@@ -161,6 +161,19 @@ int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const 
 int lcbsa_set_attn_sm_reserve(int n_sms);
 
 /*
+ * The cdf_threshold selectors: get_select_indices_cdf and get_select_indices_cdf_topk
+ * (longcat_video/block_sparse_attention/bsa_interface.py:226-266) on pooled rows q_cmp [BH, Nq, D], k_cmp [BH, Nk, D]
+ * (bf16 / fp16, head_dim 64 or 128, Nk <= 4096).  Per row of block scores: weights = softmax(score * sm_scale) in the
+ * input dtype, the whole row sorted by descending weight (equal weights by ascending index; torch.sort leaves that
+ * open), cdf = running sum of the sorted weights rounded to the dtype, count = number of entries with
+ * cdf <= cdf_threshold, raised to nsel_min (0 for the cdf selector, int((1 - sparsity) * Nk) for the combined one).
+ * idx: int32 [BH, Nq, Nk], the sorted index rows (the reference returns them as int64); cnt: int32 [BH, Nq]; both go to
+ * lcbsa_attn_fwd with cap = Nk.  keys_ws: lcbsa_score_keys_bytes(...) bytes of scratch.
+ */
+int lcbsa_score_cdf(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, float sm_scale, float cdf_threshold,
+                    int nsel_min, int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream);
+
+/*
  * The step in front of the BSA path, for q and for k (one call each): RMSNorm in fp32 over head_dim times the
  * learned weight, then the 3-D rotary embedding, in one pass from the strided [B, H, S, D] view of the fused qkv
  * projection into `out` (any B/H/S strides, e.g. the layout the attention or the Ulysses exchange reads).  Stands in

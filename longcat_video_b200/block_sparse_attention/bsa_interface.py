@@ -58,14 +58,16 @@ def mean_pooling_compression_3d(x: torch.Tensor, latent_shape, chunk_3d_shape) -
 
 def get_select_indices_from_pooled(q_cmp: torch.Tensor, k_cmp: torch.Tensor, sparsity: float,
                                    cdf_threshold: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Top-k block lists from pooled tensors: int32 ``idx [B,H,Nq,nsel]`` (ascending) and ``lens [B,H,Nq]``."""
-    if cdf_threshold is not None:
-        raise NotImplementedError("cdf_threshold selection is not built; use sparsity only")
-    if sparsity is None:
+    """Block lists from pooled tensors, the three branches of ``get_select_indices`` (bsa_interface.py:268-277):
+    ``sparsity`` only: int32 ``idx [B,H,Nq,nsel]`` (ascending) and ``lens [B,H,Nq]``; with ``cdf_threshold``: the whole
+    index row sorted by descending softmax weight, ``idx [B,H,Nq,Nk]``, and the number of leading entries to use."""
+    if sparsity is None and cdf_threshold is None:
         raise ValueError
     q_cmp, k_cmp = q_cmp.contiguous(), k_cmp.contiguous()
     B, H, Nq, D = q_cmp.shape
     Nk = k_cmp.shape[2]
+    if cdf_threshold is not None:
+        return _select_cdf(q_cmp, k_cmp, float(cdf_threshold), 0 if sparsity is None else num_selected(sparsity, Nk))
     nsel = num_selected(sparsity, Nk)
     cap = max(nsel, 1)
     idx = torch.empty(B, H, Nq, cap, dtype=torch.int32, device=q_cmp.device)
@@ -80,6 +82,23 @@ def get_select_indices_from_pooled(q_cmp: torch.Tensor, k_cmp: torch.Tensor, spa
     return idx, cnt
 
 
+def _select_cdf(q_cmp: torch.Tensor, k_cmp: torch.Tensor, cdf_threshold: float, nsel_min: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """get_select_indices_cdf / get_select_indices_cdf_topk (bsa_interface.py:226-266) in two launches: scores, then one
+    CTA per row for softmax, sort, running sum and count."""
+    B, H, Nq, D = q_cmp.shape
+    Nk = k_cmp.shape[2]
+    dt = L.dtype_code(q_cmp.dtype)
+    idx = torch.empty(B, H, Nq, Nk, dtype=torch.int32, device=q_cmp.device)
+    cnt = torch.empty(B, H, Nq, dtype=torch.int32, device=q_cmp.device)
+    keys_bytes = L.lib().lcbsa_score_keys_bytes(dt, B * H, Nq, Nk, D)
+    ws = torch.empty(max(keys_bytes, 16), dtype=torch.uint8, device=q_cmp.device)
+    with torch.cuda.device(q_cmp.device):
+        L.check(L.lib().lcbsa_score_cdf(q_cmp.data_ptr(), k_cmp.data_ptr(), dt, B * H, Nq, Nk, D, ctypes.c_float(1 / D ** 0.5),
+                                        ctypes.c_float(cdf_threshold), int(nsel_min), idx.data_ptr(), cnt.data_ptr(),
+                                        ws.data_ptr(), keys_bytes, L.current_stream(q_cmp.device)))
+    return idx, cnt
+
+
 def get_select_indices(q: torch.Tensor, k: torch.Tensor, latent_shape_q, latent_shape_k, sparsity,
                        cdf_threshold=None, chunk_3d_shape_q=(4, 4, 8), chunk_3d_shape_k=(4, 4, 8)
                        ) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -87,7 +106,8 @@ def get_select_indices(q: torch.Tensor, k: torch.Tensor, latent_shape_q, latent_
     if sparsity is None and cdf_threshold is None:
         raise ValueError
     if cdf_threshold is not None:
-        raise NotImplementedError("cdf_threshold selection is not built; use sparsity only")
+        return get_select_indices_from_pooled(mean_pooling_compression_3d(q, latent_shape_q, chunk_3d_shape_q),
+                                              mean_pooling_compression_3d(k, latent_shape_k, chunk_3d_shape_k), sparsity, cdf_threshold)
     q, k = _as_abi(q), _as_abi(k)
     B, H, _, D = q.shape
     gq, gk = L.grid_desc(latent_shape_q, chunk_3d_shape_q), L.grid_desc(latent_shape_k, chunk_3d_shape_k)

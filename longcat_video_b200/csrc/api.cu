@@ -243,6 +243,29 @@ int lcbsa_set_attn_sm_reserve(int n_sms) {
     return lcbsa::set_attn_sm_reserve(n_sms);
 }
 
+int lcbsa_score_cdf(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, float sm_scale, float cdf_threshold,
+                    int nsel_min, int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream) {
+    if (!q_cmp || !k_cmp || !idx || !cnt) return fail(LCBSA_EINVAL, "score_cdf: null pointer");
+    if (dtype != LCBSA_BF16 && dtype != LCBSA_FP16) return fail(LCBSA_EUNSUPPORTED, "score_cdf: bf16 or fp16 only");
+    if (BH < 0 || Nq < 0 || Nk <= 0) return fail(LCBSA_EINVAL, "score_cdf: bad sizes");
+    if (Nk > 4096) return fail(LCBSA_EUNSUPPORTED, "score_cdf: more than 4096 key blocks");
+    if (nsel_min < 0 || nsel_min > Nk) return fail(LCBSA_EINVAL, "score_cdf: nsel_min %d outside [0, %d]", nsel_min, Nk);
+    if (!(cdf_threshold == cdf_threshold)) return fail(LCBSA_EINVAL, "score_cdf: threshold is NaN");
+    if (reinterpret_cast<uintptr_t>(q_cmp) % 16 || reinterpret_cast<uintptr_t>(k_cmp) % 16)
+        return fail(LCBSA_EINVAL, "score_cdf: pooled tensors must be 16-byte aligned");
+    const size_t need = lcbsa::score_keys_bytes(dtype, BH, Nq, Nk, D);
+    if (need == 0) return fail(LCBSA_EUNSUPPORTED, "score_cdf: head_dim 64 or 128 and batch*heads up to 65535");
+    if (!keys_ws || keys_bytes < need) return fail(LCBSA_EWORKSPACE, "score_cdf: workspace of %zu bytes, %zu needed", keys_bytes, need);
+    if (reinterpret_cast<uintptr_t>(keys_ws) % 16) return fail(LCBSA_EINVAL, "score_cdf: workspace not 16-byte aligned");
+    const char* why = "";
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = lcbsa::launch_score_keys(dtype, q_cmp, k_cmp, BH, Nq, Nk, D, keys_ws, st, &why);
+    if (e == cudaSuccess)
+        e = lcbsa::launch_cdf_rows(dtype, keys_ws, (long long)BH * Nq, Nk, sm_scale, cdf_threshold, nsel_min, idx, cnt, st, &why);
+    if (e != cudaSuccess) return cuda_fail(e, "score_cdf", why);
+    return LCBSA_OK;
+}
+
 size_t lcbsa_rope_table_floats(const LcbsaGrid* g, int D) {
     if (!grid_ok(g) || D <= 0 || D % 2 != 0) return 0;
     return lcbsa::rope_table_floats(g->T, g->H, g->W, D);

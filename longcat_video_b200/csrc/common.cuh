@@ -100,6 +100,11 @@ struct AttnArgs {
 cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why);
 bool attn_tc_supported(const AttnArgs& a, const char** why);
+cudaError_t launch_score_keys(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, void* keys_ws, cudaStream_t st,
+                              const char** why);
+// cdf_threshold selectors on the keys of launch_score_keys (select_cdf.cu): idx [rows, Nk] sorted by descending weight, cnt [rows]
+cudaError_t launch_cdf_rows(int dtype, const void* keys, long long rows, int Nk, float sm_scale, float threshold, int nsel_min,
+                            int32_t* idx, int32_t* cnt, cudaStream_t st, const char** why);
 int set_attn_sm_reserve(int n_sms);  // SMs the tcgen05 attention kernel leaves idle; returns the previous value
 
 // q/k RMSNorm + 3-D rotary embedding in one pass (norm_rope.cu).  The table is the packed separable form

@@ -134,6 +134,22 @@ size_t score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D) {
     return (size_t)BH * Nq * nk_pad * sizeof(uint16_t);
 }
 
+// scores only: the 16-bit keys of all [BH, Nq, Nk] scores into keys_ws (score_keys_bytes(...) bytes)
+cudaError_t launch_score_keys(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, void* keys_ws, cudaStream_t st,
+                              const char** why) {
+    if (BH == 0 || Nq == 0) return cudaSuccess;
+    if (score_keys_bytes(dtype, BH, Nq, Nk, D) == 0) {
+        *why = "the score kernel takes bf16 or fp16 with head_dim 64 or 128";
+        return cudaErrorInvalidValue;
+    }
+    const int nk_pad = (Nk + 63) / 64 * 64;
+    uint16_t* keys = static_cast<uint16_t*>(keys_ws);
+    if (dtype == LCBSA_BF16)
+        return D == 128 ? launch_gemm<__nv_bfloat16, 128>(qc, kc, BH, Nq, Nk, nk_pad, keys, st)
+                        : launch_gemm<__nv_bfloat16, 64>(qc, kc, BH, Nq, Nk, nk_pad, keys, st);
+    return D == 128 ? launch_gemm<__half, 128>(qc, kc, BH, Nq, Nk, nk_pad, keys, st) : launch_gemm<__half, 64>(qc, kc, BH, Nq, Nk, nk_pad, keys, st);
+}
+
 cudaError_t launch_score_gemm_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel, int cap,
                                    int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why) {
     if (BH == 0 || Nq == 0) return cudaSuccess;

@@ -172,10 +172,14 @@ def attention(q, k, v, latent_shape_q, latent_shape_k, chunk_q, chunk_k, idx, cn
 def flash_attn_bsa_3d(q, k, v, latent_shape_q, latent_shape_k, sparsity=0.875, cdf_threshold=None,
                       chunk_3d_shape_q=(4, 4, 8), chunk_3d_shape_k=(4, 4, 8)):
     """Whole forward with the reference's signature (bsa_interface.py:612-623); fp32 result."""
-    if cdf_threshold is not None:
-        raise NotImplementedError("oracle covers the top-k selector only")
-    if sparsity is None:
+    if sparsity is None and cdf_threshold is None:
         raise ValueError
+    if cdf_threshold is not None:  # bsa_interface.py:271-274
+        qc, kc = pool(q, latent_shape_q, chunk_3d_shape_q), pool(k, latent_shape_k, chunk_3d_shape_k)
+        nsel_min = 0 if sparsity is None else num_selected(sparsity, kc.shape[2])
+        idx, cnt = cdf_select(score(qc, kc), cdf_threshold, 1 / q.shape[-1] ** 0.5, nsel_min)
+        out, _ = attention(q, k, v, latent_shape_q, latent_shape_k, chunk_3d_shape_q, chunk_3d_shape_k, idx, cnt)
+        return out
     idx, cnt, _, _ = block_select(q, k, latent_shape_q, latent_shape_k, sparsity,
                                   chunk_3d_shape_q, chunk_3d_shape_k)
     out, _ = attention(q, k, v, latent_shape_q, latent_shape_k, chunk_3d_shape_q, chunk_3d_shape_k,
