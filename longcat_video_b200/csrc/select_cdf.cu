@@ -10,8 +10,8 @@
 //
 // Arithmetic, in the order the CPU oracle fixes where the reference leaves it to the library:
 //   x = T(score * sm_scale);  e = exp(x - max x) with the machine-independent exp below;  the denominator as 256
-//   partial sums (thread t adds entries t, t + 256, ... in ascending order), a butterfly over each warp and over the
-//   8 warp sums;  w = T(e / sum);  sort by (w descending, index ascending): all keys are distinct, so the result does
+//   partial sums (thread t adds its E consecutive entries t E .. t E + E - 1 in ascending order, E = 8 up to 2048
+//   entries and 16 above), a butterfly over each warp and over the 8 warp sums;  w = T(e / sum);  sort by (w descending, index ascending): all keys are distinct, so the result does
 //   not depend on the sorting network;  cdf = T(fp32 running sum), count = #(cdf <= threshold), at least nsel_min.
 #include "select_common.cuh"
 
@@ -47,6 +47,159 @@ __device__ __forceinline__ __half from_bits<__half>(uint16_t u) { return __ushor
 __device__ __forceinline__ uint16_t to_bits(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
 __device__ __forceinline__ uint16_t to_bits(__half v) { return __half_as_ushort(v); }
 
+// The running sum of the sorted weights is sequential by definition (fp32, every partial result rounded to T for the
+// comparison).  One warp: lane l holds entry 32 c + l of chunk c, the weights go round by shuffle and every lane adds
+// them in order, keeping the sum as it stood after its own entry.  Stops at the first chunk that passes the threshold.
+template <typename T>
+__device__ __forceinline__ void count_row_cdf(const uint32_t* row, int Nk, float threshold, int nsel_min, int32_t* cnt, int lane) {
+    float acc = 0.0f;
+    int n = 0;
+    for (int c = 0; c < Nk; c += 32) {
+        const bool have = c + lane < Nk;
+        const float w = have ? DType<T>::to_f32(from_bits<T>((uint16_t)(row[c + lane] >> 16))) : 0.0f;
+        float mine = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, w, i));  // absent entries add +0: no change
+            mine = lane == i ? acc : mine;
+        }
+        const bool ok = have && DType<T>::to_f32(DType<T>::from_f32(mine)) <= threshold;
+        const uint32_t pass = __ballot_sync(0xffffffffu, ok);
+        const int lead = __ffs(~pass) - 1;  // entries before the first that fails (the sums do not decrease)
+        if (lead >= 0) {
+            n += lead;
+            break;
+        }
+        n += 32;
+    }
+    if (lane == 0) *cnt = max(min(n, Nk), nsel_min);
+}
+
+// Rows of up to 2048 entries: thread t keeps entries 8 t .. 8 t + 7 in registers from the load to the sorted row.
+// Of the 66 compare-exchange stages of the 2048-wide bitonic network, the 30 with a distance below 8 stay inside a
+// thread, the 30 with a distance of 8 .. 128 entries go through warp shuffles, and only the 6 with a distance of
+// 256 .. 1024 entries cross warps through shared memory.
+constexpr int kFastE = 8;
+constexpr int kFastP = kFastE * kCdfThreads;
+
+template <typename T>
+__global__ void __launch_bounds__(kCdfThreads) cdf_rows_fast_kernel(const uint16_t* __restrict__ keys, int Nk, int nk_pad, float sm_scale,
+                                                                   float threshold, int nsel_min, int32_t* __restrict__ idx,
+                                                                   int32_t* __restrict__ cnt) {
+    __shared__ __align__(16) uint32_t row[kFastP];
+    __shared__ float red[kCdfThreads / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long r = blockIdx.x;
+    const int base = tid * kFastE;
+
+    // x = T(score * sm_scale) and its maximum
+    float x[kFastE];
+    float m = -INFINITY;
+    {
+        uint4 raw4 = make_uint4(0u, 0u, 0u, 0u);
+        if (base < nk_pad) raw4 = __ldg(reinterpret_cast<const uint4*>(keys + r * nk_pad + base));
+        const uint16_t* kk = reinterpret_cast<const uint16_t*>(&raw4);
+#pragma unroll
+        for (int e = 0; e < kFastE; ++e) {
+            const uint16_t raw = (kk[e] & 0x8000u) ? (uint16_t)(kk[e] & 0x7fffu) : (uint16_t)~kk[e];  // inverse of make_key
+            x[e] = DType<T>::to_f32(DType<T>::from_f32(__fmul_rn(DType<T>::to_f32(from_bits<T>(raw)), sm_scale)));
+            if (base + e < Nk) m = fmaxf(m, x[e]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < kCdfThreads / 32; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+
+    // e = exp(x - m) and the denominator
+    float part = 0.0f;
+#pragma unroll
+    for (int e = 0; e < kFastE; ++e) {
+        if (base + e < Nk) {
+            x[e] = exp_portable(__fsub_rn(x[e], m));
+            part = __fadd_rn(part, x[e]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    if (lane == 0) red[warp] = part;
+    __syncthreads();
+    float grp[kCdfThreads / 32];
+#pragma unroll
+    for (int w = 0; w < kCdfThreads / 32; ++w) grp[w] = red[w];
+#pragma unroll
+    for (int o = kCdfThreads / 64; o > 0; o >>= 1) {
+        float nxt[kCdfThreads / 32];
+#pragma unroll
+        for (int w = 0; w < kCdfThreads / 32; ++w) nxt[w] = __fadd_rn(grp[w], grp[w ^ o]);
+#pragma unroll
+        for (int w = 0; w < kCdfThreads / 32; ++w) grp[w] = nxt[w];
+    }
+    const float sum = grp[0];
+
+    // sort keys: weight bits above, reversed index below; padding sorts last
+    uint32_t v[kFastE];
+#pragma unroll
+    for (int e = 0; e < kFastE; ++e) {
+        v[e] = 0u;
+        if (base + e < Nk) v[e] = ((uint32_t)to_bits(DType<T>::from_f32(__fdiv_rn(x[e], sum))) << 16) | (uint32_t)(0xffff - (base + e));
+    }
+
+    // bitonic network, descending: entry i and entry i ^ j; the lower index keeps the larger key where (i & k) == 0
+#pragma unroll
+    for (int k = 2; k <= kFastP; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j < kFastE) {
+#pragma unroll
+                for (int e = 0; e < kFastE; ++e) {
+                    if ((e & j) == 0) {
+                        const bool desc = ((base + e) & k) == 0;
+                        const uint32_t a = v[e], b = v[e | j];
+                        const uint32_t hi = max(a, b), lo = min(a, b);
+                        v[e] = desc ? hi : lo;
+                        v[e | j] = desc ? lo : hi;
+                    }
+                }
+            } else {
+                const bool keep_max = ((base & j) == 0) == ((base & k) == 0);
+                uint32_t other[kFastE];
+                if (j < kFastE * 32) {
+#pragma unroll
+                    for (int e = 0; e < kFastE; ++e) other[e] = __shfl_xor_sync(0xffffffffu, v[e], j / kFastE);
+                } else {
+                    __syncthreads();  // the previous exchange has been read
+                    uint4* mine = reinterpret_cast<uint4*>(row + base);
+                    mine[0] = make_uint4(v[0], v[1], v[2], v[3]);
+                    mine[1] = make_uint4(v[4], v[5], v[6], v[7]);
+                    __syncthreads();
+                    const uint4* theirs = reinterpret_cast<const uint4*>(row + (base ^ j));
+                    const uint4 t0 = theirs[0], t1 = theirs[1];
+                    other[0] = t0.x; other[1] = t0.y; other[2] = t0.z; other[3] = t0.w;
+                    other[4] = t1.x; other[5] = t1.y; other[6] = t1.z; other[7] = t1.w;
+                }
+#pragma unroll
+                for (int e = 0; e < kFastE; ++e) v[e] = keep_max ? max(v[e], other[e]) : min(v[e], other[e]);
+            }
+        }
+    }
+
+    __syncthreads();
+    {
+        uint4* mine = reinterpret_cast<uint4*>(row + base);
+        mine[0] = make_uint4(v[0], v[1], v[2], v[3]);
+        mine[1] = make_uint4(v[4], v[5], v[6], v[7]);
+    }
+    __syncthreads();
+    int32_t* out = idx + r * Nk;
+    for (int j = tid; j < Nk; j += kCdfThreads) out[j] = (int32_t)(0xffffu - (row[j] & 0xffffu));
+    if (warp == 0) count_row_cdf<T>(row, Nk, threshold, nsel_min, cnt + r, lane);
+}
+
 // keys: [rows, nk_pad] order-preserving 16-bit keys of the scores; idx: [rows, Nk]; cnt: [rows].  P: power of two >= Nk.
 template <typename T>
 __global__ void __launch_bounds__(kCdfThreads) cdf_rows_kernel(const uint16_t* __restrict__ keys, int Nk, int nk_pad, int P, float sm_scale,
@@ -76,9 +229,10 @@ __global__ void __launch_bounds__(kCdfThreads) cdf_rows_kernel(const uint16_t* _
     for (int w = 1; w < kCdfThreads / 32; ++w) m = fmaxf(m, red[w]);
     __syncthreads();
 
-    // e = exp(x - m) and the denominator
+    // e = exp(x - m) and the denominator: thread t sums its E consecutive entries
     float part = 0.0f;
-    for (int j = tid; j < Nk; j += kCdfThreads) {
+    const int E = Nk <= 2048 ? 8 : 16;
+    for (int j = tid * E; j < min(Nk, tid * E + E); ++j) {
         const float e = exp_portable(__fsub_rn(__uint_as_float(row[j]), m));
         row[j] = __float_as_uint(e);
         part = __fadd_rn(part, e);
@@ -99,6 +253,7 @@ __global__ void __launch_bounds__(kCdfThreads) cdf_rows_kernel(const uint16_t* _
         for (int w = 0; w < kCdfThreads / 32; ++w) grp[w] = nxt[w];
     }
     const float sum = grp[0];
+    __syncthreads();  // every e is in place before other threads read it
 
     // sort keys: weight bits above, reversed index below; padding sorts last
     for (int j = tid; j < P; j += kCdfThreads) {
@@ -131,24 +286,7 @@ __global__ void __launch_bounds__(kCdfThreads) cdf_rows_kernel(const uint16_t* _
     int32_t* out = idx + r * Nk;
     for (int j = tid; j < Nk; j += kCdfThreads) out[j] = (int32_t)(0xffffu - (row[j] & 0xffffu));
 
-    if (tid == 0) {  // the running sum is sequential by definition; loads go eight at a time so that they overlap
-        float acc = 0.0f;
-        int n = 0;
-        bool open = true;
-        for (int base = 0; base < Nk && open; base += 8) {
-            uint32_t v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = base + i < Nk ? row[base + i] : 0u;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (open && base + i < Nk) {
-                    acc = __fadd_rn(acc, DType<T>::to_f32(from_bits<T>((uint16_t)(v[i] >> 16))));
-                    if (DType<T>::to_f32(DType<T>::from_f32(acc)) <= threshold) ++n; else open = false;
-                }
-            }
-        }
-        cnt[r] = max(n, nsel_min);
-    }
+    if (warp == 0) count_row_cdf<T>(row, Nk, threshold, nsel_min, cnt + r, lane);
 }
 
 }  // namespace
@@ -164,9 +302,17 @@ cudaError_t launch_cdf_rows(int dtype, const void* keys, long long rows, int Nk,
         *why = "the cdf selectors take at most 2^31 - 1 rows";
         return cudaErrorInvalidValue;
     }
+    const int nk_pad = (Nk + 63) / 64 * 64;
+    const uint16_t* kp0 = static_cast<const uint16_t*>(keys);
+    if (Nk <= kFastP) {
+        if (dtype == LCBSA_BF16)
+            cdf_rows_fast_kernel<__nv_bfloat16><<<(unsigned)rows, kCdfThreads, 0, st>>>(kp0, Nk, nk_pad, sm_scale, threshold, nsel_min, idx, cnt);
+        else
+            cdf_rows_fast_kernel<__half><<<(unsigned)rows, kCdfThreads, 0, st>>>(kp0, Nk, nk_pad, sm_scale, threshold, nsel_min, idx, cnt);
+        return cudaGetLastError();
+    }
     int P = 2;
     while (P < Nk) P <<= 1;
-    const int nk_pad = (Nk + 63) / 64 * 64;
     const size_t smem = (size_t)P * sizeof(uint32_t);
     const uint16_t* kp = static_cast<const uint16_t*>(keys);
     if (dtype == LCBSA_BF16)

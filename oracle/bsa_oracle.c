@@ -304,7 +304,8 @@ static int cmp_u32_desc(const void* a, const void* b) {
  *   count = number of entries with cdf <= threshold (searchsorted, right=True), raised to nsel_min for the combined
  *   "max(cdf, topk)" selector; the list is the whole sorted index row, of which the first `count` entries are used.
  * What the reference leaves to the library is fixed here: exp is lco_exp; the softmax denominator is summed as 256
- * partial sums (partial t takes entries t, t + 256, ... in ascending order) combined by a butterfly over each group
+ * partial sums (partial t takes the E consecutive entries t E .. t E + E - 1 in ascending order, E = 8 up to 2048
+ * entries and 16 above) combined by a butterfly over each group
  * of 32 (xor 16, 8, 4, 2, 1) and then over the 8 group sums (xor 4, 2, 1); equal weights are ordered by ascending
  * index (torch.sort leaves the order of ties open); the comparison with the threshold is done in fp32.
  * score: [rows, Nk] in dtype (bf16 / fp16); idx: [rows, Nk]; cnt: [rows].
@@ -324,9 +325,10 @@ void lco_cdf_select(const void* score, int dtype, int64_t rows, int Nk, float sm
             }
             float part[256];
             for (int t = 0; t < 256; ++t) part[t] = 0.0f;
+            const int E = Nk <= 2048 ? 8 : 16;
             for (int j = 0; j < Nk; ++j) {
                 e[j] = lco_exp(e[j] - m);
-                part[j & 255] += e[j];
+                part[j / E] += e[j];
             }
             for (int o = 16; o > 0; o >>= 1) {
                 float nxt[256];

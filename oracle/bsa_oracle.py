@@ -131,7 +131,7 @@ def cdf_select(score_: torch.Tensor, cdf_threshold: float, sm_scale: float, nsel
     index row sorted by descending softmax weight (int32 ``[B,H,Nq,Nk]``; ties by ascending index) and the number of
     leading entries to use (int32 ``[B,H,Nq]``), at least ``nsel_min`` (the combined "max(cdf, topk)" selector)."""
     B, H, Nq, Nk = score_.shape
-    assert score_.dtype in (torch.bfloat16, torch.float16) and 0 < Nk < 65535
+    assert score_.dtype in (torch.bfloat16, torch.float16) and 0 < Nk <= 4096
     score_ = score_.contiguous()
     idx = torch.empty(B, H, Nq, Nk, dtype=torch.int32)
     cnt = torch.empty(B, H, Nq, dtype=torch.int32)

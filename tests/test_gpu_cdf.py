@@ -25,9 +25,10 @@ def test_kernel_equals_oracle_and_reference_fixture(name):
     check_against_reference(c, idx, cnt)
 
 
-@pytest.mark.parametrize("nk,thr,nmin", [(1, 0.5, 0), (2, 0.5, 0), (33, 2.0, 0), (64, 0.0, 0), (65, 0.0, 7), (257, 0.8, 0), (1000, 0.99, 100)])
+@pytest.mark.parametrize("nk,thr,nmin", [(1, 0.5, 0), (2, 0.5, 0), (33, 2.0, 0), (64, 0.0, 0), (65, 0.0, 7), (257, 0.8, 0), (1000, 0.99, 100), (2048, 0.9, 0), (2500, 0.7, 0)])
 def test_edge_sizes_and_thresholds(nk, thr, nmin):
-    """Rows shorter than a warp, rows that are not a power of two, thresholds nothing or everything exceeds."""
+    """Rows shorter than a warp, rows that are not a power of two, rows above 2048 entries (the shared-memory form of the
+    kernel), thresholds nothing or everything exceeds."""
     g = torch.Generator().manual_seed(nk)
     q = torch.randn(1, 2, 9, 64, generator=g).bfloat16()
     k = torch.randn(1, 2, nk, 64, generator=g).bfloat16()
