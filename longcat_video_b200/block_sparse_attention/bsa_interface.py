@@ -127,11 +127,15 @@ def get_select_indices(q: torch.Tensor, k: torch.Tensor, latent_shape_q, latent_
 
 
 def attn_fwd_bsa_varlen(q, k, v, sm_scale, block_indices, block_indices_lens, latent_shape_q, latent_shape_k,
-                        chunk_3d_shape_q, chunk_3d_shape_k, return_lse: bool = False, impl: int = L.ATTN_AUTO):
-    """Block-sparse attention forward over the listed K/V blocks; q/k/v and the result in T,H,W order."""
+                        chunk_3d_shape_q, chunk_3d_shape_k, return_lse: bool = False, impl: int = L.ATTN_AUTO, out=None):
+    """Block-sparse attention forward over the listed K/V blocks; q/k/v and the result in T,H,W order.  ``out`` may be a
+    ``[B,H,Sq,D]`` view (head_dim contiguous, 16-byte strides) to write into."""
     q, k, v = _as_abi(q), _as_abi(k), _as_abi(v)
     B, H, Sq, D = q.shape
-    out = torch.empty(B, H, Sq, D, dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty(B, H, Sq, D, dtype=q.dtype, device=q.device)
+    elif tuple(out.shape) != (B, H, Sq, D) or out.dtype != q.dtype or not L.abi_ok(out):
+        raise ValueError("out must be a [B, H, Sq, D] view of the input dtype with 16-byte aligned strides")
     lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device) if return_lse else None
     idx = block_indices.to(torch.int32).contiguous()
     cnt = block_indices_lens.to(torch.int32).contiguous()
@@ -192,6 +196,38 @@ def flash_attn_bsa_3d(
                                   chunk_3d_shape_q, chunk_3d_shape_k)
     return attn_fwd_bsa_varlen(q, k, v, 1 / head_dim ** 0.5, idx, cnt, latent_shape_q, latent_shape_k,
                                chunk_3d_shape_q, chunk_3d_shape_k)
+
+
+@torch.compiler.disable
+def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params) -> torch.Tensor:
+    """The cond / noise split of ``Attention.forward`` (longcat_video/modules/attention.py:124-137) as one op: the first
+    ``num_cond_latents`` frames attend among themselves, the remaining frames attend to everything, and the two results
+    are one ``[B,H,S,D]`` tensor.  The reference makes contiguous copies of q_cond, k_cond, v_cond and q_noise, calls
+    the attention twice and concatenates; here both calls work on views of q, k, v and write into their part of one
+    output, so nothing is copied.  Bit-identical to the two separate calls.  ``latent_shape`` is the (T, H, W) of q."""
+    T, Hh, W = (int(x) for x in latent_shape)
+    B_, H_, S, D = q.shape
+    nc = int(num_cond_latents or 0)
+    if nc <= 0:
+        return flash_attn_bsa_3d(q, k, v, latent_shape, latent_shape, **bsa_params)
+    if not 0 < nc < T:
+        raise ValueError(f"num_cond_latents {nc} outside (0, {T})")
+    assert T * Hh * W == S and k.shape[2] == S and v.shape[2] == S
+    sc = nc * Hh * W
+    out = torch.empty(B_, H_, S, D, dtype=q.dtype, device=q.device)
+    chunk_q = bsa_params.get("chunk_3d_shape_q", [4, 4, 8])
+    chunk_k = bsa_params.get("chunk_3d_shape_k", [4, 4, 8])
+    sparsity, cdf = bsa_params.get("sparsity", 0.875), bsa_params.get("cdf_threshold", None)
+    if not bsa_params.get("allow_ragged", False):
+        assert nc % chunk_q[0] == 0 and (T - nc) % chunk_q[0] == 0 and nc % chunk_k[0] == 0 and T % chunk_k[0] == 0
+        assert Hh % chunk_q[1] == 0 and W % chunk_q[2] == 0 and Hh % chunk_k[1] == 0 and W % chunk_k[2] == 0
+    for q_part, kv_len, o_part, gq, gk in (
+            (q[:, :, :sc], sc, out[:, :, :sc], (nc, Hh, W), (nc, Hh, W)),
+            (q[:, :, sc:], S, out[:, :, sc:], (T - nc, Hh, W), (T, Hh, W))):
+        k_part, v_part = k[:, :, :kv_len], v[:, :, :kv_len]
+        idx, cnt = get_select_indices(q_part, k_part, gq, gk, sparsity, cdf, chunk_q, chunk_k)
+        attn_fwd_bsa_varlen(q_part, k_part, v_part, 1 / D ** 0.5, idx, cnt, gq, gk, chunk_q, chunk_k, out=o_part)
+    return out
 
 
 _HOST_STATE = {}
