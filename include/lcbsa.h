@@ -192,6 +192,16 @@ int lcbsa_norm_rope(const LcbsaTensor* x, const void* weight, const LcbsaGrid* g
                     const LcbsaTensor* out, void* stream);
 
 /*
+ * The same kernel with its parts switchable, for the KV-cache path (longcat_video/modules/attention.py:118-119 and
+ * 149-171): weight == NULL skips the normalisation (keys that were cached after q_norm / k_norm and before rope_3d),
+ * rope_tab == NULL skips the rotary embedding (what return_kv caches), and the token at grid position (t, h, w) takes
+ * the angles of frame t + t_offset of a table built for table_T >= grid->T + t_offset frames (the new tokens behind
+ * num_cond_latents cached frames, attention.py:165-169, without padding q).
+ */
+int lcbsa_norm_rope_ex(const LcbsaTensor* x, const void* weight, const LcbsaGrid* grid, const float* rope_tab, int table_T, int t_offset,
+                       float eps, const LcbsaTensor* out, void* stream);
+
+/*
  * Enqueue `count` device-to-device copies of `nbytes` each on `stream`: dst[i] <- src[i], one cudaMemcpyAsync per
  * slab, so the copy engines move them; a destination may be another GPU's memory mapped into this process
  * (symmetric memory, CUDA IPC).  The pointer arrays are host memory and are read before the call returns.

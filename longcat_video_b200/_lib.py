@@ -63,6 +63,8 @@ SIGNATURES = {
     "lcbsa_block_select_static": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_int,
                                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "lcbsa_set_attn_sm_reserve": (ctypes.c_int, [ctypes.c_int]),
+    "lcbsa_norm_rope_ex": (ctypes.c_int, [_P(LcbsaTensor), ctypes.c_void_p, _P(LcbsaGrid), ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_float, _P(LcbsaTensor), ctypes.c_void_p]),
     "lcbsa_score_cdf": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_float, ctypes.c_int,
                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "lcbsa_rope_table_floats": (ctypes.c_size_t, [_P(LcbsaGrid), ctypes.c_int]),

@@ -271,24 +271,32 @@ size_t lcbsa_rope_table_floats(const LcbsaGrid* g, int D) {
     return lcbsa::rope_table_floats(g->T, g->H, g->W, D);
 }
 
-int lcbsa_norm_rope(const LcbsaTensor* x, const void* weight, const LcbsaGrid* g, const float* rope_tab, float eps,
-                    const LcbsaTensor* out, void* stream) {
+int lcbsa_norm_rope_ex(const LcbsaTensor* x, const void* weight, const LcbsaGrid* g, const float* rope_tab, int table_T, int t_offset,
+                       float eps, const LcbsaTensor* out, void* stream) {
     if (!grid_ok(g)) return fail(LCBSA_EINVAL, "norm_rope: bad grid");
     if (int rc = check_tensor("norm_rope input", x, g)) return rc;
     if (int rc = check_tensor("norm_rope output", out, g)) return rc;
-    if (!weight || !rope_tab) return fail(LCBSA_EINVAL, "norm_rope: null weight or rope table");
+    if (!weight && !rope_tab) return fail(LCBSA_EINVAL, "norm_rope: null weight and null rope table: nothing to do");
     if (reinterpret_cast<uintptr_t>(rope_tab) % 16 != 0 || reinterpret_cast<uintptr_t>(weight) % 16 != 0)
         return fail(LCBSA_EINVAL, "norm_rope: weight and rope table must be 16-byte aligned");
+    if (rope_tab && (t_offset < 0 || table_T < g->T + t_offset))
+        return fail(LCBSA_EINVAL, "norm_rope: frames %d..%d outside the table's %d frames", t_offset, g->T + t_offset - 1, table_T);
     if (x->dtype != out->dtype) return fail(LCBSA_EINVAL, "norm_rope: input and output dtypes differ");
     for (int i = 0; i < 4; ++i)
         if (x->size[i] != out->size[i]) return fail(LCBSA_EINVAL, "norm_rope: input and output shapes differ");
     if (!(eps >= 0.f)) return fail(LCBSA_EINVAL, "norm_rope: eps must be non-negative");
     const char* why = "";
-    cudaError_t e = lcbsa::launch_norm_rope(x->dtype, view_of(x), (int)x->size[0], (int)x->size[1], (int)x->size[2], (int)x->size[3], g->T,
-                                            g->H, g->W, weight, rope_tab, eps, out->data, out->stride[0], out->stride[1], out->stride[2],
-                                            static_cast<cudaStream_t>(stream), &why);
+    cudaError_t e = lcbsa::launch_norm_rope(x->dtype, view_of(x), (int)x->size[0], (int)x->size[1], (int)x->size[2], (int)x->size[3], table_T,
+                                            t_offset, g->H, g->W, weight, rope_tab, eps, out->data, out->stride[0], out->stride[1],
+                                            out->stride[2], static_cast<cudaStream_t>(stream), &why);
     if (e != cudaSuccess) return cuda_fail(e, "norm_rope", why);
     return LCBSA_OK;
+}
+
+int lcbsa_norm_rope(const LcbsaTensor* x, const void* weight, const LcbsaGrid* g, const float* rope_tab, float eps,
+                    const LcbsaTensor* out, void* stream) {
+    if (!weight || !rope_tab) return fail(LCBSA_EINVAL, "norm_rope: null weight or rope table");
+    return lcbsa_norm_rope_ex(x, weight, g, rope_tab, g ? g->T : 0, 0, eps, out, stream);
 }
 
 int lcbsa_copy_slabs(void* const* dst, const void* const* src, size_t nbytes, int count, void* stream) {

@@ -110,7 +110,7 @@ int set_attn_sm_reserve(int n_sms);  // SMs the tcgen05 attention kernel leaves 
 // q/k RMSNorm + 3-D rotary embedding in one pass (norm_rope.cu).  The table is the packed separable form
 // cos_t [T, dt] sin_t [T, dt] cos_h [H, dh] sin_h [H, dh] cos_w [W, dh] sin_w [W, dh], dh = 2 * (D / 6), dt = D - 2 * dh.
 size_t rope_table_floats(int Tg, int Hg, int Wg, int D);
-cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int D, int Tg, int Hg, int Wg, const void* weight,
+cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int D, int tab_t, int t_off, int Hg, int Wg, const void* weight,
                              const float* tab, float eps, void* out, long long osb, long long osh, long long oss, cudaStream_t st,
                              const char** why);
 

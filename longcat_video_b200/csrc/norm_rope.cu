@@ -68,10 +68,13 @@ struct Pair<__half> {
     }
 };
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, int S, int Tg, int Hg, int Wg, const T* __restrict__ weight,
-                                                               const float* __restrict__ tab, float eps, T* out, long long osb,
-                                                               long long osh, long long oss) {
+// NORM: RMSNorm times weight (off: the input is already normalised, e.g. cached keys); ROPE: the rotary embedding
+// (off: normalised q / k as they are cached before the embedding, attention.py:118-119).  The token at grid position
+// (t, h, w) takes the angles of frame t + t_off; tab_t is the number of frames the table holds (>= T + t_off).
+template <typename T, int D, bool NORM, bool ROPE>
+__global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, int S, int tab_t, int t_off, int Hg, int Wg,
+                                                               const T* __restrict__ weight, const float* __restrict__ tab, float eps, T* out,
+                                                               long long osb, long long osh, long long oss) {
     constexpr int PER = D / 8;   // elements per lane: 16 or 8
     constexpr int NV = PER / 8;  // 16-byte vectors per lane
     constexpr int NP = PER / 2;  // rotation pairs per lane
@@ -84,12 +87,12 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
     const int s = live ? (int)(first + tok) : S - 1;
     const int b = blockIdx.z;
     const int h0 = blockIdx.y * kHeadsPerCta, h1 = min(H, h0 + kHeadsPerCta);
-    const int w_pos = s % Wg, h_pos = (s / Wg) % Hg, t_pos = s / (Wg * Hg);
+    const int w_pos = s % Wg, h_pos = (s / Wg) % Hg, t_pos = s / (Wg * Hg) + t_off;
 
     // table layout: cos_t [T, DT] sin_t [T, DT] cos_h [H, DH] sin_h [H, DH] cos_w [W, DW] sin_w [W, DW]
     const float* cos_t = tab;
-    const float* sin_t = cos_t + (long long)Tg * DT;
-    const float* cos_h = sin_t + (long long)Tg * DT;
+    const float* sin_t = cos_t + (long long)tab_t * DT;
+    const float* cos_h = sin_t + (long long)tab_t * DT;
     const float* sin_h = cos_h + (long long)Hg * DH;
     const float* cos_w = sin_h + (long long)Hg * DH;
     const float* sin_w = cos_w + (long long)Wg * DW;
@@ -105,12 +108,12 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
         } else {
             c = cos_w + w_pos * DW + (d - DT - DH); n = sin_w + w_pos * DW + (d - DT - DH);
         }
-        cs[p] = __ldg(c);
-        sn[p] = __ldg(n);
+        cs[p] = ROPE ? __ldg(c) : 1.0f;
+        sn[p] = ROPE ? __ldg(n) : 0.0f;
     }
     uint4 wv[NV];  // the lane's weights, packed as they are stored
 #pragma unroll
-    for (int j = 0; j < NV; ++j) wv[j] = __ldg(reinterpret_cast<const uint4*>(weight + sub * PER) + j);
+    for (int j = 0; j < NV; ++j) wv[j] = NORM ? __ldg(reinterpret_cast<const uint4*>(weight + sub * PER) + j) : make_uint4(0u, 0u, 0u, 0u);
     const uint32_t* wp = reinterpret_cast<const uint32_t*>(wv);
 
     const T* sp = reinterpret_cast<const T*>(x.data) + (long long)b * x.sb + (long long)s * x.ss + (long long)h0 * x.sh + sub * PER;
@@ -126,25 +129,36 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
             for (int j = 0; j < NV; ++j) nxt[j] = reinterpret_cast<const uint4*>(sp)[j];
         }
         const uint32_t* cw = reinterpret_cast<const uint32_t*>(cur);
-        float v[PER];
+        float rinv = 1.0f;
+        if (NORM) {
+            float v[PER];
 #pragma unroll
-        for (int p = 0; p < NP; ++p) Pair<T>::unpack(cw[p], v[2 * p], v[2 * p + 1]);
-        float ss = 0.f;
+            for (int p = 0; p < NP; ++p) Pair<T>::unpack(cw[p], v[2 * p], v[2 * p + 1]);
+            float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
+            for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
-        const float mean = __fmul_rn(ss, 1.0f / (float)D);
-        const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+            for (int o = 4; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+            const float mean = __fmul_rn(ss, 1.0f / (float)D);
+            rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+        }
         uint4 res[NV];
         uint32_t* rw = reinterpret_cast<uint32_t*>(res);
 #pragma unroll
         for (int p = 0; p < NP; ++p) {
-            const uint32_t y = Pair<T>::pack(__fmul_rn(v[2 * p], rinv), __fmul_rn(v[2 * p + 1], rinv));
-            float z0, z1;
-            Pair<T>::unpack(Pair<T>::mul(y, wp[p]), z0, z1);
-            rw[p] = Pair<T>::pack(__fadd_rn(__fmul_rn(z0, cs[p]), __fmul_rn(-z1, sn[p])),
+            uint32_t z = cw[p];
+            if (NORM) {
+                float v0, v1;
+                Pair<T>::unpack(cw[p], v0, v1);
+                z = Pair<T>::mul(Pair<T>::pack(__fmul_rn(v0, rinv), __fmul_rn(v1, rinv)), wp[p]);
+            }
+            if (ROPE) {
+                float z0, z1;
+                Pair<T>::unpack(z, z0, z1);
+                z = Pair<T>::pack(__fadd_rn(__fmul_rn(z0, cs[p]), __fmul_rn(-z1, sn[p])),
                                   __fadd_rn(__fmul_rn(z1, cs[p]), __fmul_rn(z0, sn[p])));
+            }
+            rw[p] = z;
         }
         if (live) {
 #pragma unroll
@@ -156,14 +170,22 @@ __global__ void __launch_bounds__(kWarps * 32) norm_rope_kernel(View x, int H, i
     }
 }
 
-template <typename T, int D>
-cudaError_t run(const View& x, int B, int H, int S, int Tg, int Hg, int Wg, const void* weight, const float* tab, float eps, void* out,
-                long long osb, long long osh, long long oss, cudaStream_t st) {
+template <typename T, int D, bool NORM, bool ROPE>
+cudaError_t run(const View& x, int B, int H, int S, int tab_t, int t_off, int Hg, int Wg, const void* weight, const float* tab, float eps,
+                void* out, long long osb, long long osh, long long oss, cudaStream_t st) {
     if ((long long)B * H * S == 0) return cudaSuccess;
     dim3 grid((unsigned)((S + kTokens * kWarps - 1) / (kTokens * kWarps)), (unsigned)((H + kHeadsPerCta - 1) / kHeadsPerCta), (unsigned)B);
-    norm_rope_kernel<T, D><<<grid, kWarps * 32, 0, st>>>(x, H, S, Tg, Hg, Wg, reinterpret_cast<const T*>(weight), tab, eps,
-                                                        reinterpret_cast<T*>(out), osb, osh, oss);
+    norm_rope_kernel<T, D, NORM, ROPE><<<grid, kWarps * 32, 0, st>>>(x, H, S, tab_t, t_off, Hg, Wg, reinterpret_cast<const T*>(weight), tab,
+                                                                    eps, reinterpret_cast<T*>(out), osb, osh, oss);
     return cudaGetLastError();
+}
+
+template <typename T, int D>
+cudaError_t pick(bool norm, bool rope, const View& x, int B, int H, int S, int tab_t, int t_off, int Hg, int Wg, const void* weight,
+                 const float* tab, float eps, void* out, long long osb, long long osh, long long oss, cudaStream_t st) {
+    if (norm && rope) return run<T, D, true, true>(x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
+    if (norm) return run<T, D, true, false>(x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
+    return run<T, D, false, true>(x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
 }
 
 }  // namespace
@@ -173,7 +195,8 @@ size_t rope_table_floats(int Tg, int Hg, int Wg, int D) {
     return 2 * ((size_t)Tg * dt + (size_t)Hg * dh + (size_t)Wg * dh);
 }
 
-cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int D, int Tg, int Hg, int Wg, const void* weight,
+// weight == nullptr: no normalisation; tab == nullptr: no rotary embedding (not both)
+cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int D, int tab_t, int t_off, int Hg, int Wg, const void* weight,
                              const float* tab, float eps, void* out, long long osb, long long osh, long long oss, cudaStream_t st,
                              const char** why) {
     if (dtype == LCBSA_FP32 || (D != 64 && D != 128)) {
@@ -184,11 +207,16 @@ cudaError_t launch_norm_rope(int dtype, const View& x, int B, int H, int S, int 
         *why = "norm_rope: batch above 65535";
         return cudaErrorInvalidValue;
     }
+    const bool norm = weight != nullptr, rope = tab != nullptr;
+    if (!norm && !rope) {
+        *why = "norm_rope: neither a weight nor a rope table";
+        return cudaErrorInvalidValue;
+    }
     if (dtype == LCBSA_BF16)
-        return D == 128 ? run<__nv_bfloat16, 128>(x, B, H, S, Tg, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st)
-                        : run<__nv_bfloat16, 64>(x, B, H, S, Tg, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
-    return D == 128 ? run<__half, 128>(x, B, H, S, Tg, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st)
-                    : run<__half, 64>(x, B, H, S, Tg, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
+        return D == 128 ? pick<__nv_bfloat16, 128>(norm, rope, x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st)
+                        : pick<__nv_bfloat16, 64>(norm, rope, x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
+    return D == 128 ? pick<__half, 128>(norm, rope, x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st)
+                    : pick<__half, 64>(norm, rope, x, B, H, S, tab_t, t_off, Hg, Wg, weight, tab, eps, out, osb, osh, oss, st);
 }
 
 }  // namespace lcbsa

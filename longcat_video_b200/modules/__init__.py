@@ -1,2 +1,2 @@
 """Host mirrors of the reference's `longcat_video/modules` pieces that touch the BSA path."""
-from .rope_3d import qk_norm_rope, norm_rope, rope_table  # noqa: F401
+from .rope_3d import norm_rope, qk_norm_rope, qk_norm_rope_with_kv_cache, rms_norm, rope_table  # noqa: F401

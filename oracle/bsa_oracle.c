@@ -450,7 +450,9 @@ void lco_round_through(float* x, int64_t n, int dtype) {
  *   accumulated in ascending order with fmaf) combined by the butterfly
  *   p[i] += p[i ^ o] for o = 4, 2, 1; mean = sum * (1/D); rsqrt(v) = 1 / sqrtf(v) (both correctly rounded);
  *   the two products of the rotation are rounded separately before the addition (no fused multiply-add).
- * x: [rows, D] with row stride xs elements; cos, sin: row index = row % S; out: dense [rows, D]. */
+ * x: [rows, D] with row stride xs elements; cos, sin: row index = row % S; out: dense [rows, D].
+ * weight == NULL: no normalisation (z = x); cos_tab == NULL: no rotary embedding (o = z) -- the two halves as the
+ * KV-cache path applies them (attention.py:118-119, 149-171). */
 void lco_norm_rope(const void* x, int64_t xs, int dtype, int64_t rows, int D, int64_t S, const void* weight,
                    const float* cos_tab, const float* sin_tab, float eps, void* out) {
     const int per = D / 8;
@@ -472,12 +474,21 @@ void lco_norm_rope(const void* x, int64_t xs, int dtype, int64_t rows, int D, in
         }
         const float mean = part[0] * (1.0f / (float)D);
         const float rinv = 1.0f / sqrtf(mean + eps);
+        const int norm = weight != NULL, rope = cos_tab != NULL;
         const int64_t pos = r % S;
         for (int d = 0; d < D; d += 2) {
             float z[2];
             for (int e = 0; e < 2; ++e) {
-                const float y = round_to(dtype, load_elem(x, dtype, r * xs + d + e) * rinv);
-                z[e] = round_to(dtype, y * load_elem(weight, dtype, d + e));
+                z[e] = load_elem(x, dtype, r * xs + d + e);
+                if (norm) {
+                    const float y = round_to(dtype, z[e] * rinv);
+                    z[e] = round_to(dtype, y * load_elem(weight, dtype, d + e));
+                }
+            }
+            if (!rope) {
+                store_elem(out, dtype, r * D + d, z[0]);
+                store_elem(out, dtype, r * D + d + 1, z[1]);
+                continue;
             }
             const float c0 = cos_tab[pos * D + d], c1 = cos_tab[pos * D + d + 1];
             const float s0 = sin_tab[pos * D + d], s1 = sin_tab[pos * D + d + 1];

@@ -211,14 +211,21 @@ def rope_tables(grid_size, head_dim: int, base: float = 10000.0):
     return full.cos().contiguous(), full.sin().contiguous()
 
 
-def norm_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """RMSNorm (fp32) + weight + 3-D rotary embedding of ``x [B, H, S, D]`` (any strides, D contiguous); dense result."""
+def norm_rope(x: torch.Tensor, weight: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+              eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm (fp32) + weight + 3-D rotary embedding of ``x [B, H, S, D]`` (any strides, D contiguous); dense result.
+    ``weight=None`` skips the normalisation, ``cos=sin=None`` the embedding (the halves the KV-cache path uses)."""
     B, H, S, D = x.shape
-    assert D % 16 == 0 and x.stride(3) == 1 and cos.shape == (S, D) and sin.shape == (S, D)
+    assert D % 16 == 0 and x.stride(3) == 1 and (weight is not None or cos is not None)
     xc = x.contiguous()
     out = torch.empty(B, H, S, D, dtype=x.dtype)
-    w = weight.to(x.dtype).contiguous()
+    w = None if weight is None else weight.to(x.dtype).contiguous()
+    if cos is not None:
+        assert cos.shape == (S, D) and sin.shape == (S, D)
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+    null = ctypes.c_void_p(None)
     lib().lco_norm_rope(ctypes.c_void_p(xc.data_ptr()), ctypes.c_int64(D), _DTYPE_CODE[x.dtype], ctypes.c_int64(B * H * S), D,
-                        ctypes.c_int64(S), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(cos.float().contiguous().data_ptr()),
-                        ctypes.c_void_p(sin.float().contiguous().data_ptr()), ctypes.c_float(eps), ctypes.c_void_p(out.data_ptr()))
+                        ctypes.c_int64(S), null if w is None else ctypes.c_void_p(w.data_ptr()),
+                        null if cos is None else ctypes.c_void_p(cos.data_ptr()), null if cos is None else ctypes.c_void_p(sin.data_ptr()),
+                        ctypes.c_float(eps), ctypes.c_void_p(out.data_ptr()))
     return out

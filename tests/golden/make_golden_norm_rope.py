@@ -6,7 +6,10 @@ Seeded qkv activations (bf16, the ``[B, N, 3, H, D]`` output layout of the fused
 weights go through ``RMSNorm_FP32`` (``longcat_video/modules/blocks.py:42-53``, eps 1e-6 as in
 ``longcat_video/modules/attention.py:40-41``) and ``RotaryPositionalEmbedding`` (``longcat_video/modules/rope_3d.py``)
 exactly as ``Attention.forward`` chains them (``attention.py:113-121``).  Stored: the inputs' bit patterns, the weights,
-and the reference's q and k (bf16 bit patterns).
+the reference's q and k (bf16 bit patterns), the normalised q and k before the embedding (what ``return_kv`` caches,
+``attention.py:118-119``), and the KV-cache flow of ``forward_with_kv_cache`` (``attention.py:156-171``) with ``NC``
+cached frames: cached keys (normalised, not embedded), then ``rope_3d`` over ``(T + NC, H, W)`` on
+``cat([k_cache, k_norm(k)])`` and on q padded in front, of which the last N tokens are kept.
 """
 import os
 import sys
@@ -19,6 +22,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 from longcat_video.modules.blocks import RMSNorm_FP32  # noqa: E402  (the reference)
 from longcat_video.modules.rope_3d import RotaryPositionalEmbedding  # noqa: E402  (the reference)
+
+NC = 2  # cached frames in the KV-cache flow
 
 CASES = {
     # name: (seed, B, heads, head_dim, grid)
@@ -44,8 +49,17 @@ def main():
             qn.weight.data = wq.clone()
             kn.weight.data = wk.clone()
             rope = RotaryPositionalEmbedding(D, cp_split_hw=(1, 1))
-            q2, k2 = rope(qn(q), kn(k), grid)
+            q1, k1 = qn(q), kn(k)
+            q2, k2 = rope(q1, k1, grid)
+            # forward_with_kv_cache: keys of NC earlier frames, cached after k_norm and before rope_3d
+            kc_raw = (torch.randn(B, H, NC * grid[1] * grid[2], D, generator=g) * 1.5).to(torch.bfloat16)
+            k_cache = kn(kc_raw)
+            k_full = torch.cat([k_cache, k1], dim=2).contiguous()
+            q_padding = torch.cat([torch.zeros_like(k_cache), q1], dim=2).contiguous()
+            q_padding, k_full = rope(q_padding, k_full, (grid[0] + NC, grid[1], grid[2]))
+            q_kv = q_padding[:, :, -N:].contiguous()
         np.savez_compressed(os.path.join(HERE, name + ".npz"), qkv=bits(qkv), wq=bits(wq), wk=bits(wk), q=bits(q2), k=bits(k2),
+                            q_normed=bits(q1), k_normed=bits(k1), k_cache=bits(k_cache), q_kv=bits(q_kv), k_full=bits(k_full),
                             grid=np.array(grid), meta=np.array([seed, B, H, D]))
         print(name, tuple(q2.shape), q2.dtype)
 

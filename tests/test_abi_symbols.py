@@ -76,6 +76,10 @@ def test_norm_rope_host_side():
     bad = L.grid_desc((4, 4, 5), (1, 1, 1))
     assert lib.lcbsa_norm_rope(ctypes.byref(t), 4096, ctypes.byref(bad), 4096, 1e-6, ctypes.byref(t), None) == -1
     assert b"does not match the latent grid" in lib.lcbsa_last_error()
+    assert lib.lcbsa_norm_rope_ex(ctypes.byref(t), None, ctypes.byref(g), None, 4, 0, 1e-6, ctypes.byref(t), None) == -1
+    assert b"nothing to do" in lib.lcbsa_last_error()
+    assert lib.lcbsa_norm_rope_ex(ctypes.byref(t), 4096, ctypes.byref(g), 4096, 4, 1, 1e-6, ctypes.byref(t), None) == -1
+    assert b"outside the table" in lib.lcbsa_last_error()
     from longcat_video_b200.modules import norm_rope
     with pytest.raises(RuntimeError):
         norm_rope(torch.zeros(1, 1, 64, 128, dtype=torch.bfloat16), torch.ones(128), (4, 4, 4))

@@ -9,7 +9,7 @@ import torch
 from longcat_video_b200 import _lib as L
 from longcat_video_b200.modules import rope_3d as R
 from oracle import bsa_oracle as O
-from tests.test_oracle_norm_rope import NAMES, load
+from tests.test_oracle_norm_rope import NAMES, close_to_reference, load
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -89,6 +89,29 @@ def test_kernel_against_reference_fixtures(name):
         assert float((diff / (want.float().abs() + 1e-3)).max()) < 2 ** -6
 
 
+@pytest.mark.parametrize("name", NAMES)
+def test_halves_and_kv_cache_flow(name):
+    """Normalisation alone, embedding alone, and the frame offset, as the KV-cache path of the attention layer uses them
+    (longcat_video/modules/attention.py:118-119, 156-171): bit for bit against the oracle, and against the reference's
+    fixtures within the bound of the oracle's own pin."""
+    c = load(name)
+    T, H, W = c["grid"]
+    nc, sc = c["nc"], c["nc"] * H * W
+    got = R.rms_norm(c["q_in"].to(DEV), c["wq"]).cpu()
+    assert torch.equal(_bits(got), _bits(O.norm_rope(c["q_in"], c["wq"], None, None)))
+    close_to_reference(got, c["q_normed"])
+    q_out, k_full = R.qk_norm_rope_with_kv_cache(c["q_in"].to(DEV), c["k_in"].to(DEV), c["wq"], c["wk"], c["k_cache"].to(DEV),
+                                                 c["grid"], nc)
+    torch.cuda.synchronize()
+    q_out, k_full = q_out.cpu(), k_full.cpu()
+    cos, sin = _tables((T + nc, H, W), c["D"])
+    assert torch.equal(_bits(k_full[:, :, :sc]), _bits(O.norm_rope(c["k_cache"], None, cos[:sc], sin[:sc])))
+    assert torch.equal(_bits(k_full[:, :, sc:]), _bits(O.norm_rope(c["k_in"], c["wk"], cos[sc:], sin[sc:])))
+    assert torch.equal(_bits(q_out), _bits(O.norm_rope(c["q_in"], c["wq"], cos[sc:], sin[sc:])))
+    close_to_reference(k_full, c["k_full"])
+    close_to_reference(q_out, c["q_kv"])
+
+
 def test_full_size_rows_keep_their_norm():
     """720p-sized property check: a rotation keeps the length of every pair, so with weight 1 every output row has
     mean square 1 (up to the two bf16 roundings), whatever its position."""
@@ -117,3 +140,7 @@ def test_bad_arguments_are_refused():
     xd, g = L.tensor_desc(x), L.grid_desc(grid, (1, 1, 1))
     rc = L.lib().lcbsa_norm_rope(ctypes.byref(xd), None, ctypes.byref(g), None, ctypes.c_float(1e-6), ctypes.byref(xd), None)
     assert rc == -1
+    with pytest.raises(L.LcbsaError, match="outside the table"):  # frames 3..4 of a table that holds 4
+        R.norm_rope(x, torch.ones(128), grid, t_offset=3, table_frames=4)
+    with pytest.raises(ValueError):
+        R.norm_rope(x, None, grid, rope=False)
