@@ -204,7 +204,9 @@ def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params
     ``num_cond_latents`` frames attend among themselves, the remaining frames attend to everything, and the two results
     are one ``[B,H,S,D]`` tensor.  The reference makes contiguous copies of q_cond, k_cond, v_cond and q_noise, calls
     the attention twice and concatenates; here both calls work on views of q, k, v and write into their part of one
-    output, so nothing is copied.  Bit-identical to the two separate calls.  ``latent_shape`` is the (T, H, W) of q."""
+    output, so nothing is copied; when the cond frames are whole blocks, the two block lists are put into one table and
+    a single attention launch serves both parts.  Bit-identical to the two separate calls.  ``latent_shape`` is the
+    (T, H, W) of q."""
     T, Hh, W = (int(x) for x in latent_shape)
     B_, H_, S, D = q.shape
     nc = int(num_cond_latents or 0)
@@ -221,12 +223,23 @@ def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params
     if not bsa_params.get("allow_ragged", False):
         assert nc % chunk_q[0] == 0 and (T - nc) % chunk_q[0] == 0 and nc % chunk_k[0] == 0 and T % chunk_k[0] == 0
         assert Hh % chunk_q[1] == 0 and W % chunk_q[2] == 0 and Hh % chunk_k[1] == 0 and W % chunk_k[2] == 0
-    for q_part, kv_len, o_part, gq, gk in (
-            (q[:, :, :sc], sc, out[:, :, :sc], (nc, Hh, W), (nc, Hh, W)),
-            (q[:, :, sc:], S, out[:, :, sc:], (T - nc, Hh, W), (T, Hh, W))):
-        k_part, v_part = k[:, :, :kv_len], v[:, :, :kv_len]
-        idx, cnt = get_select_indices(q_part, k_part, gq, gk, sparsity, cdf, chunk_q, chunk_k)
-        attn_fwd_bsa_varlen(q_part, k_part, v_part, 1 / D ** 0.5, idx, cnt, gq, gk, chunk_q, chunk_k, out=o_part)
+    parts = ((q[:, :, :sc], sc, out[:, :, :sc], (nc, Hh, W), (nc, Hh, W)),
+             (q[:, :, sc:], S, out[:, :, sc:], (T - nc, Hh, W), (T, Hh, W)))
+    lists = [get_select_indices(qp, k[:, :, :n], gq, gk, sparsity, cdf, chunk_q, chunk_k) for qp, n, _, gq, gk in parts]
+    if nc % chunk_q[0] == 0 and nc % chunk_k[0] == 0:
+        # Blocks are numbered frame-major, so the cond blocks are the first blocks of the whole grid on both sides and
+        # their lists hold the same numbers there: both parts go through one attention launch over the whole q.
+        (idx_c, cnt_c), (idx_n, cnt_n) = lists
+        cap = max(idx_c.shape[-1], idx_n.shape[-1])
+        nq_c = idx_c.shape[2]
+        idx = torch.full((B_, H_, nq_c + idx_n.shape[2], cap), -1, dtype=torch.int32, device=q.device)
+        idx[:, :, :nq_c, :idx_c.shape[-1]] = idx_c
+        idx[:, :, nq_c:, :idx_n.shape[-1]] = idx_n
+        attn_fwd_bsa_varlen(q, k, v, 1 / D ** 0.5, idx, torch.cat([cnt_c, cnt_n], dim=2), (T, Hh, W), (T, Hh, W), chunk_q, chunk_k,
+                            out=out)
+        return out
+    for (qp, n, op, gq, gk), (idx, cnt) in zip(parts, lists):  # ragged split: two launches on views
+        attn_fwd_bsa_varlen(qp, k[:, :, :n], v[:, :, :n], 1 / D ** 0.5, idx, cnt, gq, gk, chunk_q, chunk_k, out=op)
     return out
 
 
