@@ -223,7 +223,7 @@ def main():
 
         def e2e_step():
             # host tensors in, host tensor out: copies and kernels pipelined by chunks of four heads
-            B.flash_attn_bsa_3d_host(q_h, k_h, v_h, wl.grid_q, wl.grid_k, out=out_h, heads_per_chunk=4,
+            B.flash_attn_bsa_3d_host(q_h, k_h, v_h, wl.grid_q, wl.grid_k, out=out_h, heads_per_chunk=2,
                                      allow_ragged=ragged, **params)
 
         for _ in range(2):

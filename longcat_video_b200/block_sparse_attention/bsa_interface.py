@@ -246,7 +246,7 @@ def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params
 _HOST_STATE = {}
 
 
-def flash_attn_bsa_3d_host(q, k, v, latent_shape_q, latent_shape_k, out=None, heads_per_chunk=4, device=None, **bsa_params):
+def flash_attn_bsa_3d_host(q, k, v, latent_shape_q, latent_shape_k, out=None, heads_per_chunk=2, device=None, **bsa_params):
     """``flash_attn_bsa_3d`` for tensors that live in (pinned) host memory: q, k, v ``[B, H, S, D]`` on the host in,
     the result on the host out (``out`` is filled and returned if given, else a pinned tensor is allocated).
 
