@@ -4,15 +4,18 @@ on more than one GPU) on synthetic tensors of the named workload.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--heads H] [--impl ours|reference]
 
 One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 prints ONE JSON line.
-  value      effective TFLOP/s of the whole job (algorithmic flops of the selected blocks / step time),
-             inputs resident in HBM;  ms_per_step is ms/layer.
+  value      effective TFLOP/s of the whole job (algorithmic flops of the selected blocks / step time) of the public
+             entry point ``flash_attn_bsa_3d`` called eagerly on inputs resident in HBM; ms_per_step is ms/layer.
+             ``config.ms_per_step_cuda_graph`` is the same call replayed from a CUDA graph (side figure).
   e2e        the same metric through ``flash_attn_bsa_3d_host`` with HOST (pinned) inputs and output: the
              host->device copies of q,k,v and the device->host copy of the result are inside the timing
-             (pipelined with the kernels by chunks of four heads).
-  N > 1      ``flash_attn_bsa_3d_ulysses`` on every rank's [1, H, S/N, D] slices (longcat_video_b200/
-             context_parallel/bench_support.py), replayed from a CUDA graph captured after the warm-up.
-  roofline   the attention kernel against the measured bf16 tensor peak (events around that launch);
-             roofline_select does the same for the block-select stage against the measured HBM copy rate.
+             (pipelined with the kernels by chunks of two heads).
+  N > 1      ``flash_attn_bsa_3d_ulysses`` on every rank's [1, H, S/N, D] slices (bench_multi_gpu.py).
+  roofline   the attention kernel against the measured bf16 tensor peak (events around that launch, inside the
+             timed region); roofline_select does the same for the block-select stage against the measured HBM rate.
+  literal_720p   a short leg on BASELINE's literal 24x45x80 grid (ragged: through ``allow_ragged=True``).
+  gpu_reference  the reference's own Triton BSA (baseline/_ref, see baseline/install_reference.py) timed on the
+             same GPU and inputs, outside the timed region of this library; absent checkout -> "unavailable".
   cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
              host cores, on a bounded sample of the same workload.
 ``--impl reference`` times that CPU path alone (rank 0 only).
@@ -21,6 +24,7 @@ Inputs (2.8 GB at 720p) are far larger than the 126 MB L2, so no flush is needed
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -60,21 +64,31 @@ def n_selected(sparsity, nk):
     return int((1 - sparsity) * nk)
 
 
+def is_ragged(wl):
+    return any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
+
+
 def algorithmic_flops(wl, heads, nsel):
     """4 * B * H * Sq * (nsel * block) * D on legal grids; present rows / keys only on ragged ones."""
     ct, ch, cw = wl.chunk
     bs = ct * ch * cw
-    ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
-    if not ragged:
+    if not is_ragged(wl):
         return 4.0 * wl.batch * heads * wl.sq * nsel * bs * wl.head_dim
     return None  # counted from the lists at run time
 
 
+def _present_per_block(grid, chunk):
+    """Number of present tokens of every 3-D block (blocks numbered t-major, then h, then w), as a float64 vector."""
+    def axis(n, c):
+        nb = -(-n // c)
+        return torch.tensor([min(c, n - i * c) for i in range(nb)], dtype=torch.float64)
+    t, h, w = (axis(n, c) for n, c in zip(grid, chunk))
+    return (t[:, None, None] * h[None, :, None] * w[None, None, :]).reshape(-1)
+
+
 def flops_from_lists(wl, idx, cnt):
     """Exact count for ragged grids: rows(i) * sum of present keys of the listed blocks."""
-    from oracle import bsa_oracle as O  # checker-side helper: block -> token map only
-    present_q = (O.token_map(wl.grid_q, wl.chunk) >= 0).sum(1).to(torch.float64)
-    present_k = (O.token_map(wl.grid_k, wl.chunk) >= 0).sum(1).to(torch.float64)
+    present_q, present_k = _present_per_block(wl.grid_q, wl.chunk), _present_per_block(wl.grid_k, wl.chunk)
     idx_c, cnt_c = idx.cpu().long(), cnt.cpu()
     valid = torch.arange(idx_c.shape[-1])[None, None, None, :] < cnt_c[..., None]
     keys = (present_k[idx_c.clamp_min(0)] * valid).sum(-1)  # [B,H,Nq]
@@ -100,8 +114,96 @@ def cpu_reference_arm(wl, steps, warmup, heads_per_step=1):
 
 
 def legal_twin(wl):
-    ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
-    return WORKLOADS["720p_legal"] if ragged else wl
+    return WORKLOADS["720p_legal"] if is_ragged(wl) else wl
+
+
+class StepTimer:
+    """Times K eager calls of ``flash_attn_bsa_3d`` with an event between its two stages (bsa_interface.STAGE_HOOK)."""
+
+    def __init__(self, B, q, k, v, wl, params):
+        self.B, self.q, self.k, self.v, self.wl, self.params = B, q, k, v, wl, params
+        self.mids = []
+
+    def call(self):
+        return self.B.flash_attn_bsa_3d(self.q, self.k, self.v, self.wl.grid_q, self.wl.grid_k, **self.params)
+
+    def _hook(self):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.mids.append(ev)
+
+    def run(self, steps):
+        """-> (ms per step, ms of the block-select stage, ms of the attention launch), means over the steps."""
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        self.mids = []
+        self.B.STAGE_HOOK = self._hook
+        try:
+            torch.cuda.synchronize()
+            marks[0].record()
+            for i in range(steps):
+                self.call()
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+        finally:
+            self.B.STAGE_HOOK = None
+        ms = marks[0].elapsed_time(marks[steps]) / steps
+        ms_sel = statistics.mean(marks[i].elapsed_time(self.mids[i]) for i in range(steps))
+        ms_att = statistics.mean(self.mids[i].elapsed_time(marks[i + 1]) for i in range(steps))
+        return ms, ms_sel, ms_att
+
+    def run_graph(self, steps):
+        """The same call captured once in a CUDA graph and replayed; None if capture is not possible."""
+        try:
+            cap = torch.cuda.Stream()
+            cap.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=cap):
+                self.call()
+            torch.cuda.current_stream().wait_stream(cap)
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / steps
+        except Exception:  # noqa: BLE001 - a side figure only
+            torch.cuda.synchronize()
+            return None
+
+
+def gpu_reference_leg(wl, q, k, v, params, flops, steps=5, warmup=2):
+    """The reference's Triton BSA on this GPU, same inputs: ms per layer of its ``flash_attn_bsa_3d`` (gating,
+    rearranges and kernel, as the DiT calls it).  Its prints are sent to stderr so that stdout stays one JSON line."""
+    if is_ragged(wl):
+        return {"unavailable": "the reference asserts on grids that do not divide by the block (bsa_interface.py:639-640)"}
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_gpu as R
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"baseline/reference_gpu.py: {e!r}"[:200]}
+    with contextlib.redirect_stdout(sys.stderr):
+        if R.load() is None:
+            return {"unavailable": R.why(), **R.versions()}
+        try:
+            for _ in range(warmup):
+                out = R.flash_attn_bsa_3d(q, k, v, wl.grid_q, wl.grid_k, **params)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                out = R.flash_attn_bsa_3d(q, k, v, wl.grid_q, wl.grid_k, **params)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            del out
+        except Exception as e:  # noqa: BLE001 - e.g. a Triton construct this Triton version no longer compiles
+            torch.cuda.synchronize()
+            return {"unavailable": f"the reference failed on this box: {e!r}"[:400], **R.versions()}
+    return {"ms_per_step": ms, "tflops": flops / ms / 1e9, "steps": steps, "what": "reference flash_attn_bsa_3d (Triton), same inputs",
+            **R.versions()}
 
 
 def main():
@@ -112,9 +214,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="720p_legal", choices=sorted(WORKLOADS))
     ap.add_argument("--heads", type=int, default=None, help="total heads (default: the workload's 32)")
-    ap.add_argument("--attn-impl", default="auto", choices=["auto", "tc", "mma"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-literal", action="store_true", help="no extra leg on the literal 24x45x80 grid")
+    ap.add_argument("--skip-gpu-reference", action="store_true", help="do not time the reference's Triton kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -147,82 +250,86 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    attn_impl = {"auto": L.ATTN_AUTO, "tc": L.ATTN_TC, "mma": L.ATTN_MMA}[args.attn_impl]
     peaks, peak_src = load_peaks()
 
     if world > 1:
-        from longcat_video_b200.context_parallel import bench_support
-        return bench_support.run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src, attn_impl)
+        import bench_multi_gpu
+        return bench_multi_gpu.run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src)
 
     # ------------------------------------------------------------------ single GPU
     q_h, k_h, v_h = (t.pin_memory() for t in make_qkv(wl, heads=heads))
     q, k, v = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h))
-    scale = wl.head_dim ** -0.5
-    launches = {"n": 0}
-
-    def step(events=None):
-        if events:
-            events[0].record()
-        idx, cnt = B.get_select_indices(q, k, wl.grid_q, wl.grid_k, wl.sparsity, None, wl.chunk, wl.chunk)
-        if events:
-            events[1].record()
-        out = B.attn_fwd_bsa_varlen(q, k, v, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk, impl=attn_impl)
-        if events:
-            events[2].record()
-        launches["n"] += 5  # pool(q), pool(k), score GEMM, top-k, attention
-        return idx, cnt, out
+    params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
+    ragged = is_ragged(wl)
+    timer = StepTimer(B, q, k, v, wl, dict(params, allow_ragged=ragged))
+    launches_per_step = 5  # pool(q), pool(k), score GEMM, top-k, attention
 
     for _ in range(args.warmup):
-        idx, cnt, out = step()
+        timer.call()
     torch.cuda.synchronize()
     L.check(L.lib().lcbsa_check_device_status())
+    idx, cnt = B.get_select_indices(q, k, wl.grid_q, wl.grid_k, wl.sparsity, None, wl.chunk, wl.chunk)
     nsel = int(cnt.flatten()[0])
     flops = algorithmic_flops(wl, heads, nsel)
     if flops is None:
         flops = flops_from_lists(wl, idx, cnt)
+    del idx, cnt
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches["n"] = 0
-    torch.cuda.synchronize()
-    start.record()
-    for i in range(args.steps):
-        step(ev[i])
-    end.record()
-    torch.cuda.synchronize()
+    ms, ms_select, ms_attn = timer.run(args.steps)
     clocks = sampler.stop()
     L.check(L.lib().lcbsa_check_device_status())
-    ms = start.elapsed_time(end) / args.steps
-    ms_select = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    ms_attn = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    gpu_launches = launches["n"]
+    gpu_launches = launches_per_step * args.steps
+    ms_graph = timer.run_graph(args.steps)
 
     es = q.element_size()
     select_bytes = es * wl.batch * heads * (wl.sq + wl.sk) * wl.head_dim  # read Q and K once
     attn_io_bytes = es * wl.batch * heads * (2 * wl.sq + 2 * wl.sk) * wl.head_dim  # q, out, k, v once
     attn_tf = flops / ms_attn / 1e9
-    roofline = {"bound": "tensor", "kernel": "attn_tc_kernel" if attn_impl != L.ATTN_MMA else "attn_mma_kernel",
+    roofline = {"bound": "tensor", "kernel": "attn_tc_kernel",
                 "achieved": attn_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
                 "peak_source": f"{peak_src} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
                 "ms_per_launch": ms_attn,
-                "traffic": (NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes) if attn_impl != L.ATTN_MMA else None,
+                "traffic": NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes,
                 "traffic_source": "ncu capture of 480p_legal/16 heads scaled by the bytes of q,k,v,out"}
     sel_gbs = select_bytes / ms_select / 1e6
     roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_gemm_kernel + topk_rows_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
                        "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"], "peak_source": peak_src, "ms_per_stage": ms_select,
                        "traffic": NCU_SELECT_DRAM_PER_IO_BYTE * select_bytes}
 
+    # ------------------------------------------------------------------ BASELINE's literal 720p grid (ragged), short leg
+    literal = None
+    if wl.name == "720p_legal" and not args.skip_literal:
+        lw = WORKLOADS["720p_ragged"]
+        lq, lk, lv = (t.to(dev) for t in make_qkv(lw, heads=heads))
+        lt = StepTimer(B, lq, lk, lv, lw, dict(params, allow_ragged=True))
+        for _ in range(3):
+            lt.call()
+        li, lc = B.get_select_indices(lq, lk, lw.grid_q, lw.grid_k, lw.sparsity, None, lw.chunk, lw.chunk)
+        lflops = flops_from_lists(lw, li, lc)
+        lms, lms_sel, lms_att = lt.run(5)
+        L.check(L.lib().lcbsa_check_device_status())
+        literal = {"workload": lw.name, "grid": list(lw.grid_k), "steps": 5, "ms_per_step": lms, "ms_select": lms_sel, "ms_attention": lms_att,
+                   "algorithmic_tflop": lflops / 1e12, "value": lflops / lms / 1e9, "attention_tflops": lflops / lms_att / 1e9,
+                   "attention_frac_of_peak": lflops / lms_att / 1e9 / peaks["bf16_tflops"],
+                   "note": "extension: ragged grid through allow_ragged=True, flops counted on present rows and keys only"}
+        del lq, lk, lv, lt, li, lc
+
+    # ------------------------------------------------------------------ the reference's Triton kernels on this GPU
+    gpu_reference = None
+    if not args.skip_gpu_reference:
+        gpu_reference = gpu_reference_leg(wl, q, k, v, params, flops)
+        if "ms_per_step" in gpu_reference:
+            gpu_reference["speedup_of_this_library"] = gpu_reference["ms_per_step"] / ms
+
     # ------------------------------------------------------------------ end to end from host buffers
     e2e = None
     if not args.skip_e2e:
         out_h = torch.empty(q_h.shape, dtype=q_h.dtype).pin_memory()
-        params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
-        ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
 
         def e2e_step():
-            # host tensors in, host tensor out: copies and kernels pipelined by chunks of four heads
+            # host tensors in, host tensor out: copies and kernels pipelined by chunks of two heads
             B.flash_attn_bsa_3d_host(q_h, k_h, v_h, wl.grid_q, wl.grid_k, out=out_h, heads_per_chunk=2,
                                      allow_ragged=ragged, **params)
 
@@ -251,9 +358,11 @@ def main():
             "config": {"workload": wl.name, "grid_q": list(wl.grid_q), "grid_k": list(wl.grid_k), "heads": heads,
                        "head_dim": wl.head_dim, "block": list(wl.chunk), "sparsity": wl.sparsity, "selected_blocks": nsel,
                        "algorithmic_tflop": flops / 1e12, "ms_select": ms_select, "ms_attention": ms_attn,
-                       "l2": "inputs (q,k,v,out) exceed the 126 MB L2; no flush between iterations", "parallelism": "1 GPU"},
+                       "timed_call": "flash_attn_bsa_3d, eager", "ms_per_step_cuda_graph": ms_graph,
+                       "l2": "inputs (q,k,v,out) exceed the 126 MB L2; no flush between iterations", "parallelism": "1 GPU",
+                       "literal_720p": literal},
             "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "clocks": clocks, "gpu_launches": gpu_launches}
+            "gpu_reference": gpu_reference, "clocks": clocks, "gpu_launches": gpu_launches}
     print(json.dumps(line))
 
 

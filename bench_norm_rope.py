@@ -1,6 +1,6 @@
 """Times the fused q/k RMSNorm + 3-D rotary kernel on one GPU and prints one JSON line with its HBM roofline.
 
-    python -m longcat_video_b200.modules.bench_norm_rope [--grid 24 48 80] [--heads 32] [--head-dim 128] [--steps 20] [--warmup 3]
+    python bench_norm_rope.py [--grid 24 48 80] [--heads 32] [--head-dim 128] [--steps 20] [--warmup 3]
 
 A step is the producer of one attention layer: q and k of the fused qkv projection ([B, S, 3, H, D], read through
 their strided views) -> two dense [B, H, S, D] outputs, two launches.  Algorithmic bytes per element: 2 read +
@@ -13,9 +13,13 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
 
-from . import rope_3d as R
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from longcat_video_b200.modules import rope_3d as R  # noqa: E402
 
 # DRAM bytes per algorithmic byte of one launch, from the ncu capture of this kernel at 8 heads of the same grid
 # (188.9 MB read + 142.3 MB written for 377.5 MB); both grow in proportion to the number of heads.
@@ -24,7 +28,7 @@ NCU_DRAM_PER_IO_BYTE = 331.2 / 377.5
 
 def _peak_gbs():
     here = os.path.dirname(os.path.abspath(__file__))
-    path = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    path = os.path.join(here, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"

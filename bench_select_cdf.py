@@ -1,6 +1,6 @@
 """Times the cdf_threshold selector (score_gemm_kernel + cdf_rows kernel) on one GPU and prints one JSON line.
 
-    python -m longcat_video_b200.block_sparse_attention.bench_select_cdf [--blocks 1440] [--heads 32] [--threshold 0.5]
+    python bench_select_cdf.py [--blocks 1440] [--heads 32] [--threshold 0.5]
 
 A step is the selection of one attention layer from pooled rows ([1, H, N, 128] bf16, seeded random): N x N block
 scores per head, then per row softmax, sort, running sum and count.  Algorithmic bytes of the row kernel: 2 read +
@@ -13,9 +13,13 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
 
-from . import bsa_interface as B
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from longcat_video_b200.block_sparse_attention import bsa_interface as B  # noqa: E402
 
 
 def main():
@@ -45,7 +49,7 @@ def main():
     scores = float(H) * N * N
     here = os.path.dirname(os.path.abspath(__file__))
     try:
-        with open(os.path.join(here, "..", "..", "MEASURED_PEAKS.json")) as f:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
             peak, which = float(json.load(f)["hbm_gbs"]), "measured"
     except (OSError, KeyError, ValueError):
         peak, which = 6650.0, "fallback"

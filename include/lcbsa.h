@@ -29,7 +29,8 @@ enum {
     LCBSA_EUNSUPPORTED = -2, /* valid request that no kernel here covers */
     LCBSA_EWORKSPACE = -3,   /* workspace smaller than lcbsa_*_workspace_bytes() says */
     LCBSA_ECUDA = -4,        /* a CUDA runtime / driver call failed */
-    LCBSA_EDEVICE = -5       /* a kernel gave up on a bounded wait and flagged it */
+    LCBSA_EDEVICE = -5       /* a kernel flagged a problem it met on the device: a bounded wait that ran out,
+                                or a block list entry outside [0, Nk) (lcbsa_check_device_status) */
 };
 
 enum { LCBSA_BF16 = 0, LCBSA_FP16 = 1, LCBSA_FP32 = 2 };
@@ -128,7 +129,10 @@ int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGr
  * Stands in for the three rearrange_THW_to_3d_block copies, attn_fwd_bsa_varlen_triton and
  * rearrange_3d_block_to_THW (bsa_interface.py:650-659, 290-341) and the Triton kernels
  * _attn_fwd_bsa_varlen_align / _attn_fwd_bsa_varlen (flash_attn_bsa_varlen_mask.py:172-285, 35-153).
- * idx: int32 [B*H, Nq, cap], cnt: int32 [B*H, Nq] (entries beyond cnt are ignored).
+ * idx: int32 [B*H, Nq, cap], cnt: int32 [B*H, Nq] (entries beyond cnt are ignored; cnt is clamped to [0, cap]).
+ *      An entry outside [0, Nk) is never turned into an address: the generic kernel skips that block, the tcgen05
+ *      kernel reads zeros for it; either way the device status is flagged (lcbsa_check_device_status returns
+ *      LCBSA_EDEVICE naming the entry) and the rows of that query block are finite but unspecified.
  * out: [B, H, Sq, D], dtype of q.   lse: nullable, fp32 dense [B*H, Sq], natural log.
  * impl: LCBSA_ATTN_*.
  */
@@ -212,7 +216,8 @@ int lcbsa_copy_slabs(void* const* dst, const void* const* src, size_t nbytes, in
 
 /*
  * Synchronise the current device and report whether any kernel of this library flagged a
- * bounded wait that ran out since the last call (LCBSA_EDEVICE), clearing the flag.
+ * bounded wait that ran out or a block list entry outside the key grid since the last call
+ * (LCBSA_EDEVICE), clearing the flag.
  * Debug aid for tests; not part of the hot path.
  */
 int lcbsa_check_device_status(void);

@@ -22,6 +22,11 @@ import torch
 from .. import _lib as L
 
 
+# A callable that ``flash_attn_bsa_3d`` invokes between its two stages (block-select done, attention not yet
+# launched); a profiler or a benchmark sets it to record a CUDA event there.  None: nothing happens.
+STAGE_HOOK = None
+
+
 def _prod(x: Sequence[int]) -> int:
     return int(x[0]) * int(x[1]) * int(x[2])
 
@@ -194,6 +199,8 @@ def flash_attn_bsa_3d(
 
     idx, cnt = get_select_indices(q, k, latent_shape_q, latent_shape_k, sparsity, cdf_threshold,
                                   chunk_3d_shape_q, chunk_3d_shape_k)
+    if STAGE_HOOK is not None:
+        STAGE_HOOK()
     return attn_fwd_bsa_varlen(q, k, v, 1 / head_dim ** 0.5, idx, cnt, latent_shape_q, latent_shape_k,
                                chunk_3d_shape_q, chunk_3d_shape_k)
 
@@ -254,6 +261,7 @@ def flash_attn_bsa_3d_host(q, k, v, latent_shape_q, latent_shape_k, out=None, he
     independent, so the call is pipelined by chunks of ``heads_per_chunk`` heads over three streams: while the
     kernels work on chunk c, the copy engines bring in chunk c+1 and take the result of chunk c-1 back, through two
     device staging buffers per tensor.  End to end the call then costs about what moving the bytes over PCIe costs.
+    The call returns when the result is complete in ``out``: no further synchronisation is needed to read it.
     """
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise RuntimeError("flash_attn_bsa_3d_host takes host tensors; use flash_attn_bsa_3d for device tensors")
@@ -305,4 +313,8 @@ def flash_attn_bsa_3d_host(q, k, v, latent_shape_q, latent_shape_k, out=None, he
             out[:, lo:hi].copy_(o, non_blocking=True)
     main.wait_stream(d2h)
     main.wait_stream(h2d)
+    # The result is host memory: the caller may read it (and reuse q, k, v) as soon as this returns, so the host
+    # itself waits for the copies here; ordering the streams alone would not cover a CPU reader.
+    d2h.synchronize()
+    h2d.synchronize()
     return out

@@ -153,6 +153,15 @@ class PeerExchange:
         # call's exchange is already writing
         self.extra_off = 3 * self.in_elems + 2 * out_elems  # `extra_elems` more for the caller (pooled rows)
         self.ar.ensure(self.extra_off + extra_elems)
+        # The regions are laid out from this call's shape.  The argument that a call cannot overwrite what the
+        # previous one is still using (two alternating result regions, receive regions guarded by the previous call's
+        # barriers) holds between calls of ONE layout; when the layout changes, every rank first finishes what it has
+        # queued and the group meets, exactly as when the buffer grows.
+        layout = (H, Sl, D, int(extra_elems))
+        if getattr(self.ar, "_layout", layout) != layout:
+            torch.cuda.synchronize(query.device)
+            dist.barrier(group=group)
+        self.ar._layout = layout
         calls = getattr(self.ar, "_calls", 0)
         self.ar._calls = calls + 1
         self.out_off = 3 * self.in_elems + (calls & 1) * out_elems

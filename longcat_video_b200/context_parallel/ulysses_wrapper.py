@@ -333,16 +333,23 @@ def ulysses_wrapper(func):
                 ev = side.record_event()  # covers the self-slab copies, which ran on the side stream
             return fin, ev
 
-        out, pending_out = None, []
+        out, pending_out, done = None, [], []
         nxt = start_in(*stages[0])
         for g, (lo, hi) in enumerate(stages):
             cur = nxt
             if g + 1 < len(stages):
+                # The receive buffers of stage g+1 come from the caching allocator of `main` and may be blocks that
+                # stage g-1 (its q, k, v, its block lists and workspaces) has just given back while its kernels are
+                # still queued on `main`; the exchange fills them from `side`, so `side` first waits for those kernels.
+                if side is not None and done:
+                    side.wait_event(done[-1])
                 nxt = start_in(*stages[g + 1])
             q, k, v = cur[0]()
             if cur[1] is not None:
                 main.wait_event(cur[1])
             o = func(self, q, k, v, shape)
+            if main is not None:
+                done.append(main.record_event())
             if out is None:
                 out = torch.empty(B, H, o.shape[2] // n, o.shape[3], dtype=o.dtype, device=o.device)
             pending_out.append(seq_scatter_heads_gather(o, group, out=out, head_lo=lo, heads_per_rank=hn, async_op=True))

@@ -318,6 +318,10 @@ int lcbsa_check_device_status(void) {
     if (h[0] != 0) {
         unsigned int z[4] = {0, 0, 0, 0};
         cudaMemcpyToSymbol(g_device_status, z, sizeof(z));
+        if (h[0] == lcbsa::kStatusBadBlockIndex)
+            return fail(LCBSA_EDEVICE, "attn_fwd: block list entry outside [0, Nk) at (batch*head %u, query block %u, position %u); "
+                        "the entry was not dereferenced, the rows of that query block are unspecified", h[1], h[2], h[3]);
+        if (h[0] == 1u) return fail(LCBSA_EDEVICE, "attn_fwd: dynamic shared memory base not 1024-byte aligned (CTA %u)", h[1]);
         return fail(LCBSA_EDEVICE, "a kernel gave up on a bounded wait: code %u at (%u, %u, %u)", h[0], h[1], h[2], h[3]);
     }
     return LCBSA_OK;

@@ -77,7 +77,10 @@ __device__ __forceinline__ void load_tile(unsigned char* tile, const T* head_bas
                                           const SlotEntry* tab, int blk, int slot0, int tid) {
     constexpr int CPR = D * 2 / 16;  // 16-byte chunks per row
     int bt, bh, bw;
-    block_coords(g, blk, bt, bh, bw);
+    // a block number outside the grid (a caller's list may hold anything) is never turned into an address:
+    // the whole tile is zero-filled and the caller of load_tile masks the block out of the softmax
+    const bool blk_ok = (unsigned)blk < (unsigned)g.nblk;
+    block_coords(g, blk_ok ? blk : 0, bt, bh, bw);
     const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
     const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
     const uint32_t sbase = smem_u32(tile);
@@ -85,7 +88,7 @@ __device__ __forceinline__ void load_tile(unsigned char* tile, const T* head_bas
     for (int v = tid; v < ROWS * CPR; v += NTHREADS) {
         const int row = v / CPR, c = v % CPR;
         const SlotEntry e = tab[slot0 + row];
-        const bool present = !g.ragged || slot_present(g, e.packed, t0, h0, w0);
+        const bool present = blk_ok && (!g.ragged || slot_present(g, e.packed, t0, h0, w0));
         const T* src = head_base + (present ? (origin + e.off) * ss : 0) + c * 8;
         cp_async16(sbase + row * (D * 2) + ((c ^ (row & 7)) << 4), src, present);
     }
@@ -192,7 +195,16 @@ __global__ void __launch_bounds__(BQ * 2) attn_mma_kernel(AttnArgs a) {
             }
         }
 
-        if (gk.ragged) {  // absent keys of a partial block do not take part in the softmax
+        if ((unsigned)blk >= (unsigned)gk.nblk) {
+            // list entry outside [0, Nk): the block is skipped and the call is flagged (lcbsa_check_device_status)
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = -INFINITY;
+            if (tid == 0 && sub == 0 && atomicCAS(a.status, 0u, kStatusBadBlockIndex) == 0u) {
+                a.status[1] = bh;
+                a.status[2] = qb;
+                a.status[3] = (unsigned)(it / nsub);
+            }
+        } else if (gk.ragged) {  // absent keys of a partial block do not take part in the softmax
             int bt, bhh, bw;
             block_coords(gk, blk, bt, bhh, bw);
             const int t0 = bt * gk.ct, h0 = bhh * gk.ch, w0 = bw * gk.cw;

@@ -100,24 +100,7 @@ struct TcParams {
     Geom gq, gk;
     float scale2;   // sm_scale * log2(e)
     int is_bf16;
-#ifdef LCBSA_TC_DEBUG
-    float* dbg;     // [2 blocks][2 tiles][64 rows][64] raw S of the first work item's first two blocks
-    long long* ts;  // [4 roles][4096][2] (tag, clock64) timeline of CTA 0: PV issuer, S issuer, softmax warps 0 and 4
-#endif
 };
-
-#ifdef LCBSA_TC_DEBUG
-#define LCBSA_TS(role, tag)                                                        \
-    do {                                                                           \
-        if (P.ts && blockIdx.x == 0 && ts_n < 4096) {                              \
-            P.ts[((role) * 4096 + ts_n) * 2] = (tag);                              \
-            P.ts[((role) * 4096 + ts_n) * 2 + 1] = clock64();                      \
-            ++ts_n;                                                                \
-        }                                                                          \
-    } while (0)
-#else
-#define LCBSA_TS(role, tag) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------------------------------ PTX
 
@@ -375,9 +358,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same value, but provably warp-uniform
-#ifdef LCBSA_TC_DEBUG
-    int ts_n = 0;
-#endif
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -465,8 +445,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
             const int32_t* my_l = P.idx + ((long long)bh * P.nq + min(qa + my_t, P.nq - 1)) * P.cap;
             auto fetch = [&](int it) {
                 if (it >= my_c) return 0;
+                const int blk = my_l[it];
+                if ((unsigned)blk >= (unsigned)P.gk.nblk) {
+                    // A list entry outside [0, Nk) never becomes an address: its box is placed at w = W, wholly
+                    // outside the tensor map, so TMA fills the tile with zeros; the call is flagged.
+                    if (atomicCAS(P.status, 0u, kStatusBadBlockIndex) == 0u) {
+                        P.status[1] = bh;
+                        P.status[2] = qa + my_t;
+                        P.status[3] = it;
+                    }
+                    return P.gk.W;
+                }
                 int bt, bhh, bw;
-                block_coords(P.gk, my_l[it], bt, bhh, bw);
+                block_coords(P.gk, blk, bt, bhh, bw);
                 return ((bt * P.gk.ct) << 20) | ((bhh * P.gk.ch) << 10) | (bw * P.gk.cw);
             };
             int win = 0, prv = 0;
@@ -556,15 +547,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 const int wg = i & 1;
                 const unsigned rr = wg ? rr1 : rr0;
                 const int slot = gb % kKSlots, buf = rr & 1;
-                if (lane == 0) LCBSA_TS(1, 10000 + i);
                 if (!pre) {  // not already seen ready by the look-ahead of the block before
                     ok = mbar_wait_warp(bar_k_full(slot), (gb / kKSlots) & 1, ctl, 40, gb);
-                    if (lane == 0) LCBSA_TS(1, 20000 + i);
                     // the buffer held P of the warpgroup's round rr - 2: that PV has to be finished
                     if (ok) ok = mbar_wait_warp(bar_pv_done(wg, buf), ((rr >> 1) & 1) ^ 1, ctl, 34 + wg, rr);
                     if (!ok) break;
                 }
-                if (lane == 0) LCBSA_TS(1, 30000 + i);
                 // look ahead: probe the two barriers of the item's next block now, read the answer after the MMAs
                 bool nk = false, np = false;
                 if (i + 1 < n_iter) {
@@ -590,7 +578,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 tc_commit(bar_k_empty(slot));  // K is free once these MMAs have read it
                 tc_commit(bar_s_full(wg, buf));
                 if (i == n_iter - 1) tc_commit(bar_q_empty);  // and so is Q after the last S of the item
-                if (lane == 0) LCBSA_TS(1, 40000 + i);
                 if (wg) ++rr1; else ++rr0;
                 pre = __all_sync(0xffffffffu, nk && np);
             }
@@ -611,14 +598,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 const int wg = i & 1;
                 const unsigned rr = wg ? rr1 : rr0;
                 const int slot = gb % kVSlots, buf = rr & 1;
-                if (lane == 0) LCBSA_TS(0, 10000 + i);
                 if (!pre) {
                     ok = mbar_wait_warp(bar_v_full(slot), (gb / kVSlots) & 1, ctl, 60, gb);
-                    if (lane == 0) LCBSA_TS(0, 20000 + i);
                     if (ok) ok = mbar_wait_warp(bar_p_full(wg, buf), (rr >> 1) & 1, ctl, 50 + wg, rr);
                     if (!ok) break;
                 }
-                if (lane == 0) LCBSA_TS(0, 30000 + i);
                 bool nv = false, np = false;  // look ahead to the item's next block
                 if (i + 1 < n_iter) {
                     const int wg2 = wg ^ 1;
@@ -643,7 +627,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 // the V slot of the item's last block goes to the epilogue, which stages O in it and frees it
                 if (i < n_iter - 1) tc_commit(bar_v_empty(slot));
                 tc_commit(bar_pv_done(wg, buf));
-                if (lane == 0) LCBSA_TS(0, 40000 + i);
                 if (wg) ++rr1; else ++rr0;
                 pre = __all_sync(0xffffffffu, nv && np);
             }
@@ -708,18 +691,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 const bool active = i < my_cnt;
                 const int buf = rr & 1;
                 const unsigned bph = (rr >> 1) & 1;
-                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 10000 + i);
                 ok = mbar_wait_warp(bar_s_full(wg, buf), bph, ctl, 80 + wg, rr);
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t sr[64];
                 tc_ld64(tm_s + 64u * buf, sr);
                 tc_wait_ld();
-                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 20000 + i);
-#ifdef LCBSA_TC_DEBUG
-                if (P.dbg && w == 0 && i < 2)
-                    for (int j = 0; j < 64; ++j) P.dbg[((i * 2 + hf) * 64 + row) * 64 + j] = __uint_as_float(sr[j]);
-#endif
                 float alpha = 1.f;
                 bool need = false;
                 uint4 pk[8];  // this row of P in the input dtype, 8 keys per 16-byte chunk
@@ -779,7 +756,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                     l_sum = l_sum * alpha + rs;  // alpha is 1 unless this row's reference maximum moved
                 }
                 first = false;
-                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 30000 + i);
                 const bool any_need = __any_sync(0xffffffffu, need);
                 // O is rescaled only at rest: the warpgroup's PV of the round before has to be finished
                 // (need implies that this is not the warpgroup's first round of the item, so rr > 0)
@@ -814,7 +790,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive_elect(bar_p_full(wg, buf));
-                if (wq == 0 && lane == 0) LCBSA_TS(2 + wg, 40000 + i);
             }
             if (!ok) break;
             gb += n_iter;
@@ -934,7 +909,7 @@ int merge_mode(const View& v, int B, int H, const Geom& g) {
     return -1;
 }
 
-bool make_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, const Geom& g, int merge) {
+bool encode_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, const Geom& g, int merge) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t es = 2;
@@ -950,17 +925,50 @@ bool make_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, const Geo
     return r == CUDA_SUCCESS;
 }
 
-#ifdef LCBSA_TC_DEBUG
-float* g_tc_debug = nullptr;
-long long* g_tc_ts = nullptr;
-#endif
+// Tensor maps are a pure function of (pointer, dtype, strides, batch, heads, grid, block, fold mode); a DiT calls the
+// op with the same few buffers layer after layer, so the last encodings are kept per host thread and reused.
+struct MapKey {
+    const void* data;
+    long long sb, sh, ss;
+    int dtype, B, H, T, Hh, W, ct, ch, cw, merge;
+    bool operator==(const MapKey& o) const {
+        return data == o.data && sb == o.sb && sh == o.sh && ss == o.ss && dtype == o.dtype && B == o.B && H == o.H && T == o.T &&
+               Hh == o.Hh && W == o.W && ct == o.ct && ch == o.ch && cw == o.cw && merge == o.merge;
+    }
+};
+constexpr int kMapCache = 32;
+struct MapCache {
+    MapKey key[kMapCache];
+    CUtensorMap map[kMapCache];
+    int used = 0, next = 0;
+};
+
+bool make_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, const Geom& g, int merge) {
+    static thread_local MapCache cache;
+    const MapKey k{v.data, v.sb, v.sh, v.ss, dtype, B, H, g.T, g.H, g.W, g.ct, g.ch, g.cw, merge};
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == k) {
+            *tm = cache.map[i];
+            return true;
+        }
+    if (!encode_map(tm, dtype, v, B, H, g, merge)) return false;
+    const int slot = cache.next;
+    cache.key[slot] = k;
+    cache.map[slot] = *tm;
+    cache.next = (slot + 1) % kMapCache;
+    if (cache.used < kMapCache) ++cache.used;
+    return true;
+}
+
+// Per-device launch state: SM count, and whether the kernels' shared-memory limit has been raised on that device.
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    std::atomic<int> sm_count{0};
+    std::atomic<int> attr_set{0};  // bit 0: bf16 kernel, bit 1: fp16 kernel
+};
+DeviceState g_dev[kMaxDevices];
 
 }  // namespace
-
-#ifdef LCBSA_TC_DEBUG
-extern "C" void lcbsa_debug_set_buffer(float* p) { g_tc_debug = p; }
-extern "C" void lcbsa_debug_set_timeline(long long* p) { g_tc_ts = p; }
-#endif
 
 static std::atomic<int> g_sm_reserve{0};
 int set_attn_sm_reserve(int n_sms) { return g_sm_reserve.exchange(n_sms); }
@@ -988,7 +996,7 @@ bool attn_tc_supported(const AttnArgs& a, const char** why) {
 
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why) {
     if (a.gq.nblk == 0 || a.B * a.H == 0) return cudaSuccess;
-    static thread_local TcParams P;
+    TcParams P;
     const int mq = merge_mode(a.q, a.B, a.H, a.gq), mk = merge_mode(a.k, a.B, a.H, a.gk);
     const int mv = merge_mode(a.v, a.B, a.H, a.gk), mo = merge_mode(a.o, a.B, a.H, a.gq);
     if (!make_map(&P.tm_q, a.dtype, a.q, a.B, a.H, a.gq, mq) || !make_map(&P.tm_k, a.dtype, a.k, a.B, a.H, a.gk, mk) ||
@@ -1002,20 +1010,25 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
     P.gq = a.gq; P.gk = a.gk;
     P.scale2 = a.sm_scale * 1.4426950408889634f;
     P.is_bf16 = a.dtype == LCBSA_BF16;
-#ifdef LCBSA_TC_DEBUG
-    P.dbg = g_tc_debug;
-    P.ts = g_tc_ts;
-#endif
 
-    static int sm_count = 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) { *why = "device ordinal above 63"; return cudaErrorInvalidValue; }
+    DeviceState& ds = g_dev[dev];
+    int sm_count = ds.sm_count.load(std::memory_order_relaxed);
     if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        ds.sm_count.store(sm_count, std::memory_order_relaxed);
     }
     auto kern = P.is_bf16 ? attn_tc_kernel<true> : attn_tc_kernel<false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
+    const int bit = P.is_bf16 ? 1 : 2;
+    if (!(ds.attr_set.load(std::memory_order_relaxed) & bit)) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        ds.attr_set.fetch_or(bit, std::memory_order_relaxed);
+    }
     const long long groups = (a.gq.nblk + kTilesPerWork - 1) / kTilesPerWork;
     const long long work = groups * a.B * a.H;
     const int usable = sm_count - g_sm_reserve.load() > 0 ? sm_count - g_sm_reserve.load() : 1;

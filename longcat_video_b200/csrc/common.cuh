@@ -71,6 +71,10 @@ __device__ __forceinline__ void block_coords(const Geom& g, int blk, int& bt, in
     bt = q / g.Nh;
 }
 
+// Device status word [0]: 1 = shared memory base not 1024-byte aligned, 2 = a block list entry outside [0, Nk)
+// (words 1..3: batch*head, query block, list position), >= 10 = a bounded wait ran out (words 1..3: CTA, thread, iteration).
+constexpr unsigned kStatusBadBlockIndex = 2u;
+
 // Message returned by lcbsa_last_error() for the calling thread (api.cu owns the buffer).
 void set_last_error(const char* msg);
 

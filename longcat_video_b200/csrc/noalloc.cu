@@ -62,6 +62,12 @@ size_t lcbsa_static_scratch_bytes(void) { return kStaticScratchBytes; }
 int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel,
                               int cap, int32_t* idx, int32_t* cnt, void* stream) {
     char msg[256];
+    if (q && k)  // a malformed descriptor is an argument error, not a workspace error
+        for (int i = 0; i < 4; ++i)
+            if (q->size[i] < 0 || k->size[i] < 0) {
+                lcbsa::set_last_error("block_select_static: negative size in a tensor description");
+                return LCBSA_EINVAL;
+            }
     const size_t need = lcbsa_select_workspace_bytes(q, k, gq, gk);
     if (need == 0) {
         lcbsa::set_last_error("block_select_static: bad tensor or grid description");

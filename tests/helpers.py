@@ -18,11 +18,6 @@ def from_bits(arr, dtype):
     return torch.from_numpy(arr.copy())
 
 
-def sets_equal_modulo_ties(idx_a, idx_b, score_row_fn=None):
-    """True when two index lists select the same set."""
-    return sorted(int(x) for x in idx_a) == sorted(int(x) for x in idx_b)
-
-
 def rel_l2(a, b):
     a, b = a.double(), b.double()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
