@@ -264,6 +264,8 @@ def main():
     timer = StepTimer(B, q, k, v, wl, dict(params, allow_ragged=ragged))
     launches_per_step = 5  # pool(q), pool(k), score GEMM, top-k, attention
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # nvidia-smi needs a moment to start: long before the timed region
     for _ in range(args.warmup):
         timer.call()
     torch.cuda.synchronize()
@@ -275,9 +277,9 @@ def main():
         flops = flops_from_lists(wl, idx, cnt)
     del idx, cnt
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark_begin()
     ms, ms_select, ms_attn = timer.run(args.steps)
+    sampler.mark_end()
     clocks = sampler.stop()
     L.check(L.lib().lcbsa_check_device_status())
     gpu_launches = launches_per_step * args.steps

@@ -81,6 +81,21 @@ int lcbsa_num_selected(double sparsity, int n_k_blocks);
 int lcbsa_pool(const LcbsaTensor* x, const LcbsaGrid* g, void* out, void* stream);
 
 /*
+ * lcbsa_pool for q and k of a context-parallel rank in ONE launch, with the pooled rows stored where the block-select
+ * of the Ulysses-gathered tensors will read them: every rank of the group holds q, k as [1, H, S/N, D] (all heads, its
+ * own tokens; longcat_video/context_parallel/ulysses_wrapper.py:86-95 would all-to-all them), pools the 3-D blocks of
+ * ITS tokens for all heads and writes the rows of head h straight into the buffer of the rank that owns that head
+ * (rank h / (H/N)): dst_q[r], dst_k[r] are that rank's buffers (this GPU's memory or a peer's, mapped into this
+ * process), each [H/N][N source ranks][nblk][D] in the tensor dtype, and this call fills source slot `rank`.  Once
+ * every rank has made the call (and the group has synchronised), each buffer is the dense pooled tensor
+ * [H/N, N * nblk, D] of the gathered rank-major sequence.  The stores to peers are ordinary global stores issued by the
+ * kernel.  No counterpart in the reference, which exchanges the full tensors first and pools afterwards
+ * (bsa_interface.py:547-548).  Batch 1, up to 8 ranks.
+ */
+int lcbsa_pool_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk,
+                       void* const* dst_q, void* const* dst_k, int n_ranks, int rank, void* stream);
+
+/*
  * Block scores and per-row top-k from pooled tensors; the scores never reach HBM.
  * Stands in for cal_score + get_select_indices_topk_from_score (bsa_interface.py:180-184, 212-224).
  * q_cmp: dense [BH, Nq, D]; k_cmp: dense [BH, Nk, D]; dtype as given.

@@ -45,6 +45,8 @@ SIGNATURES = {
     "lcbsa_num_blocks": (ctypes.c_int, [_P(LcbsaGrid)]),
     "lcbsa_num_selected": (ctypes.c_int, [ctypes.c_double, ctypes.c_int]),
     "lcbsa_pool": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaGrid), ctypes.c_void_p, ctypes.c_void_p]),
+    "lcbsa_pool_scatter": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "lcbsa_score_topk": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_void_p]),

@@ -5,8 +5,9 @@
 then all-to-all back.  ``flash_attn_bsa_3d_ulysses`` computes the same result (bit for bit) in a different order:
 
   1. every rank mean-pools the 3-D blocks of ITS tokens for all heads (blocks never straddle ranks: the gathered
-     sequence is rank-major and the grid is split along T), and only the pooled rows -- 1/64 of the bytes --
-     are exchanged first;
+     sequence is rank-major and the grid is split along T); the pooling kernel stores each head's rows -- 1/64 of
+     the bytes -- straight into the memory of the rank that owns the head (``lcbsa_pool_scatter``), so the pooled
+     tensors of the gathered sequence exist after one kernel and one barrier, while the first q, k, v slabs travel;
   2. the block lists of all the rank's heads are selected in one launch while the first q, k, v slabs are still on
      their way;
   3. the attention runs stage by stage over head groups, each stage's q, k, v arriving by peer DMA during the stage
@@ -63,21 +64,19 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
         return _generic(q, k, v, latent_shape, params)
     main, side = ex.main, ex.side
 
-    # 1. pooled rows of this rank's tokens, all heads -> their owners
-    qc_l = B.mean_pooling_compression_3d(q, local_grid, chunk)  # [1, H, nblk_l, D]
-    kc_l = B.mean_pooling_compression_3d(k, local_grid, chunk)
-    pooled = main.record_event()
+    # 0. the first stage's q, k, v slabs start travelling at once (copy engines, side stream)
     side.wait_stream(main)
     if not torch.cuda.is_current_stream_capturing():
         for t in (q, k, v):
             t.record_stream(side)
-    ev_pooled = ex.push_rows((qc_l, kc_l), nblk_l, pooled)
     stages = U._stages(hn, U._heads_per_group(hn))
     ev = ex.push_in((q, k, v), *stages[0])
 
+    # 1. pooled rows of this rank's tokens, all heads, stored straight into their owners' memory; one barrier
+    ex.pool_scatter(q, k, local_grid, chunk, nblk_l)
+
     # 2. block lists of all local heads while the first slabs travel
-    main.wait_event(ev_pooled)
-    qc, kc = ex.rows_received(2, nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
+    qc, kc = ex.pooled_received(nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
     idx, cnt = B.get_select_indices_from_pooled(qc, kc, sparsity, None)
     scale = 1 / D ** 0.5
 
@@ -96,3 +95,66 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
     if os.environ.get("LCBSA_ULYSSES_ALIAS_OUT", "0") == "1":
         return ex.local_out
     return ex.local_out.clone()
+
+
+_HOST_STATE = {}
+
+
+def flash_attn_bsa_3d_ulysses_host(q, k, v, latent_shape, out=None, heads_per_chunk=None, device=None, **bsa_params):
+    """``flash_attn_bsa_3d_ulysses`` for shards that live in (pinned) HOST memory: ``q, k, v [1, H, S/N, D]`` on the host
+    in, this rank's ``[1, H, S/N, D]`` result on the host out (``out`` is filled and returned if given).
+
+    Heads are independent, so the call is pipelined by chunks of ``heads_per_chunk`` heads (a multiple of the group
+    size; default: a quarter of the heads): while the group works on chunk c, the copy engines bring chunk c+1 to the
+    device and take the result of chunk c-1 back.  Every rank must call it with the same chunking.  Extension without
+    counterpart in the reference, whose op takes device tensors.  Returns when the result is complete in ``out``."""
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise RuntimeError("flash_attn_bsa_3d_ulysses_host takes host tensors")
+    n = context_parallel_util.get_cp_size()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B_, H, Sl, D = q.shape
+    hc = H // 4 if heads_per_chunk is None else int(heads_per_chunk)
+    hc = max(n, (hc // n) * n)
+    if H % hc:
+        hc = H
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    key = (dev.index, B_, hc, Sl, D, q.dtype)
+    st = _HOST_STATE.get(key)
+    if st is None:
+        _HOST_STATE.clear()
+        st = {name: [torch.empty(B_, hc, Sl, D, dtype=q.dtype, device=dev) for _ in range(2)] for name in ("q", "k", "v")}
+        st["h2d"], st["d2h"] = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        _HOST_STATE[key] = st
+    main = torch.cuda.current_stream(dev)
+    h2d, d2h = st["h2d"], st["d2h"]
+    h2d.wait_stream(main)
+    d2h.wait_stream(main)
+    chunks = [(lo, lo + hc) for lo in range(0, H, hc)]
+    done = []
+
+    def bring(c):
+        lo, hi = chunks[c]
+        with torch.cuda.stream(h2d):
+            if c >= 2:
+                h2d.wait_event(done[c - 2])  # the kernels and pushes of chunk c-2 are through with this staging buffer
+            for name, src in (("q", q), ("k", k), ("v", v)):
+                st[name][c & 1].copy_(src[:, lo:hi], non_blocking=True)
+            return h2d.record_event()
+
+    arrived = [bring(0)]
+    for c, (lo, hi) in enumerate(chunks):
+        if c + 1 < len(chunks):
+            arrived.append(bring(c + 1))
+        main.wait_event(arrived[c])
+        o = flash_attn_bsa_3d_ulysses(st["q"][c & 1], st["k"][c & 1], st["v"][c & 1], latent_shape, **bsa_params)
+        done.append(main.record_event())
+        o.record_stream(d2h)
+        with torch.cuda.stream(d2h):
+            d2h.wait_event(done[c])
+            out[:, lo:hi].copy_(o, non_blocking=True)
+    main.wait_stream(d2h)
+    main.wait_stream(h2d)
+    d2h.synchronize()
+    h2d.synchronize()
+    return out

@@ -73,8 +73,10 @@ class PeerArena:
             return self.buf[offset:offset + n].view(shape)
         return self.hdl.get_buffer(rank, tuple(shape), self.dtype, offset)
 
-    def barrier(self) -> None:
-        self.hdl.barrier(channel=0)
+    def barrier(self, channel: int = 0) -> None:
+        """Barrier of the group on the current stream.  Barriers issued from different streams use different channels
+        (each channel has its own signal pad), so that they cannot be taken for one another."""
+        self.hdl.barrier(channel=channel)
 
 
 def arena(group, device: torch.device, dtype: torch.dtype) -> PeerArena:
@@ -198,6 +200,27 @@ class PeerExchange:
             self._L.check(self._L.lib().lcbsa_copy_slabs(base, base + m * ctypes.sizeof(ctypes.c_void_p), nbytes, m, stream.cuda_stream))
             if g > 0:
                 self.side.wait_event(stream.record_event())
+
+    def pool_scatter(self, q: torch.Tensor, k: torch.Tensor, local_grid, chunk, rows: int) -> None:
+        """Mean-pool the 3-D blocks of this rank's tokens of q and k (all heads) and store the rows of every head
+        straight into the extra region of the rank that owns the head (``lcbsa_pool_scatter``: one kernel, ordinary
+        stores to peer memory), then meet the group.  Runs on the CURRENT stream (barrier channel 1); when it has
+        passed, ``pooled_received`` holds the pooled q and k of the gathered sequence for this rank's heads."""
+        L = self._L
+        part_all = self.hn * self.n * rows * self.D  # one tensor's region: [H/N][N][rows][D]
+        dq = (ctypes.c_void_p * self.n)(*[self.bases[r] + self.extra_off * self.es for r in range(self.n)])
+        dk = (ctypes.c_void_p * self.n)(*[self.bases[r] + (self.extra_off + part_all) * self.es for r in range(self.n)])
+        qd, kd = L.tensor_desc(q), L.tensor_desc(k)
+        g = L.grid_desc(local_grid, chunk)
+        L.check(L.lib().lcbsa_pool_scatter(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(g), ctypes.byref(g), dq, dk, self.n, self.rank,
+                                           L.current_stream(q.device)))
+        self.ar.barrier(channel=1)
+
+    def pooled_received(self, rows: int) -> List[torch.Tensor]:
+        """Pooled q and k of the gathered rank-major sequence for this rank's heads, ``[1, H/N, N * rows, D]`` each:
+        views of the extra region as ``pool_scatter`` of all ranks filled it (no copy)."""
+        part_all = self.hn * self.n * rows * self.D
+        return [self.ar.view(self.rank, self.extra_off + t * part_all, (1, self.hn, self.n * rows, self.D)) for t in range(2)]
 
     def push_rows(self, tensors, rows: int, after: torch.cuda.Event) -> torch.cuda.Event:
         """Heads-scatter of small per-block tensors ``[1, H, rows, D]`` (the pooled Q and K of this rank's tokens)

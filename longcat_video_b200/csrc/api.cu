@@ -105,6 +105,39 @@ int lcbsa_pool(const LcbsaTensor* x, const LcbsaGrid* g, void* out, void* stream
     return LCBSA_OK;
 }
 
+int lcbsa_pool_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, void* const* dst_q,
+                       void* const* dst_k, int n_ranks, int rank, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "pool_scatter: bad grid");
+    if (int rc = check_tensor("q", q, gq)) return rc;
+    if (int rc = check_tensor("k", k, gk)) return rc;
+    if (q->dtype != k->dtype) return fail(LCBSA_EINVAL, "pool_scatter: q and k dtypes differ");
+    if (q->size[0] != 1 || k->size[0] != 1) return fail(LCBSA_EUNSUPPORTED, "pool_scatter: batch must be 1");
+    if (q->size[1] != k->size[1] || q->size[3] != k->size[3]) return fail(LCBSA_EINVAL, "pool_scatter: q and k disagree on heads or head_dim");
+    if (n_ranks < 1 || n_ranks > lcbsa::kPoolMaxDst) return fail(LCBSA_EUNSUPPORTED, "pool_scatter: 1..%d ranks", lcbsa::kPoolMaxDst);
+    if (rank < 0 || rank >= n_ranks) return fail(LCBSA_EINVAL, "pool_scatter: rank %d outside 0..%d", rank, n_ranks - 1);
+    if (q->size[1] % n_ranks != 0) return fail(LCBSA_EINVAL, "pool_scatter: %lld heads do not split over %d ranks", (long long)q->size[1], n_ranks);
+    if (!dst_q || !dst_k) return fail(LCBSA_EINVAL, "pool_scatter: null destination table");
+    const size_t es = elem_size(q->dtype);
+    const int lpr = (int)(q->size[3] * es / 16);
+    if (lpr < 1 || lpr > 32 || (lpr & (lpr - 1)) != 0)
+        return fail(LCBSA_EUNSUPPORTED, "pool_scatter: head_dim row of %d bytes is not 16..512 bytes and a power of two", (int)(q->size[3] * es));
+    lcbsa::PoolDst dq{}, dk{};
+    for (int r = 0; r < n_ranks; ++r) {
+        if (!dst_q[r] || !dst_k[r] || reinterpret_cast<uintptr_t>(dst_q[r]) % 16 || reinterpret_cast<uintptr_t>(dst_k[r]) % 16)
+            return fail(LCBSA_EINVAL, "pool_scatter: destination %d is null or not 16-byte aligned", r);
+        dq.dst[r] = dst_q[r];
+        dk.dst[r] = dst_k[r];
+    }
+    dq.n_dst = dk.n_dst = n_ranks;
+    dq.heads_per_dst = dk.heads_per_dst = (int)(q->size[1] / n_ranks);
+    dq.src_rank = dk.src_rank = rank;
+    const lcbsa::Geom ggq = lcbsa::make_geom(*gq), ggk = lcbsa::make_geom(*gk);
+    const lcbsa::View vq = view_of(q), vk = view_of(k);
+    cudaError_t e = lcbsa::launch_pool2(q->dtype, vq, ggq, dq, &vk, &ggk, &dk, 1, (int)q->size[1], (int)q->size[3], static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "pool_scatter", nullptr);
+    return LCBSA_OK;
+}
+
 int lcbsa_score_topk(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, int nsel, int cap,
                      int32_t* idx, int32_t* cnt, void* stream) {
     if (!q_cmp || !k_cmp || !idx || !cnt) return fail(LCBSA_EINVAL, "score_topk: null pointer");
@@ -176,8 +209,18 @@ int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGr
     const size_t bhd = (size_t)q->size[0] * (size_t)q->size[1] * (size_t)q->size[3] * es;
     unsigned char* qc = static_cast<unsigned char*>(workspace);
     unsigned char* kc = qc + (bhd * ggq.nblk + 255) / 256 * 256;
-    if (int rc = lcbsa_pool(q, gq, qc, stream)) return rc;
-    if (int rc = lcbsa_pool(k, gk, kc, stream)) return rc;
+    {   // pooled Q and pooled K in one launch
+        const int lpr = (int)(q->size[3] * es / 16);
+        if (lpr < 1 || lpr > 32 || (lpr & (lpr - 1)) != 0)
+            return fail(LCBSA_EUNSUPPORTED, "pool: head_dim row of %d bytes is not 16..512 bytes and a power of two", (int)(q->size[3] * es));
+        lcbsa::PoolDst dq{}, dk{};
+        dq.dst[0] = qc;
+        dk.dst[0] = kc;
+        const lcbsa::View vq = view_of(q), vk = view_of(k);
+        cudaError_t e = lcbsa::launch_pool2(q->dtype, vq, ggq, dq, &vk, &ggk, &dk, (int)q->size[0], (int)q->size[1], (int)q->size[3],
+                                            static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_fail(e, "pool", nullptr);
+    }
     // With room for the score keys the scores are computed by the register-tiled GEMM kernel and selected by a second
     // kernel; otherwise by the fused kernel that keeps them in shared memory.
     const size_t fast = lcbsa_select_workspace_bytes_fast(q, k, gq, gk);

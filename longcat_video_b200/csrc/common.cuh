@@ -80,6 +80,17 @@ void set_last_error(const char* msg);
 
 // Launchers implemented in the .cu files (host side). All return a cudaError_t from the launch.
 cudaError_t launch_pool(int dtype, const View& x, int B, int H, int D, const Geom& g, void* out, cudaStream_t st);
+// One launch that pools one or two tensors (x1 may be null).  Each has its destination: dense rows at dst[0], or rows
+// scattered by head over up to kPoolMaxDst buffers (see pool.cu).
+constexpr int kPoolMaxDst = 8;
+struct PoolDst {
+    void* dst[kPoolMaxDst];
+    int n_dst;          // 0: dense [B*H, nblk, D] at dst[0]
+    int heads_per_dst;  // scatter: heads per destination buffer
+    int src_rank;       // scatter: which source slot of the destination layout this call fills
+};
+cudaError_t launch_pool2(int dtype, const View& x0, const Geom& g0, const PoolDst& d0, const View* x1, const Geom* g1, const PoolDst* d1,
+                         int B, int H, int D, cudaStream_t st);
 
 // two-kernel form of the same stage (select_gemm.cu): bytes of key workspace it needs (0: does not apply) and launch
 size_t score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D);
