@@ -156,6 +156,21 @@ int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor
                    const LcbsaTensor* out, float* lse, int impl, void* stream);
 
 /*
+ * lcbsa_attn_fwd for a context-parallel rank, with the return all-to-all folded into the kernel's output stores
+ * (tcgen05 kernel: head_dim 128, 64-token blocks, bf16/fp16, batch 1, grid divisible by the block).  q, k, v are the
+ * rank's heads of the Ulysses-gathered tensors, [1, h, S, D] over the rank-major grid gq (frames
+ * [r * T/n, (r+1) * T/n) are the tokens of rank r; longcat_video/modules/attention.py:60-66).  Instead of writing
+ * [1, h, S, D] and exchanging it back (ulysses_a2a_out, longcat_video/context_parallel/ulysses_wrapper.py:98-105), the
+ * rows of rank r's tokens are stored straight into out_dst[r]: that rank's result for these h heads, a [1, h, S/n, D]
+ * tensor (this GPU's memory or a peer's, mapped into this process) with the given head and token strides in
+ * elements, head_dim contiguous.  The stores are TMA stores issued by the kernel; no load ever touches peer memory.
+ * The caller synchronises the group before any rank reads its result.  No counterpart in the reference.
+ */
+int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaGrid* gq,
+                           const LcbsaGrid* gk, const int32_t* idx, const int32_t* cnt, int cap, float sm_scale,
+                           void* const* out_dst, int n_dst, int64_t out_head_stride, int64_t out_token_stride, void* stream);
+
+/*
  * lcbsa_block_select for callers that cannot allocate device memory for the workspace (a frozen
  * memory pool, a plugin that only receives its input and output buffers, code that must not touch the
  * CUDA allocator).  No counterpart in the reference: there the workspace is whatever PyTorch allocates.

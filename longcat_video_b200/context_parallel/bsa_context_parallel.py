@@ -18,12 +18,69 @@ launches.  It falls back to ``ulysses_wrapper(flash_attn_bsa_3d)`` whenever its 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
 from ..block_sparse_attention import bsa_interface as B
 from . import context_parallel_util, peer_exchange
 from . import ulysses_wrapper as U
+
+
+_PHASES = os.environ.get("LCBSA_CP_PHASES", "0") == "1"
+_SCATTER_OUT = os.environ.get("LCBSA_CP_SCATTER_OUT", "1") == "1"
+
+
+class _PhaseTimer:
+    """CUDA events between the phases of a call on the main stream (LCBSA_CP_PHASES=1, for profiling).  Nothing is
+    synchronised while calls run; ``phase_report()`` reads the events of all calls made so far."""
+    calls = []
+
+    def __init__(self, stream):
+        self.stream, self.names, self.events = stream, [], [stream.record_event(torch.cuda.Event(enable_timing=True))]
+        _PhaseTimer.calls.append(self)
+
+    def mark(self, name):
+        self.names.append(name)
+        self.events.append(self.stream.record_event(torch.cuda.Event(enable_timing=True)))
+
+
+def phase_report(skip: int = 0) -> str:
+    """Mean milliseconds per phase over the recorded calls (the first ``skip`` left out), plus the mean distance between
+    the starts of consecutive calls; clears the record."""
+    torch.cuda.synchronize()
+    calls = _PhaseTimer.calls[skip:]
+    _PhaseTimer.calls = []
+    if not calls:
+        return "no calls recorded"
+    names = calls[0].names
+    means = [sum(c.events[i].elapsed_time(c.events[i + 1]) for c in calls) / len(calls) for i in range(len(names))]
+    total = sum(c.events[0].elapsed_time(c.events[-1]) for c in calls) / len(calls)
+    period = (calls[0].events[0].elapsed_time(calls[-1].events[0]) / (len(calls) - 1)) if len(calls) > 1 else float("nan")
+    return ", ".join(f"{n} {m:.3f}" for n, m in zip(names, means)) + f", total {total:.3f}, period {period:.3f} ms over {len(calls)} calls"
+
+
+def _stages_scattered(hn: int):
+    """Head ranges of the attention stages when the result leaves through the kernel's own stores: only the FIRST stage
+    has to be small (its q, k, v slabs are the ones nothing can hide); every further launch costs a pipeline fill and a
+    tail, and a head's slabs arrive two to three times faster than its attention runs, so the rest goes in at most two
+    large stages."""
+    if "LCBSA_ULYSSES_GROUP_HEADS" in os.environ:
+        return U._stages(hn, U._heads_per_group(hn))
+    if hn <= 1:
+        sizes = [hn]
+    elif hn <= 4:
+        sizes = [1, hn - 1]
+    elif hn <= 8:
+        sizes = [1, 3, hn - 4]
+    else:
+        sizes = [2, 6, hn - 8]
+    out, lo = [], 0
+    for sz in sizes:
+        out.append((lo, lo + sz))
+        lo += sz
+    return out
 
 
 def _generic(q, k, v, latent_shape, params):
@@ -64,34 +121,53 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
         return _generic(q, k, v, latent_shape, params)
     main, side = ex.main, ex.side
 
-    # 0. the first stage's q, k, v slabs start travelling at once (copy engines, side stream)
     side.wait_stream(main)
     if not torch.cuda.is_current_stream_capturing():
         for t in (q, k, v):
             t.record_stream(side)
-    stages = U._stages(hn, U._heads_per_group(hn))
-    ev = ex.push_in((q, k, v), *stages[0])
+    scatter = _SCATTER_OUT and D == 128 and chunk[0] * chunk[1] * chunk[2] == 64
+    stages = _stages_scattered(hn) if scatter else U._stages(hn, U._heads_per_group(hn))
+    phases = _PhaseTimer(main) if _PHASES else None
 
     # 1. pooled rows of this rank's tokens, all heads, stored straight into their owners' memory; one barrier
     ex.pool_scatter(q, k, local_grid, chunk, nblk_l)
+    if phases:
+        phases.mark("pool_scatter+barrier")
 
-    # 2. block lists of all local heads while the first slabs travel
+    # 2. every stage's q, k, v slabs are queued on the copy engines at once (side stream, one barrier per stage): the
+    #    receive regions of the stages are disjoint and nothing but the inputs is needed to fill them, so the slabs of
+    #    later stages travel while the block lists are selected and the earlier stages compute
+    evs = [ex.push_in((q, k, v), lo, hi) for lo, hi in stages]
+
+    # 3. block lists of all local heads while the first slabs travel
     qc, kc = ex.pooled_received(nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
     idx, cnt = B.get_select_indices_from_pooled(qc, kc, sparsity, None)
+    if phases:
+        phases.mark("select")
     scale = 1 / D ** 0.5
 
-    # 3. attention by head group
+    # 4. attention by head group.  The kernel stores every query block's rows straight into the result buffer of the
+    #    rank that owns those tokens (the return all-to-all folded into the output stores); one barrier at the end.
+    #    LCBSA_CP_SCATTER_OUT=0: the kernel writes a local [1, h, S, D] tensor and the copy engines take it back.
     ev_out = None
     for g, (lo, hi) in enumerate(stages):
-        main.wait_event(ev)
+        main.wait_event(evs[g])
+        if phases:
+            phases.mark(f"wait_slabs_{g}")
         q_, k_, v_ = ex.received(lo, hi)
-        o = B.attn_fwd_bsa_varlen(q_, k_, v_, scale, idx[:, lo:hi], cnt[:, lo:hi], latent_shape, latent_shape, chunk, chunk)
-        ev_next = ex.push_in((q, k, v), *stages[g + 1]) if g + 1 < len(stages) else None
-        ev_out = ex.push_out(o, lo)
-        ev = ev_next
-    main.wait_event(ev_out)
-    import os
-
+        if scatter:
+            ex.attn_scatter(q_, k_, v_, scale, idx[:, lo:hi], cnt[:, lo:hi], latent_shape, chunk, lo)
+        else:
+            o = B.attn_fwd_bsa_varlen(q_, k_, v_, scale, idx[:, lo:hi], cnt[:, lo:hi], latent_shape, latent_shape, chunk, chunk)
+            ev_out = ex.push_out(o, lo)
+        if phases:
+            phases.mark(f"attention_{g}")
+    if scatter:
+        ex.finish_scatter()
+    else:
+        main.wait_event(ev_out)
+    if phases:
+        phases.mark("last_return_or_barrier")
     if os.environ.get("LCBSA_ULYSSES_ALIAS_OUT", "0") == "1":
         return ex.local_out
     return ex.local_out.clone()

@@ -63,6 +63,7 @@ class PeerArena:
         self.buf = symm_mem.empty(numel, dtype=self.dtype, device=self.device)
         self.hdl = symm_mem.rendezvous(self.buf, self.group)
         self.numel = numel
+        self.__dict__.pop("_copy_plans", None)  # cached pointer tables name addresses of the old buffer
 
     def view(self, rank: int, offset: int, shape) -> torch.Tensor:
         """``shape`` elements at ``offset`` of rank ``rank``'s buffer, as a tensor on this device."""
@@ -176,27 +177,39 @@ class PeerExchange:
             self.ar._bases_numel = self.ar.numel
         self.bases = self.ar._bases
 
-    def _copy(self, dst: List[int], src: List[int], nbytes: Optional[int] = None, lanes: Optional[List[int]] = None) -> None:
-        """Enqueue the slab copies.  Called with ``side`` current.  ``lanes[i]`` (the destination rank of slab i)
-        spreads them over a few auxiliary streams, so that copies to different peers use different copy engines
-        and links at the same time; ``side`` continues when all of them are done."""
+    def _copy(self, make_lists, key=None, nbytes: Optional[int] = None) -> None:
+        """Enqueue slab copies.  Called with ``side`` current.  ``make_lists()`` returns (dst, src, lanes): device
+        addresses and, per slab, its destination rank; the slabs are spread by destination over a few auxiliary
+        streams, so that copies to different peers use different copy engines and links at the same time, and ``side``
+        continues when all of them are done.  The pointer tables of a ``key`` (the addresses involved and the head
+        range) are built once and reused by later calls: a layer repeats the same pushes step after step."""
         nbytes = self.Sl * self.D * self.es if nbytes is None else nbytes
-        aux = _aux_streams(self.side.device, min(_AUX_STREAMS, self.n) - 1) if lanes is not None else []
-        groups: List[Tuple[List[int], List[int]]] = [([], []) for _ in range(len(aux) + 1)]
-        for i in range(len(dst)):
-            g = (lanes[i] % len(groups)) if lanes is not None else 0
-            groups[g][0].append(dst[i])
-            groups[g][1].append(src[i])
-        start = self.side.record_event() if aux else None
-        for g, (d, s_) in enumerate(groups):
-            if not d:
-                continue
+        cache = self.ar.__dict__.setdefault("_copy_plans", {})
+        plan = cache.get(key) if key is not None else None
+        if plan is None:
+            dst, src, lanes = make_lists()
+            n_aux = min(_AUX_STREAMS, self.n) - 1 if lanes is not None else 0
+            groups: List[Tuple[List[int], List[int]]] = [([], []) for _ in range(n_aux + 1)]
+            for i in range(len(dst)):
+                g = (lanes[i] % len(groups)) if lanes is not None else 0
+                groups[g][0].append(dst[i])
+                groups[g][1].append(src[i])
+            plan = []
+            for g, (d, s_) in enumerate(groups):
+                if d:
+                    m = len(d)
+                    arr = (ctypes.c_void_p * (2 * m))(*d, *s_)
+                    plan.append((g, m, arr, ctypes.addressof(arr)))
+            if key is not None:
+                if len(cache) > 256:
+                    cache.clear()
+                cache[key] = plan
+        aux = _aux_streams(self.side.device, max((g for g, _, _, _ in plan), default=0))
+        start = self.side.record_event() if any(g > 0 for g, _, _, _ in plan) else None
+        for g, m, _arr, base in plan:
             stream = self.side if g == 0 else aux[g - 1]
             if g > 0:
                 stream.wait_event(start)
-            m = len(d)
-            arr = (ctypes.c_void_p * (2 * m))(*d, *s_)
-            base = ctypes.addressof(arr)
             self._L.check(self._L.lib().lcbsa_copy_slabs(base, base + m * ctypes.sizeof(ctypes.c_void_p), nbytes, m, stream.cuda_stream))
             if g > 0:
                 self.side.wait_event(stream.record_event())
@@ -222,26 +235,50 @@ class PeerExchange:
         part_all = self.hn * self.n * rows * self.D
         return [self.ar.view(self.rank, self.extra_off + t * part_all, (1, self.hn, self.n * rows, self.D)) for t in range(2)]
 
+    def attn_scatter(self, q, k, v, sm_scale, idx, cnt, latent_shape, chunk, lo: int) -> None:
+        """Block-sparse attention of local heads ``lo:lo+h`` over the gathered tensors, with the return exchange folded
+        into the kernel's output stores (``lcbsa_attn_fwd_scatter``): the rows of rank r's tokens go straight into rank
+        r's result region.  Runs on the current stream; ``finish_scatter`` must follow the last stage."""
+        L = self._L
+        h = q.shape[1]
+        slab = self.Sl * self.D
+        dst = (ctypes.c_void_p * self.n)(*[self.bases[r] + (self.out_off + (self.rank * self.hn + lo) * slab) * self.es for r in range(self.n)])
+        qd, kd, vd = L.tensor_desc(q), L.tensor_desc(k), L.tensor_desc(v)
+        g = L.grid_desc(latent_shape, chunk)
+        assert idx.is_contiguous() and cnt.is_contiguous() and idx.dtype == torch.int32 and idx.shape[1] == h
+        L.check(L.lib().lcbsa_attn_fwd_scatter(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(vd), ctypes.byref(g), ctypes.byref(g),
+                                               idx.data_ptr(), cnt.data_ptr(), idx.shape[-1], float(sm_scale), dst, self.n, slab, self.D,
+                                               L.current_stream(q.device)))
+
+    def finish_scatter(self) -> None:
+        """Meet the group on the current stream: when it has passed, every rank's scattered stores have landed."""
+        self.ar.barrier(channel=1)
+
     def push_rows(self, tensors, rows: int, after: torch.cuda.Event) -> torch.cuda.Event:
         """Heads-scatter of small per-block tensors ``[1, H, rows, D]`` (the pooled Q and K of this rank's tokens)
         into the extra region of the owners of the heads: one contiguous copy per tensor and peer, received as
         ``[tensor][source rank][H/N][rows][D]``.  ``after`` is the event that marks them computed.  The event
         returned fires when this rank's own region is complete."""
         part = self.hn * rows * self.D  # what one rank sends another per tensor
-        dst, src, lanes = [], [], []
-        for t, x in enumerate(tensors):
+        for x in tensors:
             if not x.is_contiguous():
                 raise ValueError("push_rows takes contiguous tensors")
             if not torch.cuda.is_current_stream_capturing():
                 x.record_stream(self.side)
-            xp = x.data_ptr()
-            for r in range(self.n):
-                dst.append(self.bases[r] + (self.extra_off + (t * self.n + self.rank) * part) * self.es)
-                src.append(xp + r * part * self.es)  # x[0, r*hn:(r+1)*hn]
-                lanes.append(r)
+
+        def lists():
+            dst, src, lanes = [], [], []
+            for t, x in enumerate(tensors):
+                xp = x.data_ptr()
+                for r in range(self.n):
+                    dst.append(self.bases[r] + (self.extra_off + (t * self.n + self.rank) * part) * self.es)
+                    src.append(xp + r * part * self.es)  # x[0, r*hn:(r+1)*hn]
+                    lanes.append(r)
+            return dst, src, lanes
+
         with torch.cuda.stream(self.side):
             self.side.wait_event(after)
-            self._copy(dst, src, part * self.es, lanes=lanes)
+            self._copy(lists, key=("rows", self.extra_off, rows) + tuple(x.data_ptr() for x in tensors), nbytes=part * self.es)
             self.ar.barrier()
             return self.side.record_event()
 
@@ -259,17 +296,21 @@ class PeerExchange:
         """Send heads ``lo:hi`` (of every rank's share) of q, k, v to their owners; the event fires when this
         rank's own receive views of those heads are complete."""
         slab = self.Sl * self.D
-        dst, src, lanes = [], [], []
-        for t, x in enumerate(tensors):
-            xp, xs = x.data_ptr(), x.stride(1)
-            for r in range(self.n):
-                b = self.bases[r] + t * self.in_elems * self.es
-                for j in range(lo, hi):
-                    dst.append(b + (j * self.n + self.rank) * slab * self.es)  # [head j][source rank][S/N][D] of rank r
-                    src.append(xp + (r * self.hn + j) * xs * self.es)          # x[0, r * hn + j]
-                    lanes.append(r)
+
+        def lists():
+            dst, src, lanes = [], [], []
+            for t, x in enumerate(tensors):
+                xp, xs = x.data_ptr(), x.stride(1)
+                for r in range(self.n):
+                    b = self.bases[r] + t * self.in_elems * self.es
+                    for j in range(lo, hi):
+                        dst.append(b + (j * self.n + self.rank) * slab * self.es)  # [head j][source rank][S/N][D] of rank r
+                        src.append(xp + (r * self.hn + j) * xs * self.es)          # x[0, r * hn + j]
+                        lanes.append(r)
+            return dst, src, lanes
+
         with torch.cuda.stream(self.side):
-            self._copy(dst, src, lanes=lanes)
+            self._copy(lists, key=("in", lo, hi, self.H, self.Sl, self.D) + tuple((x.data_ptr(), x.stride(1)) for x in tensors))
             self.ar.barrier()
             return self.side.record_event()
 
@@ -282,16 +323,20 @@ class PeerExchange:
         if not torch.cuda.is_current_stream_capturing():
             o.record_stream(self.side)
         slab = self.Sl * self.D
-        op = o.data_ptr()
-        dst, src, lanes = [], [], []
-        for r in range(self.n):
-            b = self.bases[r] + self.out_off * self.es
-            for j in range(o.shape[1]):
-                dst.append(b + (self.rank * self.hn + lo + j) * slab * self.es)  # out[head rank*hn+lo+j] of rank r
-                src.append(op + (j * self.S + r * self.Sl) * self.D * self.es)   # o[0, j, r*Sl:(r+1)*Sl]
-                lanes.append(r)
+        op, nh = o.data_ptr(), o.shape[1]
+
+        def lists():
+            dst, src, lanes = [], [], []
+            for r in range(self.n):
+                b = self.bases[r] + self.out_off * self.es
+                for j in range(nh):
+                    dst.append(b + (self.rank * self.hn + lo + j) * slab * self.es)  # out[head rank*hn+lo+j] of rank r
+                    src.append(op + (j * self.S + r * self.Sl) * self.D * self.es)   # o[0, j, r*Sl:(r+1)*Sl]
+                    lanes.append(r)
+            return dst, src, lanes
+
         with torch.cuda.stream(self.side):
             self.side.wait_event(done)
-            self._copy(dst, src, lanes=lanes)
+            self._copy(lists, key=("out", lo, nh, self.out_off, self.H, self.Sl, self.D, op))
             self.ar.barrier()
             return self.side.record_event()

@@ -281,6 +281,44 @@ int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor
     return LCBSA_OK;
 }
 
+int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaGrid* gq, const LcbsaGrid* gk,
+                           const int32_t* idx, const int32_t* cnt, int cap, float sm_scale, void* const* out_dst, int n_dst,
+                           int64_t out_head_stride, int64_t out_token_stride, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "attn_fwd_scatter: bad grid");
+    if (int rc = check_tensor("q", q, gq)) return rc;
+    if (int rc = check_tensor("k", k, gk)) return rc;
+    if (int rc = check_tensor("v", v, gk)) return rc;
+    if (!idx || !cnt || cap < 1) return fail(LCBSA_EINVAL, "attn_fwd_scatter: null block lists or zero capacity");
+    if (q->dtype != k->dtype || q->dtype != v->dtype) return fail(LCBSA_EINVAL, "attn_fwd_scatter: dtypes differ");
+    if (q->dtype == LCBSA_FP32) return fail(LCBSA_EUNSUPPORTED, "attn_fwd_scatter: attention kernels take bf16 or fp16");
+    for (int i : {0, 1, 3})
+        if (q->size[i] != k->size[i] || q->size[i] != v->size[i]) return fail(LCBSA_EINVAL, "attn_fwd_scatter: q, k, v disagree on batch, heads or head_dim");
+    if (!std::isfinite(sm_scale)) return fail(LCBSA_EINVAL, "attn_fwd_scatter: sm_scale is not finite");
+    if (n_dst < 1 || n_dst > 8 || !out_dst) return fail(LCBSA_EINVAL, "attn_fwd_scatter: 1..8 destinations");
+    const size_t es = elem_size(q->dtype);
+    if (out_head_stride < 0 || out_token_stride < 0 || (out_head_stride * (long long)es) % 16 || (out_token_stride * (long long)es) % 16)
+        return fail(LCBSA_EINVAL, "attn_fwd_scatter: output strides must be non-negative multiples of 16 bytes");
+    lcbsa::AttnArgs a;
+    a.dtype = q->dtype;
+    a.q = view_of(q); a.k = view_of(k); a.v = view_of(v);
+    a.o = lcbsa::View{nullptr, 0, out_head_stride, out_token_stride};
+    a.B = (int)q->size[0]; a.H = (int)q->size[1]; a.D = (int)q->size[3];
+    a.gq = lcbsa::make_geom(*gq); a.gk = lcbsa::make_geom(*gk);
+    a.idx = idx; a.cnt = cnt; a.cap = cap; a.sm_scale = sm_scale; a.lse = nullptr;
+    a.n_out_dst = n_dst;
+    for (int r = 0; r < n_dst; ++r) {
+        if (!out_dst[r] || reinterpret_cast<uintptr_t>(out_dst[r]) % 16) return fail(LCBSA_EINVAL, "attn_fwd_scatter: destination %d is null or not 16-byte aligned", r);
+        a.out_dst[r] = out_dst[r];
+    }
+    a.status = device_status_ptr();
+    if (!a.status) return fail(LCBSA_ECUDA, "attn_fwd_scatter: cannot resolve the device status words");
+    const char* why = "";
+    if (!lcbsa::attn_tc_supported(a, &why)) return fail(LCBSA_EUNSUPPORTED, "attn_fwd_scatter (tcgen05): %s", why);
+    cudaError_t e = lcbsa::launch_attn_tc(a, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_scatter", why);
+    return LCBSA_OK;
+}
+
 int lcbsa_set_attn_sm_reserve(int n_sms) {
     if (n_sms < 0 || n_sms > 64) return fail(LCBSA_EINVAL, "sm reserve %d outside 0..64", n_sms);
     return lcbsa::set_attn_sm_reserve(n_sms);

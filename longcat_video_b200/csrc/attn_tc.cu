@@ -56,6 +56,7 @@ namespace lcbsa {
 
 namespace {
 
+constexpr int kMaxOutDst = 8;
 constexpr int kD = 128;
 constexpr int kBlk = 64;                    // tokens per query / key block
 constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB: one Q, K, V or O tile
@@ -86,7 +87,12 @@ constexpr int kOffMl = kOffMisc + 64;                 // [2 warpgroups][128 lane
 constexpr int kSmemBytes = kOffMl + 2 * 128 * 8;
 
 struct TcParams {
-    CUtensorMap tm_q, tm_k, tm_v, tm_o;
+    CUtensorMap tm_q, tm_k, tm_v;
+    // Output maps.  Normally one (tm_o[0]).  With o_frames > 0 the query grid is the rank-major grid of a
+    // context-parallel group: frames [r * o_frames, (r + 1) * o_frames) are the tokens of rank r, and the rows of a
+    // query block are stored straight into rank r's result buffer (its own map, over this GPU's or a peer's memory).
+    CUtensorMap tm_o[kMaxOutDst];
+    int o_frames;
     const int32_t* idx;
     const int32_t* cnt;
     float* lse;
@@ -648,10 +654,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc_kernel(const __grid_const
                 for (int hf = 0; hf < 2; ++hf) {
                     const int qq = g * kTilesPerWork + hf;
                     if (qq >= P.nq) continue;
-                    const Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
+                    Coord cc = block_coord(P.gq, qq, b, h, P.heads, P.merge_o, P.Tq);
+                    const CUtensorMap* tmo = &P.tm_o[0];
+                    if (P.o_frames > 0) {  // blocks never straddle ranks: o_frames is a multiple of the block's frames
+                        const int dst = cc.c3 / P.o_frames;
+                        cc.c3 -= dst * P.o_frames;
+                        tmo = &P.tm_o[dst];
+                    }
                     const uint32_t src = sbase + kOffV + (last % kVSlots) * kSlotBytes + hf * kTileBytes;
-                    tma_store_5d(&P.tm_o, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
-                    tma_store_5d(&P.tm_o, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
+                    tma_store_5d(tmo, src, 0, cc.c1, cc.c2, cc.c3, cc.c4);
+                    tma_store_5d(tmo, src + kHalfBytes, 64, cc.c1, cc.c2, cc.c3, cc.c4);
                 }
                 tma_store_commit();
                 tma_store_wait_read();
@@ -985,9 +997,17 @@ bool attn_tc_supported(const AttnArgs& a, const char** why) {
         *why = "key grid axis above 1023 tokens (block coordinates are packed into 10-bit fields)";
         return false;
     }
+    if (a.n_out_dst > 0) {
+        if (a.n_out_dst > kMaxOutDst) { *why = "more than 8 output destinations"; return false; }
+        if (a.B != 1) { *why = "scattered output needs batch 1"; return false; }
+        if (a.gq.ragged || a.gq.T % a.n_out_dst != 0 || (a.gq.T / a.n_out_dst) % a.gq.ct != 0) {
+            *why = "scattered output needs a query grid whose frames split evenly, on block boundaries, over the destinations";
+            return false;
+        }
+    }
     const View* vs[4] = {&a.q, &a.k, &a.v, &a.o};
     const Geom* gs[4] = {&a.gq, &a.gk, &a.gk, &a.gq};
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < (a.n_out_dst > 0 ? 3 : 4); ++i) {
         if (merge_mode(*vs[i], a.B, a.H, *gs[i]) < 0) { *why = "batch stride cannot be folded into a 5-D tensor map"; return false; }
         if (vs[i]->ss * 2 >= (1ll << 40) || vs[i]->sh * 2 >= (1ll << 40)) { *why = "stride too large for a tensor map"; return false; }
     }
@@ -1000,7 +1020,25 @@ cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why)
     const int mq = merge_mode(a.q, a.B, a.H, a.gq), mk = merge_mode(a.k, a.B, a.H, a.gk);
     const int mv = merge_mode(a.v, a.B, a.H, a.gk), mo = merge_mode(a.o, a.B, a.H, a.gq);
     if (!make_map(&P.tm_q, a.dtype, a.q, a.B, a.H, a.gq, mq) || !make_map(&P.tm_k, a.dtype, a.k, a.B, a.H, a.gk, mk) ||
-        !make_map(&P.tm_v, a.dtype, a.v, a.B, a.H, a.gk, mv) || !make_map(&P.tm_o, a.dtype, a.o, a.B, a.H, a.gq, mo)) {
+        !make_map(&P.tm_v, a.dtype, a.v, a.B, a.H, a.gk, mv)) {
+        *why = "cuTensorMapEncodeTiled rejected a tensor";
+        return cudaErrorInvalidValue;
+    }
+    P.o_frames = 0;
+    if (a.n_out_dst > 0) {
+        // one map per destination over [D, W, H, T / n, heads]: the rank-major grid split along T
+        Geom gl = a.gq;
+        gl.T = a.gq.T / a.n_out_dst;
+        P.o_frames = gl.T;
+        for (int r = 0; r < a.n_out_dst; ++r) {
+            View vo = a.o;
+            vo.data = a.out_dst[r];
+            if (!make_map(&P.tm_o[r], a.dtype, vo, 1, a.H, gl, 0)) {
+                *why = "cuTensorMapEncodeTiled rejected a destination of the scattered output";
+                return cudaErrorInvalidValue;
+            }
+        }
+    } else if (!make_map(&P.tm_o[0], a.dtype, a.o, a.B, a.H, a.gq, mo)) {
         *why = "cuTensorMapEncodeTiled rejected a tensor";
         return cudaErrorInvalidValue;
     }

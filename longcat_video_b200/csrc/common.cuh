@@ -110,6 +110,11 @@ struct AttnArgs {
     float sm_scale;
     float* lse;  // nullable, [B*H, Sq]
     unsigned int* status;  // device status words
+    // Scattered output (tcgen05 kernel only): with n_out_dst > 0 the query grid is rank-major over n_out_dst ranks
+    // (frames split evenly) and the rows of rank r's frames go to out_dst[r], a [1, H, Sq / n, D] tensor with the
+    // head and token strides of `o` (o.data is then unused).
+    int n_out_dst = 0;
+    void* out_dst[8] = {};
 };
 
 cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);

@@ -100,12 +100,16 @@ def _worker(rank, world, port, heads):
         # the context-parallel op (local pooling, pooled rows exchanged first, one block-select for all local heads)
         from longcat_video_b200.context_parallel.bsa_context_parallel import flash_attn_bsa_3d_ulysses
 
+        from longcat_video_b200.context_parallel import bsa_context_parallel as CP
+
         os.environ["LCBSA_ULYSSES_EXCHANGE"] = "peer"
         del os.environ["LCBSA_ULYSSES_GROUP_HEADS"]
-        for _ in range(2):
-            fused = flash_attn_bsa_3d_ulysses(q, k, v, grid, sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
-            torch.cuda.synchronize()
-            assert torch.equal(fused, want)
+        for scatter_out in (True, False, True):  # result rows stored straight into their owners' memory / sent back by copies
+            CP._SCATTER_OUT = scatter_out
+            for _ in range(2):
+                fused = flash_attn_bsa_3d_ulysses(q, k, v, grid, sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
+                torch.cuda.synchronize()
+                assert torch.equal(fused, want)
         L.check(L.lib().lcbsa_check_device_status())
         # host-resident form: pinned shards in, pinned result out, pipelined by head chunk
         from longcat_video_b200.context_parallel.bsa_context_parallel import flash_attn_bsa_3d_ulysses_host
