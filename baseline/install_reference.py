@@ -4,7 +4,8 @@
 
 The reference project has no build metadata (no setup.py / pyproject.toml), so it cannot be pip-installed; the two
 packages its block-sparse attention needs -- ``longcat_video/block_sparse_attention`` (Triton kernels and their
-launchers) and ``longcat_video/context_parallel`` -- are copied unmodified.  ``baseline/_ref/`` is ignored by git:
+launchers) and ``longcat_video/context_parallel`` -- and the files of ``longcat_video/modules`` that define one DiT block
+are copied unmodified.  ``baseline/_ref/`` is ignored by git:
 nothing of the reference enters this repository's history, and nothing in ``longcat_video_b200/`` imports it.
 """
 import os
@@ -14,6 +15,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 PACKAGES = ["block_sparse_attention", "context_parallel"]
+# the DiT block and what it is made of, for the denoising-step harness (bench_dit_step.py); the VAE, the scheduler, the
+# avatar model and the quantisation helpers stay behind
+MODULE_FILES = ["__init__.py", "attention.py", "blocks.py", "rope_3d.py", "longcat_video_dit.py", "lora_utils.py"]
 
 
 def install(src_root: str) -> str:
@@ -30,6 +34,13 @@ def install(src_root: str) -> str:
         init = os.path.join(dst_pkg, name, "__init__.py")
         if not os.path.exists(init):
             open(init, "w").close()
+    os.makedirs(os.path.join(dst_pkg, "modules"))
+    for name in MODULE_FILES:
+        src = os.path.join(src_pkg, "modules", name)
+        if os.path.exists(src):
+            shutil.copy(src, os.path.join(dst_pkg, "modules", name))
+    if not os.path.exists(os.path.join(dst_pkg, "modules", "__init__.py")):
+        open(os.path.join(dst_pkg, "modules", "__init__.py"), "w").close()
     return DEST
 
 

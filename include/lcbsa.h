@@ -130,6 +130,33 @@ size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, 
                                     const LcbsaGrid* gk);
 
 /*
+ * A latent grid with a "first part": the conditioning frames of video continuation, which attend among themselves while
+ * all other frames attend to everything (Attention.forward, longcat_video/modules/attention.py:124-137, where this
+ * is two _process_attn calls on copies).  Blocks are numbered frame-major; a block is in the first part when
+ * ((block / hw) % period) < split, with hw = blocks per frame-block plane, period = frame blocks of the whole grid
+ * (or of one rank's share of the rank-major grid of a context-parallel group) and split = conditioning frame blocks.
+ * Query blocks of the first part select nsel_first key blocks among the key blocks of the first part; every other
+ * query block selects as usual among all key blocks.  One table holds both kinds of rows; rows of the first part are
+ * padded with -1 beyond nsel_first.
+ */
+typedef struct LcbsaSplit {
+    int32_t hw_q, period_q, split_q;
+    int32_t hw_k, period_k, split_k;
+    int32_t nsel_first;
+} LcbsaSplit;
+
+/* lcbsa_score_topk_ws for a grid with a first part; needs the key workspace (bf16 / fp16, head_dim 64 or 128, up to
+ * 1536 key blocks). */
+int lcbsa_score_topk_split(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, const LcbsaSplit* split,
+                           int nsel, int cap, int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream);
+
+/* lcbsa_block_select for a grid with a first part (periods and splits in frame blocks); needs the workspace of
+ * lcbsa_select_workspace_bytes_fast. */
+int lcbsa_block_select_split(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int period_tq,
+                             int split_tq, int period_tk, int split_tk, int nsel_first, int nsel, int cap, int32_t* idx,
+                             int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * The whole block-select stage: pool Q and K, score, top-k.
  * Stands in for the gating part of _attention_bsa.forward (bsa_interface.py:547-549) with
  * cdf_threshold=None.  idx/cnt as in lcbsa_score_topk with BH = B*H.

@@ -37,6 +37,10 @@ class LcbsaGrid(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("T", "H", "W", "ct", "ch", "cw")]
 
 
+class LcbsaSplit(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("hw_q", "period_q", "split_q", "hw_k", "period_k", "split_k", "nsel_first")]
+
+
 # every symbol include/lcbsa.h declares, with its C signature
 _P = ctypes.POINTER
 SIGNATURES = {
@@ -54,6 +58,10 @@ SIGNATURES = {
     "lcbsa_score_keys_bytes": (ctypes.c_size_t, [ctypes.c_int] * 5),
     "lcbsa_score_topk_ws": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 7
                             + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "lcbsa_score_topk_split": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 5 + [_P(LcbsaSplit), ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "lcbsa_block_select_split": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid)] + [ctypes.c_int] * 7
+                                 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "lcbsa_select_workspace_bytes_fast": (ctypes.c_size_t, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid)]),
     "lcbsa_block_select": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_int,
                                           ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

@@ -87,6 +87,53 @@ def get_select_indices_from_pooled(q_cmp: torch.Tensor, k_cmp: torch.Tensor, spa
     return idx, cnt
 
 
+def get_select_indices_from_pooled_split(q_cmp: torch.Tensor, k_cmp: torch.Tensor, sparsity: float, hw_q: int, period_q: int, split_q: int,
+                                         hw_k: int, period_k: int, split_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``get_select_indices_from_pooled`` for a grid with a first part (the conditioning frames; see ``LcbsaSplit`` in
+    ``include/lcbsa.h``): query blocks of the first part select among the key blocks of the first part, with the number
+    of blocks the reference's separate call on the conditioning tokens would select; all others select among all."""
+    q_cmp, k_cmp = q_cmp.contiguous(), k_cmp.contiguous()
+    B, H, Nq, D = q_cmp.shape
+    Nk = k_cmp.shape[2]
+    nk_first = Nk // hw_k // period_k * split_k * hw_k
+    nsel, nsel_first = num_selected(sparsity, Nk), num_selected(sparsity, nk_first)
+    cap = max(nsel, nsel_first, 1)
+    idx = torch.empty(B, H, Nq, cap, dtype=torch.int32, device=q_cmp.device)
+    cnt = torch.empty(B, H, Nq, dtype=torch.int32, device=q_cmp.device)
+    dt = L.dtype_code(q_cmp.dtype)
+    keys_bytes = L.lib().lcbsa_score_keys_bytes(dt, B * H, Nq, Nk, D)
+    ws = torch.empty(max(keys_bytes, 16), dtype=torch.uint8, device=q_cmp.device)
+    sp = L.LcbsaSplit(hw_q, period_q, split_q, hw_k, period_k, split_k, nsel_first)
+    with torch.cuda.device(q_cmp.device):
+        L.check(L.lib().lcbsa_score_topk_split(q_cmp.data_ptr(), k_cmp.data_ptr(), dt, B * H, Nq, Nk, D, ctypes.byref(sp), nsel, cap,
+                                               idx.data_ptr(), cnt.data_ptr(), ws.data_ptr(), keys_bytes, L.current_stream(q_cmp.device)))
+    return idx, cnt
+
+
+def get_select_indices_split(q, k, latent_shape_q, latent_shape_k, sparsity, chunk_3d_shape_q, chunk_3d_shape_k, period_tq, split_tq,
+                             period_tk, split_tk) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The whole block-select stage (pool, score, top-k: three launches) for a grid with a first part; periods and
+    splits in frame blocks."""
+    q, k = _as_abi(q), _as_abi(k)
+    B, H, _, D = q.shape
+    gq, gk = L.grid_desc(latent_shape_q, chunk_3d_shape_q), L.grid_desc(latent_shape_k, chunk_3d_shape_k)
+    nq, nk = num_blocks(latent_shape_q, chunk_3d_shape_q), num_blocks(latent_shape_k, chunk_3d_shape_k)
+    hw_k = nk // (-(-int(latent_shape_k[0]) // int(chunk_3d_shape_k[0])))
+    nk_first = nk // hw_k // period_tk * split_tk * hw_k
+    nsel, nsel_first = num_selected(sparsity, nk), num_selected(sparsity, nk_first)
+    cap = max(nsel, nsel_first, 1)
+    qd, kd = L.tensor_desc(q), L.tensor_desc(k)
+    ws_bytes = L.lib().lcbsa_select_workspace_bytes_fast(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk))
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
+    idx = torch.empty(B, H, nq, cap, dtype=torch.int32, device=q.device)
+    cnt = torch.empty(B, H, nq, dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        L.check(L.lib().lcbsa_block_select_split(ctypes.byref(qd), ctypes.byref(kd), ctypes.byref(gq), ctypes.byref(gk), int(period_tq),
+                                                 int(split_tq), int(period_tk), int(split_tk), nsel_first, nsel, cap, idx.data_ptr(),
+                                                 cnt.data_ptr(), ws.data_ptr(), ws_bytes, L.current_stream(q.device)))
+    return idx, cnt
+
+
 def _select_cdf(q_cmp: torch.Tensor, k_cmp: torch.Tensor, cdf_threshold: float, nsel_min: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """get_select_indices_cdf / get_select_indices_cdf_topk (bsa_interface.py:226-266) in two launches: scores, then one
     CTA per row for softmax, sort, running sum and count."""
@@ -211,9 +258,10 @@ def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params
     ``num_cond_latents`` frames attend among themselves, the remaining frames attend to everything, and the two results
     are one ``[B,H,S,D]`` tensor.  The reference makes contiguous copies of q_cond, k_cond, v_cond and q_noise, calls
     the attention twice and concatenates; here both calls work on views of q, k, v and write into their part of one
-    output, so nothing is copied; when the cond frames are whole blocks, the two block lists are put into one table and
-    a single attention launch serves both parts.  Bit-identical to the two separate calls.  ``latent_shape`` is the
-    (T, H, W) of q."""
+    output, so nothing is copied; when the cond frames are whole blocks, q and k are pooled and scored once, one
+    selection launch serves both kinds of rows and a single attention launch serves both parts (four launches in all;
+    with ``cdf_threshold`` the two selections stay separate).  Bit-identical to the two separate calls.
+    ``latent_shape`` is the (T, H, W) of q."""
     T, Hh, W = (int(x) for x in latent_shape)
     B_, H_, S, D = q.shape
     nc = int(num_cond_latents or 0)
@@ -230,6 +278,15 @@ def flash_attn_bsa_3d_cond(q, k, v, latent_shape, num_cond_latents, **bsa_params
     if not bsa_params.get("allow_ragged", False):
         assert nc % chunk_q[0] == 0 and (T - nc) % chunk_q[0] == 0 and nc % chunk_k[0] == 0 and T % chunk_k[0] == 0
         assert Hh % chunk_q[1] == 0 and W % chunk_q[2] == 0 and Hh % chunk_k[1] == 0 and W % chunk_k[2] == 0
+    aligned = nc % chunk_q[0] == 0 and nc % chunk_k[0] == 0 and T % chunk_q[0] == 0 and T % chunk_k[0] == 0
+    if (aligned and cdf is None and sparsity is not None and q.dtype in (torch.bfloat16, torch.float16) and D in (64, 128)
+            and num_blocks((T, Hh, W), chunk_k) <= 1536):
+        # One pass over the whole q and k: pooled once, scored once, and a selection whose rows know which part they
+        # belong to (lcbsa_block_select_split); then one attention launch.  Four launches for both parts together.
+        idx, cnt = get_select_indices_split(q, k, (T, Hh, W), (T, Hh, W), sparsity, chunk_q, chunk_k, T // chunk_q[0], nc // chunk_q[0],
+                                            T // chunk_k[0], nc // chunk_k[0])
+        attn_fwd_bsa_varlen(q, k, v, 1 / D ** 0.5, idx, cnt, (T, Hh, W), (T, Hh, W), chunk_q, chunk_k, out=out)
+        return out
     parts = ((q[:, :, :sc], sc, out[:, :, :sc], (nc, Hh, W), (nc, Hh, W)),
              (q[:, :, sc:], S, out[:, :, sc:], (T - nc, Hh, W), (T, Hh, W)))
     lists = [get_select_indices(qp, k[:, :, :n], gq, gk, sparsity, cdf, chunk_q, chunk_k) for qp, n, _, gq, gk in parts]

@@ -83,24 +83,42 @@ def _stages_scattered(hn: int):
     return out
 
 
-def _generic(q, k, v, latent_shape, params):
+def _generic(q, k, v, latent_shape, params, latent_shape_q=None):
     class _Layer:
         @U.ulysses_wrapper
         def attn(self, q_, k_, v_, shape):
-            return B.flash_attn_bsa_3d(q_, k_, v_, shape, shape, **params)
+            return B.flash_attn_bsa_3d(q_, k_, v_, latent_shape_q or shape, shape, **params)
 
     return _Layer().attn(q, k, v, latent_shape)
 
 
+def _generic_cond(q, k, v, latent_shape, nc, n, params):
+    """The reference's formulation of the conditioning split under context parallelism
+    (longcat_video/modules/attention.py:124-137): two exchanges and two attention calls on copies, concatenated."""
+    T, Hh, Ww = latent_shape
+    sc = nc * Hh * Ww
+    x_cond = _generic(q[:, :, :sc].contiguous(), k[:, :, :sc].contiguous(), v[:, :, :sc].contiguous(), (n * nc, Hh, Ww), params)
+    x_noise = _generic(q[:, :, sc:].contiguous(), k, v, latent_shape, params, latent_shape_q=(T - n * nc, Hh, Ww))
+    return torch.cat([x_cond, x_noise], dim=2)
+
+
 @torch.compiler.disable
 def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_threshold=None, chunk_3d_shape_q=[4, 4, 8],
-                              chunk_3d_shape_k=[4, 4, 8]):
+                              chunk_3d_shape_k=[4, 4, 8], num_cond_latents=None):
     """``q, k, v``: this rank's ``[B, H, S/N, D]`` slices (all heads, its tokens); ``latent_shape``: the rank-major
-    grid ``(N*T, H', W')`` of the gathered sequence, as ``_process_attn`` receives it.  Returns ``[B, H, S/N, D]``."""
+    grid ``(N*T, H', W')`` of the gathered sequence, as ``_process_attn`` receives it.  Returns ``[B, H, S/N, D]``.
+
+    ``num_cond_latents`` (video continuation, longcat_video/modules/attention.py:124-137): the first that many frames of
+    every rank's tokens are conditioning frames, which attend among themselves, while the others attend to everything.
+    The reference runs two exchanges and two attention calls on copies; here it is still ONE exchange and one attention
+    launch per stage: the selection kernel knows which rows belong to which part.  Same bits as the two calls."""
     n = context_parallel_util.get_cp_size()
     params = dict(sparsity=sparsity, cdf_threshold=cdf_threshold, chunk_3d_shape_q=list(chunk_3d_shape_q),
                   chunk_3d_shape_k=list(chunk_3d_shape_k))
+    nc = int(num_cond_latents or 0)
     if n == 1:
+        if nc > 0:
+            return B.flash_attn_bsa_3d_cond(q, k, v, latent_shape, nc, **params)
         return B.flash_attn_bsa_3d(q, k, v, latent_shape, latent_shape, **params)
     group = context_parallel_util.get_cp_group()
     Bsz, H, Sl, D = q.shape
@@ -111,14 +129,19 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
             and (T // n) * Hh * Ww == Sl and q.dtype in (torch.bfloat16, torch.float16)
             and peer_exchange.available(q, group)
             and all(t[0, 0].is_contiguous() and t.shape == q.shape and t.dtype == q.dtype for t in (q, k, v)))
+    if nc > 0 and not 0 < nc < T // n:
+        raise ValueError(f"num_cond_latents {nc} outside (0, {T // n})")
+    if nc > 0:
+        nblk_all = (T // chunk[0]) * (Hh // chunk[1]) * (Ww // chunk[2]) if fast else 0
+        fast = fast and nc % chunk[0] == 0 and nblk_all <= 1536
     if not fast:
-        return _generic(q, k, v, latent_shape, params)
+        return _generic_cond(q, k, v, latent_shape, nc, n, params) if nc > 0 else _generic(q, k, v, latent_shape, params)
     hn = H // n
     local_grid = (T // n, Hh, Ww)
     nblk_l = B.num_blocks(local_grid, chunk)
     ex = peer_exchange.open_exchange(group, q, extra_elems=2 * hn * n * nblk_l * D)
     if ex is None:
-        return _generic(q, k, v, latent_shape, params)
+        return _generic_cond(q, k, v, latent_shape, nc, n, params) if nc > 0 else _generic(q, k, v, latent_shape, params)
     main, side = ex.main, ex.side
 
     side.wait_stream(main)
@@ -141,7 +164,11 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
 
     # 3. block lists of all local heads while the first slabs travel
     qc, kc = ex.pooled_received(nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
-    idx, cnt = B.get_select_indices_from_pooled(qc, kc, sparsity, None)
+    if nc > 0:
+        hw, period = (Hh // chunk[1]) * (Ww // chunk[2]), (T // n) // chunk[0]
+        idx, cnt = B.get_select_indices_from_pooled_split(qc, kc, sparsity, hw, period, nc // chunk[0], hw, period, nc // chunk[0])
+    else:
+        idx, cnt = B.get_select_indices_from_pooled(qc, kc, sparsity, None)
     if phases:
         phases.mark("select")
     scale = 1 / D ** 0.5

@@ -175,6 +175,39 @@ int lcbsa_score_topk_ws(const void* q_cmp, const void* k_cmp, int dtype, int BH,
     return LCBSA_OK;
 }
 
+static int check_split(const char* who, const LcbsaSplit* sp, int Nq, int Nk, int nsel, int cap) {
+    if (!sp) return fail(LCBSA_EINVAL, "%s: null split description", who);
+    if (sp->hw_q < 1 || sp->hw_k < 1 || sp->period_q < 1 || sp->period_k < 1 || sp->split_q < 0 || sp->split_k < 0 ||
+        sp->split_q > sp->period_q || sp->split_k > sp->period_k)
+        return fail(LCBSA_EINVAL, "%s: bad split description", who);
+    if (Nq % sp->hw_q != 0 || Nk % sp->hw_k != 0 || (Nq / sp->hw_q) % sp->period_q != 0 || (Nk / sp->hw_k) % sp->period_k != 0)
+        return fail(LCBSA_EINVAL, "%s: block counts %d / %d are not whole periods of the split", who, Nq, Nk);
+    const long long first_k = (long long)(Nk / sp->hw_k / sp->period_k) * sp->split_k * sp->hw_k;  // key blocks of the first part
+    if (sp->nsel_first < 0 || sp->nsel_first > first_k || sp->nsel_first > cap || nsel > cap)
+        return fail(LCBSA_EINVAL, "%s: nsel_first %d outside [0, min(%lld, cap %d)]", who, sp->nsel_first, first_k, cap);
+    return LCBSA_OK;
+}
+
+int lcbsa_score_topk_split(const void* q_cmp, const void* k_cmp, int dtype, int BH, int Nq, int Nk, int D, const LcbsaSplit* sp, int nsel,
+                           int cap, int32_t* idx, int32_t* cnt, void* keys_ws, size_t keys_bytes, void* stream) {
+    if (!q_cmp || !k_cmp || !idx || !cnt) return fail(LCBSA_EINVAL, "score_topk_split: null pointer");
+    if (BH < 0 || Nq < 0 || Nk <= 0) return fail(LCBSA_EINVAL, "score_topk_split: bad sizes");
+    if (nsel < 0 || nsel > Nk) return fail(LCBSA_EINVAL, "score_topk_split: nsel %d outside [0, %d]", nsel, Nk);
+    if (cap < nsel || cap < 1) return fail(LCBSA_EINVAL, "score_topk_split: list capacity %d below nsel %d", cap, nsel);
+    if (int rc = check_split("score_topk_split", sp, Nq, Nk, nsel, cap)) return rc;
+    const size_t need = lcbsa::score_keys_bytes(dtype, BH, Nq, Nk, D);
+    if (need == 0) return fail(LCBSA_EUNSUPPORTED, "score_topk_split: bf16 or fp16, head_dim 64 or 128, batch*heads up to 65535");
+    if (!keys_ws || keys_bytes < need) return fail(LCBSA_EWORKSPACE, "score_topk_split: workspace of %zu bytes, %zu needed", keys_bytes, need);
+    if (reinterpret_cast<uintptr_t>(q_cmp) % 16 || reinterpret_cast<uintptr_t>(k_cmp) % 16 || reinterpret_cast<uintptr_t>(keys_ws) % 16)
+        return fail(LCBSA_EINVAL, "score_topk_split: pooled tensors and workspace must be 16-byte aligned");
+    const lcbsa::SelectSplit s2{sp->hw_q, sp->period_q, sp->split_q, sp->hw_k, sp->period_k, sp->split_k, sp->nsel_first};
+    const char* why = "";
+    cudaError_t e = lcbsa::launch_score_gemm_topk(dtype, q_cmp, k_cmp, BH, Nq, Nk, D, nsel, cap, idx, cnt, keys_ws,
+                                                  static_cast<cudaStream_t>(stream), &why, &s2);
+    if (e != cudaSuccess) return cuda_fail(e, "score_topk_split", why);
+    return LCBSA_OK;
+}
+
 size_t lcbsa_select_workspace_bytes(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk) {
     if (!q || !k || !grid_ok(gq) || !grid_ok(gk)) return 0;
     const size_t es = elem_size(q->dtype);
@@ -192,8 +225,25 @@ size_t lcbsa_select_workspace_bytes_fast(const LcbsaTensor* q, const LcbsaTensor
     return base + (keys + 255) / 256 * 256;
 }
 
+static int block_select_impl(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel, int cap,
+                             int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream, const LcbsaSplit* sp);
+
 int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel,
                        int cap, int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream) {
+    return block_select_impl(q, k, gq, gk, nsel, cap, idx, cnt, workspace, workspace_bytes, stream, nullptr);
+}
+
+int lcbsa_block_select_split(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int period_tq,
+                             int split_tq, int period_tk, int split_tk, int nsel_first, int nsel, int cap, int32_t* idx, int32_t* cnt,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "block_select_split: bad grid");
+    const lcbsa::Geom a = lcbsa::make_geom(*gq), b = lcbsa::make_geom(*gk);
+    const LcbsaSplit sp{a.Nh * a.Nw, period_tq, split_tq, b.Nh * b.Nw, period_tk, split_tk, nsel_first};
+    return block_select_impl(q, k, gq, gk, nsel, cap, idx, cnt, workspace, workspace_bytes, stream, &sp);
+}
+
+static int block_select_impl(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGrid* gq, const LcbsaGrid* gk, int nsel, int cap,
+                             int32_t* idx, int32_t* cnt, void* workspace, size_t workspace_bytes, void* stream, const LcbsaSplit* sp) {
     if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "block_select: bad grid");
     if (int rc = check_tensor("q", q, gq)) return rc;
     if (int rc = check_tensor("k", k, gk)) return rc;
@@ -227,13 +277,20 @@ int lcbsa_block_select(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaGr
     if (fast > need && workspace_bytes >= fast) {
         if (nsel < 0 || cap < 1 || nsel > cap || nsel > ggk.nblk || !idx || !cnt)
             return fail(LCBSA_EINVAL, "block_select: bad nsel/cap (%d/%d for %d key blocks) or null outputs", nsel, cap, ggk.nblk);
+        lcbsa::SelectSplit s2{};
+        if (sp) {
+            if (int rc = check_split("block_select_split", sp, ggq.nblk, ggk.nblk, nsel, cap)) return rc;
+            s2 = lcbsa::SelectSplit{sp->hw_q, sp->period_q, sp->split_q, sp->hw_k, sp->period_k, sp->split_k, sp->nsel_first};
+        }
         const char* why = "";
         cudaError_t e = lcbsa::launch_score_gemm_topk(q->dtype, qc, kc, (int)(q->size[0] * q->size[1]), ggq.nblk, ggk.nblk,
                                                       (int)q->size[3], nsel, cap, idx, cnt,
-                                                      static_cast<unsigned char*>(workspace) + need, static_cast<cudaStream_t>(stream), &why);
+                                                      static_cast<unsigned char*>(workspace) + need, static_cast<cudaStream_t>(stream), &why,
+                                                      sp ? &s2 : nullptr);
         if (e != cudaSuccess) return cuda_fail(e, "score_gemm_topk", why);
         return LCBSA_OK;
     }
+    if (sp) return fail(LCBSA_EWORKSPACE, "block_select_split: needs the workspace of lcbsa_select_workspace_bytes_fast (%zu bytes) and bf16/fp16 with head_dim 64 or 128", fast);
     return lcbsa_score_topk(qc, kc, q->dtype, (int)(q->size[0] * q->size[1]), ggq.nblk, ggk.nblk, (int)q->size[3], nsel, cap,
                             idx, cnt, stream);
 }

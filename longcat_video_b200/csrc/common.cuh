@@ -94,8 +94,17 @@ cudaError_t launch_pool2(int dtype, const View& x0, const Geom& g0, const PoolDs
 
 // two-kernel form of the same stage (select_gemm.cu): bytes of key workspace it needs (0: does not apply) and launch
 size_t score_keys_bytes(int dtype, int BH, int Nq, int Nk, int D);
+// A grid with a "first part" (conditioning frames): blocks are numbered frame-major and a block is in the first part when
+// ((block / hw) % period) < split, hw = blocks per frame-block plane.  Query blocks of the first part select nsel_first
+// key blocks among the key blocks of the first part; the others select among all key blocks.
+struct SelectSplit {
+    int hw_q, period_q, split_q;
+    int hw_k, period_k, split_k;
+    int nsel_first;
+};
 cudaError_t launch_score_gemm_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel, int cap,
-                                   int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why);
+                                   int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why,
+                                   const SelectSplit* split = nullptr);
 cudaError_t launch_score_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel,
                               int cap, int32_t* idx, int32_t* cnt, cudaStream_t st, const char** why);
 

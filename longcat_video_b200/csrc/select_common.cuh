@@ -57,12 +57,21 @@ __device__ __forceinline__ int count_row(const uint32_t* row, int nk_pad, uint32
     return warp_sum(n);
 }
 
+// Which key blocks a row may select from.  Blocks are numbered frame-major (t, then h, then w); a block belongs to the
+// "first part" when (its frame-block index % period) < split -- period = all frame blocks and split = the conditioning
+// frame blocks for a single grid, period = the frame blocks of one rank for the rank-major grid of a context-parallel
+// group.  period == 0: every block is allowed.
+struct KeyMask {
+    int hw, period, split;
+    __device__ __forceinline__ bool operator()(int j) const { return period == 0 || ((j / hw) % period) < split; }
+};
+
 // The nsel largest keys of one row (ties at the threshold broken towards the lower block index), emitted as
 // ascending block indices by one warp; the cap - nsel trailing entries are set to -1.  `row` may be shared or
 // global memory; nk_pad (a multiple of 64) entries are readable and those past Nk hold key 0.
 template <typename Key>
 __device__ __forceinline__ void select_row(const Key* row, int Nk, int nk_pad, int nsel, int cap, int32_t* out, int32_t* cnt_out,
-                                           int lane) {
+                                           int lane, const KeyMask mask = KeyMask{1, 0, 0}) {
     constexpr int kKeyBits = sizeof(Key) * 8;
     if (lane == 0) *cnt_out = nsel;
     if (nsel > 0) {
@@ -76,6 +85,14 @@ __device__ __forceinline__ void select_row(const Key* row, int Nk, int nk_pad, i
             uint32_t w[kRegWords];
 #pragma unroll
             for (int i = 0; i < kRegWords; ++i) w[i] = (lane + 32 * i < nwords) ? r32[lane + 32 * i] : 0u;  // key 0 is never counted
+            if (mask.period != 0) {  // keys of blocks this row may not select become key 0
+#pragma unroll
+                for (int i = 0; i < kRegWords; ++i) {
+                    const int j = 2 * (lane + 32 * i);
+                    if (!mask(j)) w[i] &= 0xffff0000u;
+                    if (!mask(j + 1)) w[i] &= 0x0000ffffu;
+                }
+            }
             auto count = [&](uint32_t c) {  // keys >= c, c >= 1
                 int n = 0;
 #pragma unroll
@@ -87,6 +104,12 @@ __device__ __forceinline__ void select_row(const Key* row, int Nk, int nk_pad, i
                 if (count(cand) >= nsel) thr = cand;
             }
             above = count(thr + 1u);
+        } else if (mask.period != 0) {
+            // a masked row is only handled where it fits in registers (the host checks this before the launch):
+            // select nothing rather than something wrong
+            if (lane == 0) *cnt_out = 0;
+            for (int j = lane; j < cap; j += 32) out[j] = -1;
+            return;
         } else {
             for (int bit = kKeyBits - 1; bit >= 0; --bit) {
                 const uint32_t cand = thr | (1u << bit);
@@ -99,9 +122,10 @@ __device__ __forceinline__ void select_row(const Key* row, int Nk, int nk_pad, i
         const unsigned lt_mask = (1u << lane) - 1u;
         for (int j0 = 0; j0 < Nk; j0 += 32) {
             const int j = j0 + lane;
-            const uint32_t key = (j < Nk) ? (uint32_t)row[j] : 0u;
+            const bool ok = (j < Nk) && mask(j);
+            const uint32_t key = ok ? (uint32_t)row[j] : 0u;
             const bool gt = key > thr;
-            const bool eq = (key == thr) && (j < Nk);
+            const bool eq = (key == thr) && ok;
             const unsigned eq_mask = __ballot_sync(0xffffffffu, eq);
             const bool take = gt || (eq && (n_eq + __popc(eq_mask & lt_mask) < take_eq));
             const unsigned take_mask = __ballot_sync(0xffffffffu, take);

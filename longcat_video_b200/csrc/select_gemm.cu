@@ -119,6 +119,20 @@ __global__ void __launch_bounds__(256) topk_rows_kernel(const uint16_t* __restri
     select_row<uint16_t>(keys + row * nk_pad, Nk, nk_pad, nsel, cap, idx + row * cap, cnt + row, lane);
 }
 
+// The same for a grid with a "first part" (the conditioning frames of video continuation): query blocks of the first
+// part take nsel_first blocks among the key blocks of the first part, all other query blocks nsel blocks among all.
+__global__ void __launch_bounds__(256) topk_rows_split_kernel(const uint16_t* __restrict__ keys, long long rows, int Nq, int Nk, int nk_pad,
+                                                             SelectSplit sp, int nsel, int cap, int32_t* __restrict__ idx,
+                                                             int32_t* __restrict__ cnt) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int qblk = (int)(row % Nq);
+    const bool first = ((qblk / sp.hw_q) % sp.period_q) < sp.split_q;
+    const KeyMask mask{sp.hw_k, first ? sp.period_k : 0, sp.split_k};
+    select_row<uint16_t>(keys + row * nk_pad, Nk, nk_pad, first ? sp.nsel_first : nsel, cap, idx + row * cap, cnt + row, lane, mask);
+}
+
 template <typename T, int D>
 cudaError_t launch_gemm(const void* qc, const void* kc, int BH, int Nq, int Nk, int nk_pad, uint16_t* keys, cudaStream_t st) {
     dim3 grid((nk_pad + kTile - 1) / kTile, (Nq + kTile - 1) / kTile, BH);
@@ -151,7 +165,7 @@ cudaError_t launch_score_keys(int dtype, const void* qc, const void* kc, int BH,
 }
 
 cudaError_t launch_score_gemm_topk(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, int nsel, int cap,
-                                   int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why) {
+                                   int32_t* idx, int32_t* cnt, void* keys_ws, cudaStream_t st, const char** why, const SelectSplit* split) {
     if (BH == 0 || Nq == 0) return cudaSuccess;
     if (score_keys_bytes(dtype, BH, Nq, Nk, D) == 0) {
         *why = "the two-kernel form takes bf16 or fp16 with head_dim 64 or 128";
@@ -167,7 +181,15 @@ cudaError_t launch_score_gemm_topk(int dtype, const void* qc, const void* kc, in
         e = D == 128 ? launch_gemm<__half, 128>(qc, kc, BH, Nq, Nk, nk_pad, keys, st) : launch_gemm<__half, 64>(qc, kc, BH, Nq, Nk, nk_pad, keys, st);
     if (e != cudaSuccess) return e;
     const long long rows = (long long)BH * Nq;
-    topk_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(keys, rows, Nk, nk_pad, nsel, cap, idx, cnt);
+    if (split != nullptr) {
+        if (nk_pad > 2 * 32 * kRegWords) {
+            *why = "the split selection handles up to 1536 key blocks";
+            return cudaErrorInvalidValue;
+        }
+        topk_rows_split_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(keys, rows, Nq, Nk, nk_pad, *split, nsel, cap, idx, cnt);
+    } else {
+        topk_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(keys, rows, Nk, nk_pad, nsel, cap, idx, cnt);
+    }
     return cudaGetLastError();
 }
 

@@ -21,7 +21,7 @@ def _reference_form(q, k, v, shape, nc, fn, **params):
 
 @pytest.mark.parametrize("params", [dict(sparsity=0.5), dict(sparsity=None, cdf_threshold=0.7)])
 @pytest.mark.parametrize("strided", [False, True])
-@pytest.mark.parametrize("shape,nc", [((12, 8, 8), 4), ((10, 8, 8), 3)])  # whole blocks: one launch; ragged: two launches on views
+@pytest.mark.parametrize("shape,nc", [((12, 8, 8), 4), ((16, 8, 12), 12), ((10, 8, 8), 3)])  # whole blocks: one selection, one attention launch; ragged: two launches on views
 def test_cond_split_equals_two_calls(params, strided, shape, nc):
     heads, D = 3, 128
     ragged = nc % 4 != 0

@@ -111,6 +111,16 @@ def _worker(rank, world, port, heads):
                 torch.cuda.synchronize()
                 assert torch.equal(fused, want)
         L.check(L.lib().lcbsa_check_device_status())
+        # video continuation: the first 4 of every rank's 8 frames are conditioning frames; one exchange and one attention
+        # launch per stage against the reference's formulation (two exchanges, two calls on copies, concatenated)
+        kw = dict(sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
+        want_cond = CP._generic_cond(q, k, v, grid, 4, world, dict(kw, cdf_threshold=None))
+        for _ in range(2):
+            got_cond = flash_attn_bsa_3d_ulysses(q, k, v, grid, num_cond_latents=4, **kw)
+            torch.cuda.synchronize()
+            assert torch.equal(got_cond, want_cond)
+        assert not torch.equal(got_cond, want)
+        L.check(L.lib().lcbsa_check_device_status())
         # host-resident form: pinned shards in, pinned result out, pipelined by head chunk
         from longcat_video_b200.context_parallel.bsa_context_parallel import flash_attn_bsa_3d_ulysses_host
 
