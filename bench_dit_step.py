@@ -16,7 +16,8 @@ Two arms on identical modules:
   drop-in    the module global ``longcat_video.modules.attention.flash_attn_bsa_3d`` rebound to this library's op
              (one GPU), or ``Attention._process_attn`` rebound to ``flash_attn_bsa_3d_ulysses`` (context parallel)
 Rank 0 prints ONE JSON line: ms per block for both arms, the attention's share, and the difference of the outputs.
-Latent grid: the reference-legal twin 24x32x52 of the 480p grid (the reference asserts divisibility by the block).
+Latent grid: the reference-legal twin 24x32x52 of the 480p grid (the reference asserts divisibility by the block); under
+context parallelism 24x32x64, whose H x W plane splits over 2, 4 and 8 ranks into parts that divide by the block.
 Synthetic N(0,1) activations and N(0, 0.02) weights; no checkpoint or dataset is involved.
 """
 from __future__ import annotations
@@ -64,12 +65,16 @@ def main():
     ap.add_argument("--blocks", type=int, default=4)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--grid", type=int, nargs=3, default=[24, 32, 52])
+    ap.add_argument("--grid", type=int, nargs=3, default=None,
+                    help="latent grid; default 24 32 52 on one GPU (the legal twin of 480p), 24 32 64 under context parallelism "
+                         "(every rank's part of the H x W plane must divide by the 4x4 block)")
     ap.add_argument("--sparsity", type=float, default=0.9375)
     ap.add_argument("--text-tokens", type=int, default=512)
     args = ap.parse_args()
 
     world, rank, local_rank = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    if args.grid is None:
+        args.grid = [24, 32, 52] if world == 1 else [24, 32, 64]
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     mods, why = load_reference()
