@@ -325,10 +325,13 @@ int lcbsa_attn_fwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const char* why = "";
     cudaError_t e;
-    if (impl == LCBSA_ATTN_AUTO) impl = lcbsa::attn_tc_supported(a, &why) ? LCBSA_ATTN_TC : LCBSA_ATTN_MMA;
+    // two tcgen05 kernels: one for 64-token blocks, one for 128-token blocks (the reference's default [4, 4, 8])
+    const char* why128 = "";
+    const bool tc64 = lcbsa::attn_tc_supported(a, &why), tc128 = !tc64 && lcbsa::attn_tc128_supported(a, &why128);
+    if (impl == LCBSA_ATTN_AUTO) impl = (tc64 || tc128) ? LCBSA_ATTN_TC : LCBSA_ATTN_MMA;
     if (impl == LCBSA_ATTN_TC) {
-        if (!lcbsa::attn_tc_supported(a, &why)) return fail(LCBSA_EUNSUPPORTED, "attn_fwd (tcgen05): %s", why);
-        e = lcbsa::launch_attn_tc(a, st, &why);
+        if (!tc64 && !tc128) return fail(LCBSA_EUNSUPPORTED, "attn_fwd (tcgen05): %s", a.gq.bs == 128 ? why128 : why);
+        e = tc64 ? lcbsa::launch_attn_tc(a, st, &why) : lcbsa::launch_attn_tc128(a, st, &why);
     } else if (impl == LCBSA_ATTN_MMA) {
         e = lcbsa::launch_attn_mma(a, st, &why);
     } else {
@@ -370,8 +373,11 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
     a.status = device_status_ptr();
     if (!a.status) return fail(LCBSA_ECUDA, "attn_fwd_scatter: cannot resolve the device status words");
     const char* why = "";
-    if (!lcbsa::attn_tc_supported(a, &why)) return fail(LCBSA_EUNSUPPORTED, "attn_fwd_scatter (tcgen05): %s", why);
-    cudaError_t e = lcbsa::launch_attn_tc(a, static_cast<cudaStream_t>(stream), &why);
+    const char* why128 = "";
+    const bool tc64 = lcbsa::attn_tc_supported(a, &why), tc128 = !tc64 && lcbsa::attn_tc128_supported(a, &why128);
+    if (!tc64 && !tc128) return fail(LCBSA_EUNSUPPORTED, "attn_fwd_scatter (tcgen05): %s", a.gq.bs == 128 ? why128 : why);
+    cudaError_t e = tc64 ? lcbsa::launch_attn_tc(a, static_cast<cudaStream_t>(stream), &why)
+                         : lcbsa::launch_attn_tc128(a, static_cast<cudaStream_t>(stream), &why);
     if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_scatter", why);
     return LCBSA_OK;
 }

@@ -129,6 +129,9 @@ struct AttnArgs {
 cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why);
 bool attn_tc_supported(const AttnArgs& a, const char** why);
+// the same for 128-token query and key blocks (attn_tc128.cu)
+cudaError_t launch_attn_tc128(const AttnArgs& a, cudaStream_t st, const char** why);
+bool attn_tc128_supported(const AttnArgs& a, const char** why);
 cudaError_t launch_score_keys(int dtype, const void* qc, const void* kc, int BH, int Nq, int Nk, int D, void* keys_ws, cudaStream_t st,
                               const char** why);
 // cdf_threshold selectors on the keys of launch_score_keys (select_cdf.cu): idx [rows, Nk] sorted by descending weight, cnt [rows]
