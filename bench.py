@@ -14,6 +14,7 @@ One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 p
   roofline   the attention kernel against the measured bf16 tensor peak (events around that launch, inside the
              timed region); roofline_select does the same for the block-select stage against the measured HBM rate.
   literal_720p   a short leg on BASELINE's literal 24x45x80 grid (ragged: through ``allow_ragged=True``).
+  default_blocks_720p  a short leg with the entry point's default [4, 4, 8] blocks (128 tokens) on the same tensors.
   gpu_reference  the reference's own Triton BSA (baseline/_ref, see baseline/install_reference.py) timed on the
              same GPU and inputs, outside the timed region of this library; absent checkout -> "unavailable".
   cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
@@ -43,13 +44,14 @@ METRIC = "bsa_fwd_effective_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch over the bytes of q, k, v and out, from
-# the ncu capture summarised in profiles/attn_tc_kernel_480p_16heads.md (599.2 MB against 654.3 MB).  K and V of a
-# head are re-read from L2, so the traffic of a launch grows with the tensors, not with the selected blocks.
-NCU_ATTN_DRAM_PER_IO_BYTE = 599.2 / 654.3
-# the same for the block-select stage (profiles/select_kernels_480p_16heads.md): two pool launches read q and k
-# once (163.6 + 4.1 MB each against 163.6 algorithmic), the score and top-k launches add 5.2 + 12.8 MB.
-NCU_SELECT_DRAM_PER_IO_BYTE = (2 * 167.7 + 5.2 + 12.8) / (2 * 163.6)
-
+# the ncu capture summarised in profiles/attn_tc_kernel_480p_16heads.md (454.0 MB read + 150.7 MB written against
+# 654.3 MB).  K and V of a head are re-read from L2, so the traffic of a launch grows with the tensors, not with the
+# selected blocks.
+NCU_ATTN_DRAM_PER_IO_BYTE = (454.0 + 150.7) / 654.3
+# the same for the block-select stage at 720p / 32 heads (profiles/select_kernels_720p_32heads.md): the pool launch
+# reads q and k once (1524 MB read, 65 MB written against 1415.6 MB of q and k), the score launch adds 23.6 + 76 MB
+# and the top-k launch 135.7 + 8.6 MB (its 16-bit keys no longer fit in L2 at this size).
+NCU_SELECT_DRAM_PER_IO_BYTE = (1524.0 + 65.0 + 23.6 + 76.0 + 135.7 + 8.6) / 1415.6
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -217,6 +219,7 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-literal", action="store_true", help="no extra leg on the literal 24x45x80 grid")
+    ap.add_argument("--skip-blocks128", action="store_true", help="no extra leg with the default [4, 4, 8] blocks")
     ap.add_argument("--skip-gpu-reference", action="store_true", help="do not time the reference's Triton kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -262,7 +265,7 @@ def main():
     params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
     ragged = is_ragged(wl)
     timer = StepTimer(B, q, k, v, wl, dict(params, allow_ragged=ragged))
-    launches_per_step = 5  # pool(q), pool(k), score GEMM, top-k, attention
+    launches_per_step = 4  # pool (q and k in one launch), score GEMM, top-k, attention
 
     sampler = ClockSampler(local_rank)
     sampler.start()  # nvidia-smi needs a moment to start: long before the timed region
@@ -296,9 +299,10 @@ def main():
                 "traffic": NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes,
                 "traffic_source": "ncu capture of 480p_legal/16 heads scaled by the bytes of q,k,v,out"}
     sel_gbs = select_bytes / ms_select / 1e6
-    roofline_select = {"bound": "hbm", "kernel": "pool_kernel x2 + score_gemm_kernel + topk_rows_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
+    roofline_select = {"bound": "hbm", "kernel": "pool_kernel + score_gemm_kernel + topk_rows_kernel", "achieved": sel_gbs, "peak": peaks["hbm_gbs"],
                        "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"], "peak_source": peak_src, "ms_per_stage": ms_select,
-                       "traffic": NCU_SELECT_DRAM_PER_IO_BYTE * select_bytes}
+                       "traffic": NCU_SELECT_DRAM_PER_IO_BYTE * select_bytes,
+                       "traffic_source": "ncu capture of 720p_legal/32 heads scaled by the bytes of q and k"}
 
     # ------------------------------------------------------------------ BASELINE's literal 720p grid (ragged), short leg
     literal = None
@@ -317,6 +321,25 @@ def main():
                    "attention_frac_of_peak": lflops / lms_att / 1e9 / peaks["bf16_tflops"],
                    "note": "extension: ragged grid through allow_ragged=True, flops counted on present rows and keys only"}
         del lq, lk, lv, lt, li, lc
+
+    # ------------------------------------------------------------------ the entry point's default block shape, short leg
+    blocks128 = None
+    if wl.name == "720p_legal" and not args.skip_blocks128:
+        bw = WORKLOADS["720p_blocks128"]  # same grid and seed, [4, 4, 8] blocks of 128 tokens
+        bparams = dict(params, chunk_3d_shape_q=list(bw.chunk), chunk_3d_shape_k=list(bw.chunk))
+        bt = StepTimer(B, q, k, v, bw, dict(bparams, allow_ragged=False))
+        for _ in range(3):
+            bt.call()
+        bi, bc = B.get_select_indices(q, k, bw.grid_q, bw.grid_k, bw.sparsity, None, bw.chunk, bw.chunk)
+        bflops = algorithmic_flops(bw, heads, int(bc.flatten()[0]))
+        bms, bms_sel, bms_att = bt.run(5)
+        L.check(L.lib().lcbsa_check_device_status())
+        blocks128 = {"workload": bw.name, "block": list(bw.chunk), "selected_blocks": int(bc.flatten()[0]), "steps": 5,
+                     "ms_per_step": bms, "ms_select": bms_sel, "ms_attention": bms_att, "algorithmic_tflop": bflops / 1e12,
+                     "value": bflops / bms / 1e9, "attention_tflops": bflops / bms_att / 1e9,
+                     "attention_frac_of_peak": bflops / bms_att / 1e9 / peaks["bf16_tflops"], "kernel": "attn_tc128_kernel",
+                     "note": "the chunk shape flash_attn_bsa_3d takes when none is passed; the headline stays on BASELINE's 4x4x4 blocks"}
+        del bt, bi, bc
 
     # ------------------------------------------------------------------ the reference's Triton kernels on this GPU
     gpu_reference = None
@@ -362,7 +385,7 @@ def main():
                        "algorithmic_tflop": flops / 1e12, "ms_select": ms_select, "ms_attention": ms_attn,
                        "timed_call": "flash_attn_bsa_3d, eager", "ms_per_step_cuda_graph": ms_graph,
                        "l2": "inputs (q,k,v,out) exceed the 126 MB L2; no flush between iterations", "parallelism": "1 GPU",
-                       "literal_720p": literal},
+                       "literal_720p": literal, "default_blocks_720p": blocks128},
             "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_reference": gpu_reference, "clocks": clocks, "gpu_launches": gpu_launches}
     print(json.dumps(line))

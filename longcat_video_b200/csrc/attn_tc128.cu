@@ -432,8 +432,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
             float m_ref = -INFINITY, l_sum = 0.f;
             bool first = true;  // no block of this item seen yet by this warpgroup
 
+            // ragged grids: the block index of a round is fetched a round ahead, so that the global load never sits
+            // between S and the softmax (unit i belongs to list entry i >> 1)
+            int blk_ahead = (P.gk.ragged && wg < n_act) ? my_list[0] : 0;
             for (int i = wg; i < n_iter && ok; i += 2, ++rr) {
                 const bool active = i < n_act;
+                const int blk_now = blk_ahead;
+                if (P.gk.ragged && i + 2 < n_act) blk_ahead = my_list[(i + 2) >> 1];
                 const int buf = rr & 1;
                 const unsigned bph = (rr >> 1) & 1;
                 ok = mbar_wait_warp(bar_s_full(wg, buf), bph, ctl, 80 + wg, rr);
@@ -447,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                 uint4 pk[8];  // this row of P in the input dtype, 8 keys per 16-byte chunk
                 if (active) {
                     if (P.gk.ragged) {  // keys of a partial block that lie outside the grid
-                        const int blk = my_list[i >> 1];
+                        const int blk = blk_now;
                         int bt, bhh, bw;
                         block_coords(P.gk, blk, bt, bhh, bw);
                         // tokens left along each axis from the first token of this unit
@@ -458,11 +463,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                             else vw -= P.sub_len;
                         }
                         if (vt < P.gu.ct || vh < P.gu.ch || vw < P.gu.cw) {
+                            const uint64_t present = slot_mask64(P.gu.ct, P.gu.ch, P.gu.cw, vt, vh, vw);
+                            const uint32_t p_lo = (uint32_t)present, p_hi = (uint32_t)(present >> 32);
 #pragma unroll
-                            for (int j = 0; j < 64; ++j) {
-                                int lt, lh, lw;
-                                slot_coords(P.gu, j, lt, lh, lw);
-                                if (lt >= vt || lh >= vh || lw >= vw) sr[j] = 0xff800000u;  // -inf
+                            for (int j = 0; j < 32; ++j) {
+                                if (!((p_lo >> j) & 1u)) sr[j] = 0xff800000u;  // -inf
+                                if (!((p_hi >> j) & 1u)) sr[32 + j] = 0xff800000u;
                             }
                         }
                     }

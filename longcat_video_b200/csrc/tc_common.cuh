@@ -228,6 +228,22 @@ __device__ __forceinline__ uint32_t instr_desc(bool bf16, int M, int N, int b_mn
            ((uint32_t)(M >> 4) << 24);
 }
 
+// Which of the 64 slots of a block (w fastest, then h, then t) lie inside the first vt x vh x vw tokens of it: bit j
+// for slot j.  The extents are powers of two whose product is 64 (any 3-D factorisation of 64 is), so a row of cw
+// slots and a plane of cw * ch slots tile the 64 bits exactly.  Limits below 1 give an empty mask.
+__device__ __forceinline__ uint64_t slot_mask64(int ct, int ch, int cw, int vt, int vh, int vw) {
+    auto low = [](int n) { return n >= 64 ? ~0ull : ((1ull << n) - 1ull); };
+    vt = max(0, min(vt, ct));
+    vh = max(0, min(vh, ch));
+    vw = max(0, min(vw, cw));
+    const int plane = cw * ch;
+    uint64_t mw = low(vw);
+    for (int s = cw; s < 64; s <<= 1) mw |= mw << s;
+    uint64_t mh = low(vh * cw);
+    for (int s = plane; s < 64; s <<= 1) mh |= mh << s;
+    return mw & mh & low(vt * plane);
+}
+
 struct Coord {
     int c1, c2, c3, c4;
 };

@@ -30,7 +30,7 @@ SEEDED = {
 
 
 def _impls(wl):
-    tc_ok = wl.head_dim == 128 and wl.chunk[0] * wl.chunk[1] * wl.chunk[2] == 64
+    tc_ok = wl.head_dim == 128 and wl.chunk[0] * wl.chunk[1] * wl.chunk[2] in (64, 128)  # one tcgen05 kernel for each
     return [TC, MMA] if tc_ok else [MMA]
 
 
@@ -60,6 +60,29 @@ def test_golden_cases(name):
         out = _attn(q, k, v, wl, idx, cnt, impl)
         print(name, impl, _check(out, ref))
         L.check(L.lib().lcbsa_check_device_status())
+
+
+def test_config1_tensors_through_the_whole_forward():
+    """The reference's CPU-runnable configuration (B=1, 4 heads x 128, grid 4x8x8, 4x4x4 blocks, sparsity 0.5, N(0,1)
+    fp32).  fp32: the CUDA block-select reproduces the lists the reference's own functions produced (fixture
+    cfg1_fp32) and the attention kernels refuse the dtype.  The same tensors in bf16 go through the drop-in entry point
+    and are held against the oracle."""
+    wl, _ = CASES["cfg1_fp32"]
+    gold = load_golden("cfg1_fp32")
+    q, k, v = make_qkv(wl)
+    idx, cnt = B.get_select_indices(q.cuda(), k.cuda(), wl.grid_q, wl.grid_k, wl.sparsity, None, wl.chunk, wl.chunk)
+    want = torch.sort(torch.from_numpy(gold["idx"].astype("int32")), dim=-1).values
+    assert torch.equal(idx.cpu()[..., :want.shape[-1]], want)
+    with pytest.raises(Exception):
+        B.flash_attn_bsa_3d(q.cuda(), k.cuda(), v.cuda(), wl.grid_q, wl.grid_k, sparsity=wl.sparsity,
+                            chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
+    qb, kb, vb = (t.to(torch.bfloat16) for t in (q, k, v))
+    out = B.flash_attn_bsa_3d(qb.cuda(), kb.cuda(), vb.cuda(), wl.grid_q, wl.grid_k, sparsity=wl.sparsity,
+                              chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
+    L.check(L.lib().lcbsa_check_device_status())
+    oi, oc, _, _ = O.block_select(qb, kb, wl.grid_q, wl.grid_k, wl.sparsity, wl.chunk, wl.chunk)
+    ref, _ = O.attention(qb, kb, vb, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk, oi, oc)
+    print("cfg1 in bf16", _check(out, ref))
 
 
 @pytest.mark.parametrize("name", list(SEEDED))

@@ -24,7 +24,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, heads):
+def _worker(rank, world, port, heads, chunk=(4, 4, 4)):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -40,7 +40,6 @@ def _worker(rank, world, port, heads):
         cpu_.init_context_parallel(world, rank, world)
         sh, sw = cpu_.get_optimal_split(world)
         T, Hh, W = 8, 16, 16
-        chunk = (4, 4, 4)
         local_grid = (T, Hh // sh, W // sw)
         grid = (world * T, Hh // sh, W // sw)
         Sl = local_grid[0] * local_grid[1] * local_grid[2]
@@ -137,10 +136,11 @@ def _worker(rank, world, port, heads):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("heads", [4, 16])
-def test_peer_exchange_matches_nccl(heads):
+@pytest.mark.parametrize("heads,chunk", [(4, (4, 4, 4)), (16, (4, 4, 4)), (4, (4, 4, 8))])
+def test_peer_exchange_matches_nccl(heads, chunk):
+    """(4, 4, 8): the 128-token blocks that flash_attn_bsa_3d takes by default, served by the other tcgen05 kernel."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
-    mp.spawn(_worker, args=(2, _free_port(), heads), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), heads, chunk), nprocs=2, join=True)
