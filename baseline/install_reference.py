@@ -45,4 +45,4 @@ def install(src_root: str) -> str:
 
 
 if __name__ == "__main__":
-    print(install(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LONGCAT_VIDEO_ROOT", "/root/reference")))
+    print(install(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LONGCAT_VIDEO_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))))

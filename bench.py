@@ -292,7 +292,8 @@ def main():
     select_bytes = es * wl.batch * heads * (wl.sq + wl.sk) * wl.head_dim  # read Q and K once
     attn_io_bytes = es * wl.batch * heads * (2 * wl.sq + 2 * wl.sk) * wl.head_dim  # q, out, k, v once
     attn_tf = flops / ms_attn / 1e9
-    roofline = {"bound": "tensor", "kernel": "attn_tc_kernel",
+    block_tokens = wl.chunk[0] * wl.chunk[1] * wl.chunk[2]
+    roofline = {"bound": "tensor", "kernel": "attn_tc128_kernel" if block_tokens == 128 else "attn_tc_kernel",
                 "achieved": attn_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
                 "peak_source": f"{peak_src} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
                 "ms_per_launch": ms_attn,
@@ -339,6 +340,11 @@ def main():
                      "value": bflops / bms / 1e9, "attention_tflops": bflops / bms_att / 1e9,
                      "attention_frac_of_peak": bflops / bms_att / 1e9 / peaks["bf16_tflops"], "kernel": "attn_tc128_kernel",
                      "note": "the chunk shape flash_attn_bsa_3d takes when none is passed; the headline stays on BASELINE's 4x4x4 blocks"}
+        if not args.skip_gpu_reference:  # the reference's Triton kernel with BLOCK_M = BLOCK_N = 128 on the same tensors
+            bref = gpu_reference_leg(bw, q, k, v, bparams, bflops, steps=3, warmup=2)
+            blocks128["gpu_reference"] = bref
+            if "ms_per_step" in bref:
+                blocks128["speedup_of_this_library"] = bref["ms_per_step"] / bms
         del bt, bi, bc
 
     # ------------------------------------------------------------------ the reference's Triton kernels on this GPU

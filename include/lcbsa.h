@@ -203,8 +203,10 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
  * CUDA allocator).  No counterpart in the reference: there the workspace is whatever PyTorch allocates.
  * The scratch is a device array built into the library, lcbsa_static_scratch_bytes() (32 MiB) per
  * GPU, reserved on every GPU that loads the library until the process exits.  Problems whose pooled Q
- * and K do not fit are refused with LCBSA_EWORKSPACE.  The call allocates nothing; it launches the same
- * three kernels as lcbsa_block_select.  All calls on one device share the array: calls that can
+ * and K do not fit are refused with LCBSA_EWORKSPACE.  The call allocates nothing; it launches what
+ * lcbsa_block_select launches on a workspace of that size: pool, score GEMM and top-k kernels with the
+ * 16-bit score keys also in the array when lcbsa_select_workspace_bytes_fast() fits in it, else the pool
+ * kernel and the fused score + top-k kernel.  All calls on one device share the array: calls that can
  * overlap on the GPU race and must be ordered by the caller.  The first call on a device resolves
  * the array's address and should be made outside stream capture.
  */

@@ -148,7 +148,7 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
     if not torch.cuda.is_current_stream_capturing():
         for t in (q, k, v):
             t.record_stream(side)
-    scatter = _SCATTER_OUT and D == 128 and chunk[0] * chunk[1] * chunk[2] == 64
+    scatter = _SCATTER_OUT and D == 128 and chunk[0] * chunk[1] * chunk[2] in (64, 128)  # what the tcgen05 kernels take
     stages = _stages_scattered(hn) if scatter else U._stages(hn, U._heads_per_group(hn))
     phases = _PhaseTimer(main) if _PHASES else None
 
@@ -157,10 +157,12 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
     if phases:
         phases.mark("pool_scatter+barrier")
 
-    # 2. every stage's q, k, v slabs are queued on the copy engines at once (side stream, one barrier per stage): the
-    #    receive regions of the stages are disjoint and nothing but the inputs is needed to fill them, so the slabs of
-    #    later stages travel while the block lists are selected and the earlier stages compute
-    evs = [ex.push_in((q, k, v), lo, hi) for lo, hi in stages]
+    # 2. the first stage's q, k, v slabs go onto the copy engines (side stream, one barrier per stage).  The receive
+    #    regions of the stages are disjoint and nothing but the inputs is needed to fill them, so every push could be
+    #    queued here; but queueing a push costs the host tens of copies, and the main stream would sit idle behind
+    #    them.  So the host queues stage g + 1 right after it has launched the attention of stage g: the slabs still
+    #    travel a whole stage ahead of their use, and the kernels are never waiting for the host.
+    evs = [ex.push_in((q, k, v), *stages[0])]
 
     # 3. block lists of all local heads while the first slabs travel
     qc, kc = ex.pooled_received(nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
@@ -189,6 +191,8 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
             ev_out = ex.push_out(o, lo)
         if phases:
             phases.mark(f"attention_{g}")
+        if g + 1 < len(stages):
+            evs.append(ex.push_in((q, k, v), *stages[g + 1]))
     if scatter:
         ex.finish_scatter()
     else:

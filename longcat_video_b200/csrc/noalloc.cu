@@ -11,9 +11,17 @@
 // There is one array per device and every call on that device uses it, so
 //   * two calls whose kernels can overlap on the GPU (different streams, no ordering between them)
 //     race on the scratch and must be serialised by the caller;
-//   * the array still holds the pooled rows of the previous call when the next one starts; nothing in
-//     it has to be cleared, because each call overwrites every byte it later reads (the two pool
-//     kernels fill exactly the rows that the score kernel consumes).
+//   * the array still holds the data of the previous call when the next one starts; nothing in it has
+//     to be cleared, because each call overwrites every byte it later reads (the pool kernel fills
+//     exactly the rows that the score kernel consumes, the score kernel every key that the top-k
+//     kernel reads).
+//
+// Which kernels run depends on what fits in the array, exactly as for a caller-provided workspace of
+// that size.  Pooled rows and 16-bit score keys both fit (16-bit inputs, head_dim 64 or 128;
+// lcbsa_select_workspace_bytes_fast <= 32 MiB): pool_kernel, score_gemm_kernel, topk_rows_kernel,
+// with the keys in the array behind the pooled rows.  Only the pooled rows fit (a 720p layer with 32
+// heads: 23.6 MB of pooled rows, 135 MB of keys), or fp32 inputs: pool_kernel and the fused
+// score_topk_kernel, whose scores never leave shared memory.
 //
 // Inside host code the name of a __device__ array is only a handle, not a device address, so the
 // address is resolved with cudaGetSymbolAddress -- once per device, with that device current, by the
@@ -88,7 +96,8 @@ int lcbsa_block_select_static(const LcbsaTensor* q, const LcbsaTensor* k, const 
         lcbsa::set_last_error(msg);
         return LCBSA_ECUDA;
     }
-    // From here on this is the ordinary path on a different workspace: three kernel launches, no allocation.
+    // From here on this is the ordinary path on a workspace of kStaticScratchBytes: lcbsa_block_select picks the
+    // three-kernel form when the score keys fit behind the pooled rows and the two-kernel form otherwise; no allocation.
     return lcbsa_block_select(q, k, gq, gk, nsel, cap, idx, cnt, scratch, kStaticScratchBytes, stream);
 }
 
