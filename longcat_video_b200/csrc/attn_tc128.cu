@@ -92,7 +92,9 @@ __device__ __forceinline__ int clamp_cnt(const TcParams& P, int bh, int qt) {
     return qt < P.nq ? min(max(P.cnt[(long long)bh * P.nq + qt], 0), P.cap) : 0;
 }
 
-template <bool kBf16>
+// kRagged: the key grid has partial blocks.  The masking code exists only in that instantiation, which keeps the
+// instruction stream of the softmax loop of whole grids short (the loop is sensitive to instruction fetch).
+template <bool kBf16, bool kRagged>
 __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -434,11 +436,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
 
             // ragged grids: the block index of a round is fetched a round ahead, so that the global load never sits
             // between S and the softmax (unit i belongs to list entry i >> 1)
-            int blk_ahead = (P.gk.ragged && wg < n_act) ? my_list[0] : 0;
+            int blk_ahead = (kRagged && wg < n_act) ? my_list[0] : 0;
             for (int i = wg; i < n_iter && ok; i += 2, ++rr) {
                 const bool active = i < n_act;
                 const int blk_now = blk_ahead;
-                if (P.gk.ragged && i + 2 < n_act) blk_ahead = my_list[(i + 2) >> 1];
+                if (kRagged && i + 2 < n_act) blk_ahead = my_list[(i + 2) >> 1];
                 const int buf = rr & 1;
                 const unsigned bph = (rr >> 1) & 1;
                 ok = mbar_wait_warp(bar_s_full(wg, buf), bph, ctl, 80 + wg, rr);
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                 bool need = false;
                 uint4 pk[8];  // this row of P in the input dtype, 8 keys per 16-byte chunk
                 if (active) {
-                    if (P.gk.ragged) {  // keys of a partial block that lie outside the grid
+                    if (kRagged) {  // keys of a partial block that lie outside the grid
                         const int blk = blk_now;
                         int bt, bhh, bw;
                         block_coords(P.gk, blk, bt, bhh, bw);
@@ -476,39 +478,75 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                     // the row maximum is tracked on the side; only if the maximum has moved by more than 2^8
                     // (or this is the warpgroup's first block) is the pass repeated with the new reference.
                     auto probs = [&](float mref, float& rsum) {
-                        float r4[4] = {0.f, 0.f, 0.f, 0.f};
+                        // two keys per instruction where the machine has packed fp32 forms (fma, add); the four partial
+                        // sums take the keys j = 0, 1, 2, 3 (mod 4) in ascending order
+                        const float2 sc2 = make_float2(P.scale2, P.scale2), nm2 = make_float2(-mref, -mref);
+                        float2 r01 = make_float2(0.f, 0.f), r23 = make_float2(0.f, 0.f);
 #pragma unroll
                         for (int cch = 0; cch < 8; ++cch) {
-                            float pv[8];
+                            float2 e[4];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                pv[j] = ex2(fmaf(__uint_as_float(sr[cch * 8 + j]), P.scale2, -mref));
-                                r4[j & 3] += pv[j];
+                            for (int jp = 0; jp < 4; ++jp) {
+                                const float2 s2 = make_float2(__uint_as_float(sr[cch * 8 + 2 * jp]), __uint_as_float(sr[cch * 8 + 2 * jp + 1]));
+                                const float2 x = __ffma2_rn(s2, sc2, nm2);
+                                e[jp] = make_float2(ex2(x.x), ex2(x.y));
                             }
-                            pk[cch].x = pack2(bf16, pv[0], pv[1]);
-                            pk[cch].y = pack2(bf16, pv[2], pv[3]);
-                            pk[cch].z = pack2(bf16, pv[4], pv[5]);
-                            pk[cch].w = pack2(bf16, pv[6], pv[7]);
+                            r01 = __fadd2_rn(r01, e[0]);
+                            r23 = __fadd2_rn(r23, e[1]);
+                            r01 = __fadd2_rn(r01, e[2]);
+                            r23 = __fadd2_rn(r23, e[3]);
+                            pk[cch].x = pack2(bf16, e[0].x, e[0].y);
+                            pk[cch].y = pack2(bf16, e[1].x, e[1].y);
+                            pk[cch].z = pack2(bf16, e[2].x, e[2].y);
+                            pk[cch].w = pack2(bf16, e[3].x, e[3].y);
                         }
-                        rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+                        rsum = (r01.x + r01.y) + (r23.x + r23.y);
+                    };
+                    // the reference maximum this row would have after this block (in units of log2)
+                    auto row_reference = [&]() {
+                        float mx8[8];  // eight chains of eight values, three at a time
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            auto sv = [&](int i) { return __uint_as_float(sr[8 * i + k]); };
+                            mx8[k] = fmaxf(max3(max3(max3(sv(0), sv(1), sv(2)), sv(3), sv(4)), sv(5), sv(6)), sv(7));
+                        }
+                        const float mx = fmaxf(max3(max3(mx8[0], mx8[1], mx8[2]), mx8[3], mx8[4]), max3(mx8[5], mx8[6], mx8[7]));
+                        return first ? mx * P.scale2 : fmaxf(m_ref, mx * P.scale2);  // no reference yet: m_ref is a placeholder
                     };
                     float rs = 0.f;
-                    if (!first) probs(m_ref, rs);
-                    float mx8[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) mx8[j] = __uint_as_float(sr[j]);
-#pragma unroll
-                    for (int j = 8; j < 64; ++j) mx8[j & 7] = fmaxf(mx8[j & 7], __uint_as_float(sr[j]));
-                    const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                           fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-                    const float m_new = first ? mx * P.scale2 : fmaxf(m_ref, mx * P.scale2);  // no reference yet: m_ref is a placeholder
-                    if (first || m_new - m_ref > 8.f) {
-                        if (!first) {
-                            need = true;
-                            alpha = ex2(m_ref - m_new);
+                    float m_new = m_ref;
+                    if (kRagged) {
+                        // the instantiation with the masking code: a single copy of the pass in the instruction stream.
+                        // The loop body runs once in the common case (pass, then the row maximum, which confirms the
+                        // reference) and twice when the reference moves; for the warpgroup's first block the first
+                        // pass is skipped.
+                        bool run_pass = !first, decided = false;
+#pragma unroll 1
+                        for (int turn = 0; turn < 2; ++turn) {
+                            if (run_pass) probs(m_ref, rs);
+                            if (decided) break;
+                            m_new = row_reference();
+                            run_pass = first || m_new - m_ref > 8.f;
+                            if (!run_pass) break;
+                            if (!first) {
+                                need = true;
+                                alpha = ex2(m_ref - m_new);
+                            }
+                            m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+                            decided = true;
                         }
-                        m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-                        probs(m_ref, rs);
+                    } else {
+                        // whole grids: straight-line code, the second copy of the pass off the common path
+                        if (!first) probs(m_ref, rs);
+                        m_new = row_reference();
+                        if (LCBSA_UNLIKELY(first || m_new - m_ref > 8.f)) {
+                            if (!first) {
+                                need = true;
+                                alpha = ex2(m_ref - m_new);
+                            }
+                            m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+                            probs(m_ref, rs);
+                        }
                     }
                     l_sum = l_sum * alpha + rs;  // alpha is 1 unless this row's reference maximum moved
                     // a unit that lies wholly outside a ragged grid leaves no reference behind: the next one is the first
@@ -519,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                 const bool any_need = __any_sync(0xffffffffu, need);
                 // O is rescaled only at rest: the warpgroup's PV of the round before has to be finished
                 // (need implies that this is not the warpgroup's first round of the item, so rr > 0)
-                if (any_need) {
+                if (LCBSA_UNLIKELY(any_need)) {
                     ok = mbar_wait_warp(bar_pv_done(wg, buf ^ 1), ((rr - 1) >> 1) & 1, ctl, 92 + wg, rr);
                     if (!ok) break;
                 }
@@ -534,18 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                     }
                     tc_st32(tm_s + 64u * buf, pr);
                 }
-                if (any_need) {  // rare: only when a row maximum jumps
-                    tc_fence_after();
-#pragma unroll
-                    for (int cch = 0; cch < 4; ++cch) {
-                        uint32_t orr[32];
-                        tc_ld32(tm_o_mine + 32 * cch, orr);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
-                        tc_st32(tm_o_mine + 32 * cch, orr);
-                    }
-                }
+                if (LCBSA_UNLIKELY(any_need)) tc_scale_row128(tm_o_mine, alpha);  // rare: only when a row maximum jumps
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive_elect(bar_p_full(wg, buf));
@@ -734,8 +761,10 @@ cudaError_t launch_attn_tc128(const AttnArgs& a, cudaStream_t st, const char** w
         if (e != cudaSuccess) return e;
         ds.sm_count.store(sm_count, std::memory_order_relaxed);
     }
-    auto kern = P.is_bf16 ? attn_tc128_kernel<true> : attn_tc128_kernel<false>;
-    const int bit = P.is_bf16 ? 4 : 8;
+    const bool ragged = a.gk.ragged;
+    auto kern = P.is_bf16 ? (ragged ? attn_tc128_kernel<true, true> : attn_tc128_kernel<true, false>)
+                          : (ragged ? attn_tc128_kernel<false, true> : attn_tc128_kernel<false, false>);
+    const int bit = 16 << ((P.is_bf16 ? 0 : 1) + (ragged ? 2 : 0));  // bits 4-7 of attr_set
     if (!(ds.attr_set.load(std::memory_order_relaxed) & bit)) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;

@@ -61,6 +61,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Branches that are rarely taken and whose code should not sit in the instruction stream of a hot loop.
+#define LCBSA_UNLIKELY(x) __builtin_expect(!!(x), 0)
+
 struct Ctl {
     volatile int* abort;    // shared flag
     unsigned int* status;   // global status words
@@ -91,8 +94,8 @@ __device__ __forceinline__ bool mbar_wait_timeout(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, const Ctl& c, unsigned code, unsigned it) {
     unsigned spins = 0;
     while (!mbar_try(bar, parity)) {
-        if (*c.abort) return false;
-        if (++spins >= kSpinsBeforeClock) return mbar_wait_timeout(bar, parity, c, code, it);
+        if (LCBSA_UNLIKELY(*c.abort)) return false;
+        if (LCBSA_UNLIKELY(++spins >= kSpinsBeforeClock)) return mbar_wait_timeout(bar, parity, c, code, it);
     }
     return true;
 }
@@ -189,6 +192,13 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         : "memory");
 }
 
+// max of three (one instruction on sm_100; NaN operands are ignored like fmaxf does)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -202,6 +212,21 @@ __device__ __forceinline__ uint32_t pack2(bool bf16, float lo, float hi) {
     }
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Rare path of the online softmax, as a rolled loop so that it takes little room in the instruction stream of the loop:
+// multiply this thread's row of a 128-column fp32 accumulator in TMEM by alpha.  Warp-collective.
+__device__ __forceinline__ void tc_scale_row128(uint32_t taddr, float alpha) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int cch = 0; cch < 4; ++cch) {
+        uint32_t orr[32];
+        tc_ld32(taddr + 32 * cch, orr);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
+        tc_st32(taddr + 32 * cch, orr);
+    }
 }
 
 // ------------------------------------------------------------------------------------------ descriptors
@@ -341,7 +366,7 @@ inline bool make_map(CUtensorMap* tm, int dtype, const View& v, int B, int H, co
 constexpr int kMaxDevices = 64;
 struct DeviceState {
     std::atomic<int> sm_count{0};
-    std::atomic<int> attr_set{0};  // bits 0, 1: bf16 and fp16 kernel for 64-token blocks; bits 2, 3: for 128-token blocks
+    std::atomic<int> attr_set{0};  // one bit per kernel instantiation: bits 0-3 64-token blocks (dtype, ragged), bits 4-7 128-token blocks
 };
 DeviceState* device_states();  // defined once, in attn_tc.cu
 int attn_sm_reserve();           // SMs the persistent attention kernels leave idle (lcbsa_set_attn_sm_reserve)
