@@ -295,6 +295,7 @@ def main():
     block_tokens = wl.chunk[0] * wl.chunk[1] * wl.chunk[2]
     roofline = {"bound": "tensor", "kernel": "attn_tc128_kernel" if block_tokens == 128 else "attn_tc_kernel",
                 "achieved": attn_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tf / peaks["bf16_tflops"],
+                "frac_of_sustained_peak": attn_tf / peaks["bf16_tflops_sustained"],
                 "peak_source": f"{peak_src} (burst cuBLAS bf16); sustained {peaks['bf16_tflops_sustained']}",
                 "ms_per_launch": ms_attn,
                 "traffic": NCU_ATTN_DRAM_PER_IO_BYTE * attn_io_bytes,
