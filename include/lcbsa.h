@@ -198,6 +198,24 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
                            void* const* out_dst, int n_dst, int64_t out_head_stride, int64_t out_token_stride, void* stream);
 
 /*
+ * Backward of lcbsa_attn_fwd for fixed block lists: dq, dk, dv from dout.  Replaces attn_bwd_bsa_varlen_triton and
+ * its Triton kernels (longcat_video/block_sparse_attention/bsa_interface.py:343-461,
+ * flash_attn_bsa_varlen_mask.py:289-945), i.e. the body of _attention_bsa.backward (bsa_interface.py:570-596).  No
+ * gradient flows through the selection.  q, k, v, out, dout and the gradients are [B,H,S,D] descriptors with any
+ * strides (T,H,W token order, D contiguous); idx, cnt, cap are the lists the forward ran with and lse is the
+ * [B*H, Sq] fp32 log-sum-exp (natural log) that the forward returned.  bf16 or fp16, head_dim 64 or 128, block sizes
+ * multiples of 64 tokens.  The workspace (lcbsa_attn_bwd_workspace_bytes, 256-byte aligned) holds delta =
+ * rowsum(dout * out) and, for every key block, the ascending list of the query blocks that selected it; four
+ * launches, no atomics on the gradients, so two calls give the same bits.  Every row of dq, dk, dv that exists is written
+ * (rows of blocks that nothing selected get zeros).
+ */
+size_t lcbsa_attn_bwd_workspace_bytes(const LcbsaTensor* q, const LcbsaGrid* gq, const LcbsaGrid* gk, int cap);
+int lcbsa_attn_bwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaTensor* out, const LcbsaTensor* dout,
+                   const LcbsaGrid* gq, const LcbsaGrid* gk, const int32_t* idx, const int32_t* cnt, int cap, float sm_scale,
+                   const float* lse, const LcbsaTensor* dq, const LcbsaTensor* dk, const LcbsaTensor* dv, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
  * lcbsa_block_select for callers that cannot allocate device memory for the workspace (a frozen
  * memory pool, a plugin that only receives its input and output buffers, code that must not touch the
  * CUDA allocator).  No counterpart in the reference: there the workspace is whatever PyTorch allocates.

@@ -72,6 +72,10 @@ SIGNATURES = {
     "lcbsa_attn_fwd_scatter": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid),
                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_int,
                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
+    "lcbsa_attn_bwd_workspace_bytes": (ctypes.c_size_t, [_P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_int]),
+    "lcbsa_attn_bwd": (ctypes.c_int, [_P(LcbsaTensor)] * 5 + [_P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                      ctypes.c_float, ctypes.c_void_p, _P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaTensor), ctypes.c_void_p,
+                                      ctypes.c_size_t, ctypes.c_void_p]),
     "lcbsa_static_scratch_bytes": (ctypes.c_size_t, []),
     "lcbsa_block_select_static": (ctypes.c_int, [_P(LcbsaTensor), _P(LcbsaTensor), _P(LcbsaGrid), _P(LcbsaGrid), ctypes.c_int,
                                                  ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),

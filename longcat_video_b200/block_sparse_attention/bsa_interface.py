@@ -201,6 +201,48 @@ def attn_fwd_bsa_varlen(q, k, v, sm_scale, block_indices, block_indices_lens, la
     return (out, lse) if return_lse else out
 
 
+def attn_bwd_bsa_varlen(do, q, k, v, o, lse, sm_scale, block_indices, block_indices_lens, latent_shape_q, latent_shape_k,
+                        chunk_3d_shape_q, chunk_3d_shape_k):
+    """dq, dk, dv of the block-sparse attention for fixed block lists (``attn_bwd_bsa_varlen_triton`` of the reference,
+    longcat_video/block_sparse_attention/bsa_interface.py:343-461).  ``o`` and ``lse`` are what the forward returned."""
+    q, k, v, o, do = _as_abi(q), _as_abi(k), _as_abi(v), _as_abi(o), _as_abi(do)
+    dq, dk, dv = torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty_like(k, memory_format=torch.contiguous_format), \
+        torch.empty_like(v, memory_format=torch.contiguous_format)
+    idx = block_indices.to(torch.int32).contiguous()
+    cnt = block_indices_lens.to(torch.int32).contiguous()
+    lse = lse.to(torch.float32).contiguous()
+    gq, gk = L.grid_desc(latent_shape_q, chunk_3d_shape_q), L.grid_desc(latent_shape_k, chunk_3d_shape_k)
+    d = {n: L.tensor_desc(t) for n, t in dict(q=q, k=k, v=v, o=o, do=do, dq=dq, dk=dk, dv=dv).items()}
+    with torch.cuda.device(q.device):
+        need = L.lib().lcbsa_attn_bwd_workspace_bytes(ctypes.byref(d["q"]), ctypes.byref(gq), ctypes.byref(gk), idx.shape[-1])
+        ws = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+        L.check(L.lib().lcbsa_attn_bwd(ctypes.byref(d["q"]), ctypes.byref(d["k"]), ctypes.byref(d["v"]), ctypes.byref(d["o"]),
+                                       ctypes.byref(d["do"]), ctypes.byref(gq), ctypes.byref(gk), idx.data_ptr(), cnt.data_ptr(),
+                                       idx.shape[-1], float(sm_scale), lse.data_ptr(), ctypes.byref(d["dq"]), ctypes.byref(d["dk"]),
+                                       ctypes.byref(d["dv"]), ws.data_ptr(), ws.numel(), L.current_stream(q.device)))
+    return dq, dk, dv
+
+
+class _AttentionBSA(torch.autograd.Function):
+    """The autograd contract of the reference's ``_attention_bsa`` (bsa_interface.py:535-596): the forward selects the
+    blocks and attends to them, the backward differentiates the attention with the lists held fixed."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, latent_shape_q, latent_shape_k, sparsity, cdf_threshold, chunk_q, chunk_k, sm_scale):
+        idx, cnt = get_select_indices(q, k, latent_shape_q, latent_shape_k, sparsity, cdf_threshold, chunk_q, chunk_k)
+        o, lse = attn_fwd_bsa_varlen(q, k, v, sm_scale, idx, cnt, latent_shape_q, latent_shape_k, chunk_q, chunk_k, return_lse=True)
+        ctx.save_for_backward(q, k, v, o, lse, idx, cnt)
+        ctx.geom = (tuple(latent_shape_q), tuple(latent_shape_k), tuple(chunk_q), tuple(chunk_k), float(sm_scale))
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, idx, cnt = ctx.saved_tensors
+        sq, sk, cq, ck, sm_scale = ctx.geom
+        dq, dk, dv = attn_bwd_bsa_varlen(do, q, k, v, o, lse, sm_scale, idx, cnt, sq, sk, cq, ck)
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
 @torch.compiler.disable
 def flash_attn_bsa_3d(
     q: torch.Tensor,  # [B, H, Sq, D]
@@ -244,6 +286,9 @@ def flash_attn_bsa_3d(
     if not q.is_cuda:
         raise RuntimeError("flash_attn_bsa_3d (B200) needs CUDA tensors; there is no CPU path")
 
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _AttentionBSA.apply(q, k, v, latent_shape_q, latent_shape_k, sparsity, cdf_threshold, chunk_3d_shape_q,
+                                   chunk_3d_shape_k, 1 / head_dim ** 0.5)
     idx, cnt = get_select_indices(q, k, latent_shape_q, latent_shape_k, sparsity, cdf_threshold,
                                   chunk_3d_shape_q, chunk_3d_shape_k)
     if STAGE_HOOK is not None:

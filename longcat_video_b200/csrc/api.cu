@@ -382,6 +382,57 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
     return LCBSA_OK;
 }
 
+size_t lcbsa_attn_bwd_workspace_bytes(const LcbsaTensor* q, const LcbsaGrid* gq, const LcbsaGrid* gk, int cap) {
+    if (!q || !grid_ok(gq) || !grid_ok(gk) || cap < 1) return 0;
+    for (int i = 0; i < 4; ++i)
+        if (q->size[i] < 0) return 0;
+    const lcbsa::Geom a = lcbsa::make_geom(*gq), b = lcbsa::make_geom(*gk);
+    return lcbsa::attn_bwd_workspace_bytes((long long)q->size[0] * q->size[1], (long long)a.T * a.H * a.W, a.nblk, b.nblk, cap);
+}
+
+int lcbsa_attn_bwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaTensor* out, const LcbsaTensor* dout,
+                   const LcbsaGrid* gq, const LcbsaGrid* gk, const int32_t* idx, const int32_t* cnt, int cap, float sm_scale,
+                   const float* lse, const LcbsaTensor* dq, const LcbsaTensor* dk, const LcbsaTensor* dv, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+    if (!grid_ok(gq) || !grid_ok(gk)) return fail(LCBSA_EINVAL, "attn_bwd: bad grid");
+    if (int rc = check_tensor("q", q, gq)) return rc;
+    if (int rc = check_tensor("k", k, gk)) return rc;
+    if (int rc = check_tensor("v", v, gk)) return rc;
+    if (int rc = check_tensor("out", out, gq)) return rc;
+    if (int rc = check_tensor("dout", dout, gq)) return rc;
+    if (int rc = check_tensor("dq", dq, gq)) return rc;
+    if (int rc = check_tensor("dk", dk, gk)) return rc;
+    if (int rc = check_tensor("dv", dv, gk)) return rc;
+    if (!idx || !cnt || !lse || cap < 1) return fail(LCBSA_EINVAL, "attn_bwd: null block lists or lse, or zero capacity");
+    const LcbsaTensor* all[8] = {q, k, v, out, dout, dq, dk, dv};
+    for (const LcbsaTensor* t : all) {
+        if (t->dtype != q->dtype) return fail(LCBSA_EINVAL, "attn_bwd: dtypes differ");
+        for (int i : {0, 1, 3})
+            if (t->size[i] != q->size[i]) return fail(LCBSA_EINVAL, "attn_bwd: tensors disagree on batch, heads or head_dim");
+    }
+    if (q->dtype == LCBSA_FP32) return fail(LCBSA_EUNSUPPORTED, "attn_bwd: takes bf16 or fp16");
+    if (!std::isfinite(sm_scale)) return fail(LCBSA_EINVAL, "attn_bwd: sm_scale is not finite");
+    if (q->size[0] * q->size[1] > 65535) return fail(LCBSA_EUNSUPPORTED, "attn_bwd: batch*heads above 65535");
+    lcbsa::BwdArgs a{};
+    a.dtype = q->dtype;
+    a.D = (int)q->size[3];
+    a.q = view_of(q); a.k = view_of(k); a.v = view_of(v); a.o = view_of(out); a.dout = view_of(dout);
+    a.dq = view_of(dq); a.dk = view_of(dk); a.dv = view_of(dv);
+    a.B = (int)q->size[0]; a.H = (int)q->size[1];
+    a.gq = lcbsa::make_geom(*gq); a.gk = lcbsa::make_geom(*gk);
+    a.idx = idx; a.cnt = cnt; a.cap = cap; a.sm_scale = sm_scale; a.lse = lse;
+    const char* why = "";
+    if (!lcbsa::attn_bwd_supported(a, &why)) return fail(LCBSA_EUNSUPPORTED, "attn_bwd: %s", why);
+    const size_t need = lcbsa_attn_bwd_workspace_bytes(q, gq, gk, cap);
+    if (!workspace || workspace_bytes < need) return fail(LCBSA_EWORKSPACE, "attn_bwd: workspace of %zu bytes, need %zu", workspace_bytes, need);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(LCBSA_EINVAL, "attn_bwd: workspace not 256-byte aligned");
+    a.status = device_status_ptr();
+    if (!a.status) return fail(LCBSA_ECUDA, "attn_bwd: cannot resolve the device status words");
+    cudaError_t e = lcbsa::launch_attn_bwd(a, workspace, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) return cuda_fail(e, "attn_bwd", why);
+    return LCBSA_OK;
+}
+
 int lcbsa_set_attn_sm_reserve(int n_sms) {
     if (n_sms < 0 || n_sms > 64) return fail(LCBSA_EINVAL, "sm reserve %d outside 0..64", n_sms);
     return lcbsa::set_attn_sm_reserve(n_sms);

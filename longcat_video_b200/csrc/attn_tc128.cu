@@ -5,12 +5,13 @@
 // (flash_attn_bsa_varlen_mask.py:172-285, launcher bsa_interface.py:290-341).  Same contract as attn_tc.cu (the
 // 64-token kernel): q, k, v are read and the output is written straight from / to T,H,W order by 5-D TMA boxes.
 //
-// Shape handled: head_dim 128, query and key blocks of 128 tokens, bf16 or fp16.
+// Shape handled: head_dim 128, query blocks of 128 tokens, key blocks of 128, 256 or 512 tokens (for which the
+// reference switches to _attn_fwd_bsa_varlen, flash_attn_bsa_varlen_mask.py:37-153, bsa_interface.py:309-315), bf16 or fp16.
 //
 // One persistent CTA per SM.  A work item is ONE query block of one head: a 128-row tile, i.e. M=128 tcgen05 MMAs
 // that run the tensor pipe at its full rate (the 64-row tiles of the other kernel occupy it like 128-row ones).  A
-// selected key block is processed as two units of 64 keys (the first and the second 64 of its tokens in t,h,w
-// order), which keeps the S tile at 64 TMEM columns, so that every warpgroup has two S/P buffers beside its O
+// selected key block is processed as 2, 4 or 8 units of 64 keys (sub-boxes of the block, cut along its outermost even
+// axes), which keeps the S tile at 64 TMEM columns, so that every warpgroup has two S/P buffers beside its O
 // accumulator, exactly as in the 64-token kernel:
 //
 //   warps 0-3, 4-7 : softmax warpgroups 0 and 1 (units of even / odd number; thread = one query row)
@@ -41,6 +42,7 @@ constexpr int kQHalfBytes = kQTileBytes / 2;       // one 64-column half of it: 
 constexpr int kTileBytes = kBlk * kD * 2;          // 16 KiB: one K or V tile of 64 keys
 constexpr int kHalfBytes = kTileBytes / 2;         // one 64-column half: 64 rows x 128 B
 constexpr int kSlotBytes = kTileBytes;             // a ring slot holds one unit's tile
+constexpr int kMaxUnits = 8;                       // units of 64 keys per key block: blocks of up to 512 tokens
 constexpr int kKSlots = 6, kVSlots = 6;            // even: the two units of a key block sit in a slot pair
 constexpr int kKLead = 4;                   // K blocks requested ahead of V: S runs two rounds of each warpgroup ahead
 constexpr int kThreads = 384;
@@ -82,7 +84,10 @@ struct TcParams {
     Geom gq, gk;
     float scale2;   // sm_scale * log2(e)
     int is_bf16;
-    int sub_axis, sub_len;  // the second unit of a key block starts sub_len tokens further along axis 0 = t, 1 = h, 2 = w
+    // A key block of 128, 256 or 512 tokens is cut into 2, 4 or 8 units of 64 keys: unit u of a block starts
+    // (sub_t[u], sub_h[u], sub_w[u]) tokens into it.  lg_units = log2 of the units per block.
+    int lg_units;
+    int sub_t[kMaxUnits], sub_h[kMaxUnits], sub_w[kMaxUnits];
     Geom gu;                // the key geometry with that axis of the block halved: slot order inside a unit
 };
 
@@ -177,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
             const int bh = (int)(w / groups), qb = (int)(w % groups);
             const int b = bh / P.heads, h = bh % P.heads;
             const int cnt = clamp_cnt(P, bh, qb);
-            const int n_act = 2 * cnt;            // units that exist: two per listed key block
+            const int n_act = cnt << P.lg_units;  // units that exist: 2, 4 or 8 per listed key block
             const int n_iter = max(2, n_act);     // an empty list still goes through one (masked) pair of units
             // Q tile: the buffer is free once the last S of the previous item has been computed
             ok = mbar_wait_warp(bar_q_empty, (wk & 1) ^ 1, ctl, 10, wk);
@@ -214,20 +219,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
             int cur = fetch(lane);
             const int c3k = P.merge_k ? b * P.Tk : 0, c4k = P.merge_k ? h : b * P.heads + h;
             const int c3v = P.merge_v ? b * P.Tk : 0, c4v = P.merge_v ? h : b * P.heads + h;
-            // coordinates of unit u: those of its block, the second unit shifted along the split axis
+            // coordinates of unit u: those of its block plus the offset of the unit inside the block
             auto unit_coords = [&](int pk, int u, int& cw, int& chh, int& ctt) {
                 cw = pk & 1023;
                 chh = (pk >> 10) & 1023;
                 ctt = pk >> 20;
-                if (u & 1) {
-                    if (P.sub_axis == 0) ctt += P.sub_len;
-                    else if (P.sub_axis == 1) chh += P.sub_len;
-                    else cw += P.sub_len;
-                }
+                const int sub = u & ((1 << P.lg_units) - 1);
+                ctt += P.sub_t[sub];
+                chh += P.sub_h[sub];
+                cw += P.sub_w[sub];
             };
             for (int j = 0; j < n_iter + kKLead && ok; ++j) {
                 if (j >= kKLead) {  // V(j - kKLead)
-                    const int jj = j - kKLead, e = jj >> 1;
+                    const int jj = j - kKLead, e = jj >> P.lg_units;
                     const int pk = __shfl_sync(0xffffffffu, e >= win ? cur : prv, e >= win ? e - win : e - (win - 32));
                     const bool act = jj < n_act;
                     const int slot = gv % kVSlots;
@@ -246,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                     }
                 }
                 if (j < n_iter) {  // K(j)
-                    const int e = j >> 1;
+                    const int e = j >> P.lg_units;
                     while (e >= win + 32) {
                         win += 32;
                         prv = cur;
@@ -292,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), qb = (int)(w % groups);
-            const int n_act = 2 * clamp_cnt(P, bh, qb);
+            const int n_act = clamp_cnt(P, bh, qb) << P.lg_units;
             const int n_iter = max(2, n_act);
             ok = mbar_wait_warp(bar_q_full, wk & 1, ctl, 30, wk);
             bool pre = false;
@@ -341,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
         bool ok = true;
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), qb = (int)(w % groups);
-            const int n_act = 2 * clamp_cnt(P, bh, qb);
+            const int n_act = clamp_cnt(P, bh, qb) << P.lg_units;
             const int n_iter = max(2, n_act);
             // the epilogue of the previous item has read both O accumulators
             ok = mbar_wait_warp(bar_o_free, (wk & 1) ^ 1, ctl, 36, wk);
@@ -389,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), qb = (int)(w % groups);
             const int b = bh / P.heads, h = bh % P.heads;
-            gb += max(2, 2 * clamp_cnt(P, bh, qb));
+            gb += max(2, clamp_cnt(P, bh, qb) << P.lg_units);
             const int s0 = (int)((gb - 2) % kVSlots);  // gb is even and so is the ring: slots s0 and s0 + 1
             ok = mbar_wait_warp(bar_o_staged, wk & 1, ctl, 110, wk);
             if (ok && lane == 0) {
@@ -427,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
 
         for (long long w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++wk) {
             const int bh = (int)(w / groups), qt = (int)(w % groups);
-            const int n_act = 2 * clamp_cnt(P, bh, qt);
+            const int n_act = clamp_cnt(P, bh, qt) << P.lg_units;
             const int n_iter = max(2, n_act);
             const int32_t* my_list = P.idx + ((long long)bh * P.nq + qt) * P.cap;
 
@@ -435,12 +439,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
             bool first = true;  // no block of this item seen yet by this warpgroup
 
             // ragged grids: the block index of a round is fetched a round ahead, so that the global load never sits
-            // between S and the softmax (unit i belongs to list entry i >> 1)
+            // between S and the softmax (unit i belongs to list entry i >> lg_units)
             int blk_ahead = (kRagged && wg < n_act) ? my_list[0] : 0;
             for (int i = wg; i < n_iter && ok; i += 2, ++rr) {
                 const bool active = i < n_act;
                 const int blk_now = blk_ahead;
-                if (kRagged && i + 2 < n_act) blk_ahead = my_list[(i + 2) >> 1];
+                if (kRagged && i + 2 < n_act) blk_ahead = my_list[(i + 2) >> P.lg_units];
                 const int buf = rr & 1;
                 const unsigned bph = (rr >> 1) & 1;
                 ok = mbar_wait_warp(bar_s_full(wg, buf), bph, ctl, 80 + wg, rr);
@@ -459,11 +463,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
                         block_coords(P.gk, blk, bt, bhh, bw);
                         // tokens left along each axis from the first token of this unit
                         int vt = P.gk.T - bt * P.gk.ct, vh = P.gk.H - bhh * P.gk.ch, vw = P.gk.W - bw * P.gk.cw;
-                        if (i & 1) {
-                            if (P.sub_axis == 0) vt -= P.sub_len;
-                            else if (P.sub_axis == 1) vh -= P.sub_len;
-                            else vw -= P.sub_len;
-                        }
+                        const int sub = i & ((1 << P.lg_units) - 1);
+                        vt -= P.sub_t[sub];
+                        vh -= P.sub_h[sub];
+                        vw -= P.sub_w[sub];
                         if (vt < P.gu.ct || vh < P.gu.ch || vw < P.gu.cw) {
                             const uint64_t present = slot_mask64(P.gu.ct, P.gu.ch, P.gu.cw, vt, vh, vw);
                             const uint32_t p_lo = (uint32_t)present, p_hi = (uint32_t)(present >> 32);
@@ -669,19 +672,30 @@ __global__ void __launch_bounds__(kThreads, 1) attn_tc128_kernel(const __grid_co
 
 }  // namespace
 
-// The axis along which a 128-token key block is cut into two units of 64 keys: the outermost even one, so that the
-// units are as close to contiguous runs of the block's slot order as the shape allows.  -1: no even axis.
-static int split_axis(const Geom& g) {
-    if (g.ct % 2 == 0) return 0;
-    if (g.ch % 2 == 0) return 1;
-    if (g.cw % 2 == 0) return 2;
-    return -1;
+// Cuts a key block of 64 * 2^k tokens into units of 64 keys: the outermost even axis is halved until 64 tokens are
+// left, so that a unit is one TMA box and the units are as close to contiguous runs of the block's slot order as the
+// shape allows.  (ut, uh, uw): the unit's extents; units are numbered t-major, then h, then w.
+struct UnitSplit {
+    int ut, uh, uw, lg_units;
+};
+static UnitSplit split_into_units(const Geom& g) {
+    UnitSplit u{g.ct, g.ch, g.cw, 0};
+    while (u.ut * u.uh * u.uw > kBlk) {
+        if (u.ut % 2 == 0) u.ut /= 2;
+        else if (u.uh % 2 == 0) u.uh /= 2;
+        else u.uw /= 2;  // the token count is a power of two, so some axis is even
+        ++u.lg_units;
+    }
+    return u;
 }
 
 bool attn_tc128_supported(const AttnArgs& a, const char** why) {
     if (a.dtype != LCBSA_BF16 && a.dtype != LCBSA_FP16) { *why = "needs bf16 or fp16"; return false; }
     if (a.D != kD) { *why = "needs head_dim 128"; return false; }
-    if (a.gq.bs != kQRows || a.gk.bs != 2 * kBlk) { *why = "needs 128-token query and key blocks"; return false; }
+    if (a.gq.bs != kQRows || (a.gk.bs != 128 && a.gk.bs != 256 && a.gk.bs != 512)) {
+        *why = "needs 128-token query blocks and key blocks of 128, 256 or 512 tokens";
+        return false;
+    }
     if (a.gq.ct > 256 || a.gq.ch > 256 || a.gq.cw > 256 || a.gk.ct > 256 || a.gk.ch > 256 || a.gk.cw > 256) {
         *why = "block axis above the TMA box limit";
         return false;
@@ -710,13 +724,21 @@ bool attn_tc128_supported(const AttnArgs& a, const char** why) {
 cudaError_t launch_attn_tc128(const AttnArgs& a, cudaStream_t st, const char** why) {
     if (a.gq.nblk == 0 || a.B * a.H == 0) return cudaSuccess;
     TcParams P;
-    // geometry of one unit: the key block with its split axis halved (128 tokens always have an even axis)
+    // geometry of one unit of 64 keys, and where every unit starts inside its block
+    const UnitSplit us = split_into_units(a.gk);
     Geom gu = a.gk;
-    P.sub_axis = split_axis(a.gk);
-    if (P.sub_axis == 0) P.sub_len = (gu.ct /= 2);
-    else if (P.sub_axis == 1) P.sub_len = (gu.ch /= 2);
-    else P.sub_len = (gu.cw /= 2);
+    gu.ct = us.ut; gu.ch = us.uh; gu.cw = us.uw;
     gu.bs = kBlk;
+    P.lg_units = us.lg_units;
+    {
+        const int ph = a.gk.ch / us.uh, pw = a.gk.cw / us.uw;
+        for (int u = 0; u < (1 << us.lg_units); ++u) {
+            P.sub_w[u] = (u % pw) * us.uw;
+            P.sub_h[u] = ((u / pw) % ph) * us.uh;
+            P.sub_t[u] = (u / (pw * ph)) * us.ut;
+        }
+        for (int u = 1 << us.lg_units; u < kMaxUnits; ++u) P.sub_t[u] = P.sub_h[u] = P.sub_w[u] = 0;
+    }
     P.gu = gu;
     const int mq = merge_mode(a.q, a.B, a.H, a.gq), mk = merge_mode(a.k, a.B, a.H, a.gk);
     const int mv = merge_mode(a.v, a.B, a.H, a.gk), mo = merge_mode(a.o, a.B, a.H, a.gq);

@@ -129,6 +129,28 @@ struct AttnArgs {
 cudaError_t launch_attn_mma(const AttnArgs& a, cudaStream_t st, const char** why);
 cudaError_t launch_attn_tc(const AttnArgs& a, cudaStream_t st, const char** why);
 bool attn_tc_supported(const AttnArgs& a, const char** why);
+// Backward (attn_bwd.cu): dq, dk, dv for fixed block lists.
+struct BwdArgs {
+    int dtype, D;
+    View q, k, v, o, dout, dq, dk, dv;
+    int B, H;
+    Geom gq, gk;
+    const int32_t* idx;   // [B*H, Nq, cap]
+    const int32_t* cnt;   // [B*H, Nq]
+    int cap;
+    float sm_scale;
+    const float* lse;     // [B*H, Sq] natural log, from the forward
+    unsigned int* status;
+    // carved out of the workspace by launch_attn_bwd:
+    float* delta;         // [B*H, Sq]
+    int32_t* tcnt;        // [B*H, Nk]       query blocks per key block
+    int32_t* toff;        // [B*H, Nk + 1]   exclusive prefix of tcnt
+    int32_t* tidx;        // [B*H, Nq * cap] query blocks of key block j at toff[j] .. toff[j + 1], ascending
+};
+bool attn_bwd_supported(const BwdArgs& a, const char** why);
+size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap);
+cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why);
+
 // the same for 128-token query and key blocks (attn_tc128.cu)
 cudaError_t launch_attn_tc128(const AttnArgs& a, cudaStream_t st, const char** why);
 bool attn_tc128_supported(const AttnArgs& a, const char** why);

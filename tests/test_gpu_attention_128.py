@@ -175,3 +175,32 @@ def test_head_dim_64_still_takes_the_generic_kernel():
         B.attn_fwd_bsa_varlen(q.cuda(), k.cuda(), v.cuda(), wl.head_dim ** -0.5, idx.cuda(), cnt.cuda(), wl.grid_q, wl.grid_k,
                               wl.chunk, wl.chunk, impl=L.ATTN_TC)
     _check(wl, idx, cnt, q, k, v, impl=L.ATTN_AUTO)
+
+
+@pytest.mark.parametrize("chunk_k,grid,dtype", [((4, 8, 8), (8, 16, 32), torch.bfloat16), ((8, 8, 8), (8, 16, 32), torch.bfloat16),
+                                                ((4, 4, 16), (8, 8, 64), torch.float16), ((4, 8, 8), (10, 20, 29), torch.bfloat16)])
+def test_key_blocks_larger_than_query_blocks(chunk_k, grid, dtype):
+    """Query blocks of 128 tokens against key blocks of 256 and 512 tokens (the shapes for which the reference switches
+    to its multi-tile kernel): 4 and 8 units of 64 keys per selected block.  The last case is ragged on every axis."""
+    chunk_q = (4, 4, 8)
+    wl = Workload("b128_bigk", 5800 + sum(chunk_k), 1, 2, 128, grid, grid, chunk_q, 0.5, dtype, "normal")
+    q, k, v = make_qkv(wl)
+    ragged = any(g % c for g, c in zip(grid, chunk_k))
+    idx, cnt, _, _ = O.block_select(q, k, grid, grid, 0.5, chunk_q, chunk_k)
+    ref, ref_lse = O.attention(q, k, v, grid, grid, chunk_q, chunk_k, idx, cnt)
+    L.lib().lcbsa_check_device_status()
+    out, lse = B.attn_fwd_bsa_varlen(q.cuda(), k.cuda(), v.cuda(), wl.head_dim ** -0.5, idx.cuda(), cnt.cuda(), grid, grid,
+                                     chunk_q, chunk_k, return_lse=True, impl=L.ATTN_TC)
+    torch.cuda.synchronize()
+    L.check(L.lib().lcbsa_check_device_status())
+    got = out.float().cpu()
+    r, m = rel_l2(got, ref), max_abs(got, ref)
+    assert r <= REL_L2_TOL and m <= MAX_ABS_TOL, (r, m)
+    assert float((lse.cpu() - ref_lse).abs().max()) <= LSE_TOL
+    whole = B.flash_attn_bsa_3d(q.cuda(), k.cuda(), v.cuda(), grid, grid, sparsity=0.5, chunk_3d_shape_q=list(chunk_q),
+                                chunk_3d_shape_k=list(chunk_k), allow_ragged=ragged)
+    assert torch.equal(whole, out)
+    gi, gc = B.get_select_indices(q.cuda(), k.cuda(), grid, grid, 0.5, None, chunk_q, chunk_k)
+    nsel = int(cnt.flatten()[0])
+    assert torch.equal(gc.cpu(), cnt) and torch.equal(gi.cpu()[..., :nsel], idx[..., :nsel])
+    print(f"PARITY b128 key blocks {chunk_k} {dtype}: {nsel} of {O.num_blocks(grid, chunk_k)} blocks, rel-L2 {r:.3e} max-abs {m:.3e}")
