@@ -14,7 +14,8 @@ One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 p
   roofline   the attention kernel against the measured bf16 tensor peak (events around that launch, inside the
              timed region); roofline_select does the same for the block-select stage against the measured HBM rate.
   literal_720p   a short leg on BASELINE's literal 24x45x80 grid (ragged: through ``allow_ragged=True``).
-  default_blocks_720p  a short leg with the entry point's default [4, 4, 8] blocks (128 tokens) on the same tensors.
+  default_blocks_720p  two short legs on the same tensors with the entry point's default [4, 4, 8] blocks (128 tokens):
+             at the headline's sparsity and with every parameter left at its default (sparsity 0.875).
   gpu_reference  the reference's own Triton BSA (baseline/_ref, see baseline/install_reference.py) timed on the
              same GPU and inputs, outside the timed region of this library; absent checkout -> "unavailable".
   cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
@@ -324,29 +325,34 @@ def main():
                    "note": "extension: ragged grid through allow_ragged=True, flops counted on present rows and keys only"}
         del lq, lk, lv, lt, li, lc
 
-    # ------------------------------------------------------------------ the entry point's default block shape, short leg
+    # ------------------------------------------------------------------ the entry point's default parameters, short legs
     blocks128 = None
     if wl.name == "720p_legal" and not args.skip_blocks128:
-        bw = WORKLOADS["720p_blocks128"]  # same grid and seed, [4, 4, 8] blocks of 128 tokens
-        bparams = dict(params, chunk_3d_shape_q=list(bw.chunk), chunk_3d_shape_k=list(bw.chunk))
-        bt = StepTimer(B, q, k, v, bw, dict(bparams, allow_ragged=False))
-        for _ in range(3):
-            bt.call()
-        bi, bc = B.get_select_indices(q, k, bw.grid_q, bw.grid_k, bw.sparsity, None, bw.chunk, bw.chunk)
-        bflops = algorithmic_flops(bw, heads, int(bc.flatten()[0]))
-        bms, bms_sel, bms_att = bt.run(5)
-        L.check(L.lib().lcbsa_check_device_status())
-        blocks128 = {"workload": bw.name, "block": list(bw.chunk), "selected_blocks": int(bc.flatten()[0]), "steps": 5,
-                     "ms_per_step": bms, "ms_select": bms_sel, "ms_attention": bms_att, "algorithmic_tflop": bflops / 1e12,
-                     "value": bflops / bms / 1e9, "attention_tflops": bflops / bms_att / 1e9,
-                     "attention_frac_of_peak": bflops / bms_att / 1e9 / peaks["bf16_tflops"], "kernel": "attn_tc128_kernel",
-                     "note": "the chunk shape flash_attn_bsa_3d takes when none is passed; the headline stays on BASELINE's 4x4x4 blocks"}
-        if not args.skip_gpu_reference:  # the reference's Triton kernel with BLOCK_M = BLOCK_N = 128 on the same tensors
-            bref = gpu_reference_leg(bw, q, k, v, bparams, bflops, steps=3, warmup=2)
-            blocks128["gpu_reference"] = bref
-            if "ms_per_step" in bref:
-                blocks128["speedup_of_this_library"] = bref["ms_per_step"] / bms
-        del bt, bi, bc
+        blocks128 = {}
+        # "same_sparsity": only the block shape changes ([4, 4, 8], 45 of 720 blocks: the same keys per query as the
+        # headline); "all_defaults": flash_attn_bsa_3d(q, k, v, shape, shape) with nothing else passed (sparsity 0.875)
+        for key, wname in (("same_sparsity", "720p_blocks128"), ("all_defaults", "720p_defaults")):
+            bw = WORKLOADS[wname]
+            bparams = dict(sparsity=bw.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(bw.chunk), chunk_3d_shape_k=list(bw.chunk))
+            bt = StepTimer(B, q, k, v, bw, dict(bparams, allow_ragged=False))
+            for _ in range(3):
+                bt.call()
+            bi, bc = B.get_select_indices(q, k, bw.grid_q, bw.grid_k, bw.sparsity, None, bw.chunk, bw.chunk)
+            bflops = algorithmic_flops(bw, heads, int(bc.flatten()[0]))
+            bms, bms_sel, bms_att = bt.run(5)
+            L.check(L.lib().lcbsa_check_device_status())
+            leg = {"workload": bw.name, "block": list(bw.chunk), "sparsity": bw.sparsity, "selected_blocks": int(bc.flatten()[0]), "steps": 5,
+                   "ms_per_step": bms, "ms_select": bms_sel, "ms_attention": bms_att, "algorithmic_tflop": bflops / 1e12,
+                   "value": bflops / bms / 1e9, "attention_tflops": bflops / bms_att / 1e9,
+                   "attention_frac_of_peak": bflops / bms_att / 1e9 / peaks["bf16_tflops"], "kernel": "attn_tc128_kernel"}
+            if not args.skip_gpu_reference:  # the reference's Triton kernel with BLOCK_M = BLOCK_N = 128 on the same tensors
+                bref = gpu_reference_leg(bw, q, k, v, bparams, bflops, steps=3, warmup=2)
+                leg["gpu_reference"] = bref
+                if "ms_per_step" in bref:
+                    leg["speedup_of_this_library"] = bref["ms_per_step"] / bms
+            blocks128[key] = leg
+            del bt, bi, bc
+        blocks128["note"] = "the headline stays on BASELINE's 4x4x4 blocks; these legs run the same tensors with the entry point's default block shape"
 
     # ------------------------------------------------------------------ the reference's Triton kernels on this GPU
     gpu_reference = None

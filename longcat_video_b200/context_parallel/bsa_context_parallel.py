@@ -61,15 +61,19 @@ def phase_report(skip: int = 0) -> str:
     return ", ".join(f"{n} {m:.3f}" for n, m in zip(names, means)) + f", total {total:.3f}, period {period:.3f} ms over {len(calls)} calls"
 
 
-def _stages_scattered(hn: int):
+def _stages_scattered(hn: int, n: int = 2):
     """Head ranges of the attention stages when the result leaves through the kernel's own stores: only the FIRST stage
     has to be small (its q, k, v slabs are the ones nothing can hide); every further launch costs a pipeline fill and a
-    tail, and a head's slabs arrive two to three times faster than its attention runs, so the rest goes in at most two
-    large stages."""
+    tail.  On two or four GPUs a head's slabs arrive two to three times faster than its attention runs, so the rest goes
+    in at most two large stages.  On eight the slabs are eight times smaller (3 MB copies reach about half the link rate)
+    and a head's slabs take three quarters of its attention time: a stage of three heads then waits half a millisecond
+    for its slabs, so the heads go one by one."""
     if "LCBSA_ULYSSES_GROUP_HEADS" in os.environ:
         return U._stages(hn, U._heads_per_group(hn))
     if hn <= 1:
         sizes = [hn]
+    elif n >= 8:
+        sizes = [1] * min(hn, 4) + [2] * ((hn - 4) // 2 if hn > 4 else 0) + ([1] if hn > 4 and (hn - 4) % 2 else [])
     elif hn <= 4:
         sizes = [1, hn - 1]
     elif hn <= 8:
@@ -149,7 +153,7 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
         for t in (q, k, v):
             t.record_stream(side)
     scatter = _SCATTER_OUT and D == 128 and chunk[0] * chunk[1] * chunk[2] in (64, 128)  # what the tcgen05 kernels take
-    stages = _stages_scattered(hn) if scatter else U._stages(hn, U._heads_per_group(hn))
+    stages = _stages_scattered(hn, n) if scatter else U._stages(hn, U._heads_per_group(hn))
     phases = _PhaseTimer(main) if _PHASES else None
 
     # 1. pooled rows of this rank's tokens, all heads, stored straight into their owners' memory; one barrier
@@ -157,12 +161,12 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
     if phases:
         phases.mark("pool_scatter+barrier")
 
-    # 2. the first stage's q, k, v slabs go onto the copy engines (side stream, one barrier per stage).  The receive
-    #    regions of the stages are disjoint and nothing but the inputs is needed to fill them, so every push could be
-    #    queued here; but queueing a push costs the host tens of copies, and the main stream would sit idle behind
-    #    them.  So the host queues stage g + 1 right after it has launched the attention of stage g: the slabs still
-    #    travel a whole stage ahead of their use, and the kernels are never waiting for the host.
-    evs = [ex.push_in((q, k, v), *stages[0])]
+    # 2. the q, k, v slabs of the first two stages go onto the copy engines (side stream, one barrier per stage).  The
+    #    receive regions of the stages are disjoint and nothing but the inputs is needed to fill them, so every push
+    #    could be queued here; but queueing a push costs the host tens of copies, and the main stream would sit idle
+    #    behind them.  So the host queues stage g + 2 right after it has launched the attention of stage g: the slabs
+    #    travel two stages ahead of their use, and the kernels are never waiting for the host.
+    evs = [ex.push_in((q, k, v), *st) for st in stages[:2]]
 
     # 3. block lists of all local heads while the first slabs travel
     qc, kc = ex.pooled_received(nblk_l)  # [1, hn, N * nblk_l, D]: rank-major block order = block order of the grid
@@ -191,8 +195,8 @@ def flash_attn_bsa_3d_ulysses(q, k, v, latent_shape, sparsity=0.875, cdf_thresho
             ev_out = ex.push_out(o, lo)
         if phases:
             phases.mark(f"attention_{g}")
-        if g + 1 < len(stages):
-            evs.append(ex.push_in((q, k, v), *stages[g + 1]))
+        if g + 2 < len(stages):
+            evs.append(ex.push_in((q, k, v), *stages[g + 2]))
     if scatter:
         ex.finish_scatter()
     else:

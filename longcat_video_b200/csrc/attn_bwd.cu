@@ -217,41 +217,49 @@ __device__ __forceinline__ void warp_abt_16x64(float* out, const T* a_rows, cons
 
 // ------------------------------------------------------------------------------------------ shared-memory plan
 
+// About 106 KB for head_dim 128, so that two CTAs share an SM.  P and dS (input dtype) are written over the rows of S and
+// dP (fp32) they were computed from, and the fp32 staging of a finished [64][D] result lies over the two operand tiles
+// that are dead by then.
 template <typename T, int D>
 struct BwdSmem {
     static constexpr int LD = D + 8;        // operand tiles, in elements (row stride 16 bytes off a bank period)
     static constexpr int LDF = kTile + 4;   // fp32 S / dP tiles
-    static constexpr int LDP = kTile + 8;   // P / dS tiles in T
-    static constexpr int LDO = D + 4;       // fp32 staging of a [64][D] result (over the S and dP tiles and beyond)
+    static constexpr int LDP = 2 * LDF;     // the same rows seen as T: P / dS in place
+    static constexpr int LDO = D + 4;       // fp32 staging of a [64][D] result
     static constexpr size_t tile_bytes = (size_t)kTile * LD * sizeof(T);
     static constexpr size_t f_bytes = (size_t)kTile * LDF * sizeof(float);
-    static constexpr size_t p_bytes = (size_t)kTile * LDP * sizeof(T);
     static constexpr size_t stage_bytes = (size_t)kTile * LDO * sizeof(float);
-    // a, b, c, d: four operand tiles; sf, dpf: fp32; ps, dss: T; scalars: lse, delta (fp32 x 64 each), flags (2 x 64 bytes)
+    static_assert(stage_bytes <= 2 * tile_bytes, "the staging tile lies over operand tiles c and d");
+    // a, b, c, d: four operand tiles; sf, dpf: fp32 (then P, dS); scalars: lse, delta (fp32 x 64 each), flags (2 x 64 bytes)
     static constexpr size_t off_a = 0, off_b = tile_bytes, off_c = 2 * tile_bytes, off_d = 3 * tile_bytes;
     static constexpr size_t off_sf = 4 * tile_bytes;
     static constexpr size_t off_dpf = off_sf + f_bytes;
-    static constexpr size_t off_ps = off_dpf + f_bytes;
-    static constexpr size_t off_dss = off_ps + p_bytes;
-    static constexpr size_t off_sc = off_dss + p_bytes;
-    static constexpr size_t off_stage = off_sc + 2 * kTile * sizeof(float) + 2 * kTile;
-    static constexpr size_t bytes_no_tab = off_stage + stage_bytes;
+    static constexpr size_t off_sc = off_dpf + f_bytes;
+    static constexpr size_t off_stage = off_c;
+    static constexpr size_t bytes_no_tab = off_sc + 2 * kTile * sizeof(float) + 2 * kTile;
 };
 
-// P and dS of the 16 query rows of one warp from its S and dP rows (fp32) -> T.  Columns are keys.
+// P and dS of the 16 query rows of one warp from its S and dP rows (fp32) -> T, written over the same rows: a step of
+// the loop reads 32 consecutive fp32 values of a row (128 bytes) and then writes 32 values of T into the first 64 bytes
+// of the span it has just read (the second step of a row writes bytes 64 .. 127, which the first step has read).
 template <typename T, int LDF, int LDP>
-__device__ __forceinline__ void warp_softmax_grad_rows(const float* sf, const float* dpf, T* ps, T* dss, const float* lse, const float* delta,
-                                                       const unsigned char* q_ok, const unsigned char* k_ok, float sm_scale, int row0, int lane) {
+__device__ __forceinline__ void warp_softmax_grad_rows(float* sf, float* dpf, const float* lse, const float* delta, const unsigned char* q_ok,
+                                                       const unsigned char* k_ok, float sm_scale, int row0, int lane) {
     const float scale2 = sm_scale * 1.4426950408889634f;
+    T* ps = reinterpret_cast<T*>(sf);
+    T* dss = reinterpret_cast<T*>(dpf);
     for (int e = lane; e < 16 * kTile; e += 32) {
         const int r = row0 + e / kTile, c = e % kTile;
+        const float sv = sf[r * LDF + c], dv = dpf[r * LDF + c];
+        __syncwarp();  // every lane has read before any lane writes into the same bytes
         float p = 0.f, ds = 0.f;
         if (q_ok[r] && k_ok[c]) {
-            p = exp2f(sf[r * LDF + c] * scale2 - lse[r] * 1.4426950408889634f);
-            ds = p * (dpf[r * LDF + c] - delta[r]) * sm_scale;
+            p = exp2f(sv * scale2 - lse[r] * 1.4426950408889634f);
+            ds = p * (dv - delta[r]) * sm_scale;
         }
         ps[r * LDP + c] = DType<T>::from_f32(p);
         dss[r * LDP + c] = DType<T>::from_f32(ds);
+        __syncwarp();
     }
 }
 
@@ -268,8 +276,8 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
     T* vs = reinterpret_cast<T*>(smem + SM::off_d);
     float* sf = reinterpret_cast<float*>(smem + SM::off_sf);
     float* dpf = reinterpret_cast<float*>(smem + SM::off_dpf);
-    T* ps = reinterpret_cast<T*>(smem + SM::off_ps);
-    T* dss = reinterpret_cast<T*>(smem + SM::off_dss);
+    T* ps = reinterpret_cast<T*>(sf);     // P and dS replace S and dP row by row
+    T* dss = reinterpret_cast<T*>(dpf);
     float* lse = reinterpret_cast<float*>(smem + SM::off_sc);
     float* delta = lse + kTile;
     unsigned char* q_ok = reinterpret_cast<unsigned char*>(delta + kTile);
@@ -316,7 +324,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(dpf + row0 * SM::LDF, dos + row0 * SM::LD, vs);
             __syncwarp();
-            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, ps, dss, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
+            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
             __syncwarp();
             // dQ[16 x D] += dS[16 x 64] * K[64 x D]
 #pragma unroll
@@ -332,7 +340,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
             }
         }
     }
-    // every warp stages its 16 rows (its own region of the staging tile), then the CTA writes the rows that exist
+    // every warp stages its 16 rows (its own region of the staging tile, which lies over the K and V tiles), then the
+    // CTA writes the rows that exist
+    __syncthreads();
 #pragma unroll
     for (int n = 0; n < D / 16; ++n) wmma::store_matrix_sync(stage + 16 * warp * SM::LDO + n * 16, acc[n], SM::LDO, wmma::mem_row_major);
     __syncthreads();
@@ -352,8 +362,8 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dkdv_kernel(const __grid_cons
     T* dos = reinterpret_cast<T*>(smem + SM::off_d);
     float* sf = reinterpret_cast<float*>(smem + SM::off_sf);
     float* dpf = reinterpret_cast<float*>(smem + SM::off_dpf);
-    T* ps = reinterpret_cast<T*>(smem + SM::off_ps);
-    T* dss = reinterpret_cast<T*>(smem + SM::off_dss);
+    T* ps = reinterpret_cast<T*>(sf);     // P and dS replace S and dP row by row
+    T* dss = reinterpret_cast<T*>(dpf);
     float* lse = reinterpret_cast<float*>(smem + SM::off_sc);
     float* delta = lse + kTile;
     unsigned char* q_ok = reinterpret_cast<unsigned char*>(delta + kTile);
@@ -402,7 +412,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dkdv_kernel(const __grid_cons
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(dpf + row0 * SM::LDF, dos + row0 * SM::LD, vs);
             __syncwarp();
-            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, ps, dss, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
+            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
             __syncthreads();  // all 64 query rows of P and dS are needed by every warp now
             // key rows 16 * warp ..:  dV += P^T dO,  dK += dS^T Q   (A = P^T: column-major view of the [q][k] tile)
 #pragma unroll

@@ -55,6 +55,8 @@ WORKLOADS = {
     # the block shape flash_attn_bsa_3d takes when the caller passes none: [4, 4, 8], 128 tokens
     "480p_blocks128": _w("480p_blocks128", 1002, 32, (24, 32, 56), chunk=(4, 4, 8)),
     "720p_blocks128": _w("720p_blocks128", 1003, 32, (24, 48, 80), chunk=(4, 4, 8)),
+    # every parameter of the entry point left at its default: [4, 4, 8] blocks and sparsity 0.875 (90 of 720 blocks)
+    "720p_defaults": _w("720p_defaults", 1003, 32, (24, 48, 80), chunk=(4, 4, 8), sparsity=0.875),
     "vc_legal": _w("vc_legal", 1005, 32, (12, 48, 80), (24, 48, 80), recipe="normal"),
     "vc_ragged": _w("vc_ragged", 1005, 32, (11, 45, 80), (24, 45, 80), recipe="normal"),
 }

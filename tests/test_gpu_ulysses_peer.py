@@ -109,6 +109,16 @@ def _worker(rank, world, port, heads, chunk=(4, 4, 4)):
                 fused = flash_attn_bsa_3d_ulysses(q, k, v, grid, sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
                 torch.cuda.synchronize()
                 assert torch.equal(fused, want)
+        # the stage plan of an eight-rank group (heads one by one, pushes queued two stages ahead), run on this group
+        plan = CP._stages_scattered
+        CP._stages_scattered = lambda hn, n=2: plan(hn, 8)
+        try:
+            for _ in range(2):
+                fused = flash_attn_bsa_3d_ulysses(q, k, v, grid, sparsity=0.75, chunk_3d_shape_q=list(chunk), chunk_3d_shape_k=list(chunk))
+                torch.cuda.synchronize()
+                assert torch.equal(fused, want)
+        finally:
+            CP._stages_scattered = plan
         L.check(L.lib().lcbsa_check_device_status())
         # video continuation: the first 4 of every rank's 8 frames are conditioning frames; one exchange and one attention
         # launch per stage against the reference's formulation (two exchanges, two calls on copies, concatenated)
@@ -136,7 +146,7 @@ def _worker(rank, world, port, heads, chunk=(4, 4, 4)):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("heads,chunk", [(4, (4, 4, 4)), (16, (4, 4, 4)), (4, (4, 4, 8))])
+@pytest.mark.parametrize("heads,chunk", [(4, (4, 4, 4)), (8, (4, 4, 4)), (16, (4, 4, 4)), (4, (4, 4, 8))])
 def test_peer_exchange_matches_nccl(heads, chunk):
     """(4, 4, 8): the 128-token blocks that flash_attn_bsa_3d takes by default, served by the other tcgen05 kernel."""
     if torch.cuda.device_count() < 2:
