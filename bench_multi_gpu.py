@@ -96,7 +96,7 @@ def run_multi_gpu(args, wl, heads, world, rank, local_rank, peaks, peak_src):
     q, k, v = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h))
     params = dict(sparsity=wl.sparsity, cdf_threshold=None, chunk_3d_shape_q=list(wl.chunk), chunk_3d_shape_k=list(wl.chunk))
     from longcat_video_b200.context_parallel import bsa_context_parallel as CP
-    stages = CP._stages_scattered(heads // world) if CP._SCATTER_OUT else U._stages(heads // world, U._heads_per_group(heads // world))
+    stages = CP._stages_scattered(heads // world, world) if CP._SCATTER_OUT else U._stages(heads // world, U._heads_per_group(heads // world))
     launches_per_step = 1 + 2 + len(stages)  # pooling (q and k in one launch), score GEMM, top-k, one attention per stage
 
     def call():

@@ -205,9 +205,10 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
  * strides (T,H,W token order, D contiguous); idx, cnt, cap are the lists the forward ran with and lse is the
  * [B*H, Sq] fp32 log-sum-exp (natural log) that the forward returned.  bf16 or fp16, head_dim 64 or 128, block sizes
  * multiples of 64 tokens.  The workspace (lcbsa_attn_bwd_workspace_bytes, 256-byte aligned) holds delta =
- * rowsum(dout * out) and, for every key block, the ascending list of the query blocks that selected it; four
- * launches, no atomics on the gradients, so two calls give the same bits.  Every row of dq, dk, dv that exists is written
- * (rows of blocks that nothing selected get zeros).
+ * rowsum(dout * out) and, for every key block, the ascending list of the query blocks that selected it (built through a
+ * bitmap of (key block, query block) pairs; the entries of one list are taken as distinct); no atomics on the gradients,
+ * so two calls give the same bits.  Every row of dq, dk, dv that exists is written (rows of blocks that nothing selected
+ * get zeros).
  */
 size_t lcbsa_attn_bwd_workspace_bytes(const LcbsaTensor* q, const LcbsaGrid* gq, const LcbsaGrid* gk, int cap);
 int lcbsa_attn_bwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaTensor* out, const LcbsaTensor* dout,

@@ -10,10 +10,10 @@
 //   dP = dO_i V_j^T                dS = P o (dP - delta_i) * scale  dQ_i += dS K_j        dK_j += dS^T Q_i
 //   delta_i = rowsum(dO_i o O_i)
 //
-// Four launches, no atomics on the gradients, every sum in a fixed order:
+// No atomics on the gradients, every sum in a fixed order:
 //   bwd_delta_kernel      delta for every query row (fp32), one pass over dO and O;
-//   bwd_transpose_kernel  for every key block the query blocks that selected it, in ascending order (the lists hold for
-//                         every query block its key blocks): counts, prefix sum and an ordered fill, one CTA per head;
+//   bwd_mark / count / scan / emit   for every key block the query blocks that selected it, in ascending order (the
+//                         lists hold for every query block its key blocks), through a bitmap: four small launches;
 //   bwd_dq_kernel         one CTA per 64 query rows, walks the forward lists;
 //   bwd_dkdv_kernel       one CTA per 64 keys, walks the transposed lists.
 // Tiles are 64 x 64 whatever the block sizes (multiples of 64 tokens): a block of 128 or more tokens is a run of
@@ -77,55 +77,94 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(View o, View dout, float
 
 // ------------------------------------------------------------------------------------------ transposed lists
 
-// One CTA per (batch, head).  Pass 1 counts, pass 2 scans, pass 3 walks the query blocks in ascending order and
-// appends each to the rows of the key blocks on its list, so that every row comes out ascending without a sort.
-// Entries outside [0, Nk) are skipped and flagged.
-__global__ void __launch_bounds__(256) bwd_transpose_kernel(const int32_t* idx, const int32_t* cnt, int cap, int Nq, int Nk, int32_t* tcnt,
-                                                            int32_t* toff, int32_t* tidx, unsigned int* status) {
-    extern __shared__ int32_t cursor[];  // [Nk]
+// The lists hold for every query block its key blocks; the dK/dV pass needs for every key block its query blocks, in a
+// fixed order.  Four small launches: mark (one bit per (key block, query block) pair in a zeroed bitmap), count (a warp
+// per key block adds up the population counts of its bitmap row), scan (exclusive prefix of the counts per head) and emit
+// (a warp per key block turns its bitmap row into the ascending list of its query blocks).  Entries outside [0, Nk) are
+// skipped and flagged; the entries of one list are taken as distinct.
+__global__ void __launch_bounds__(256) bwd_mark_kernel(const int32_t* idx, const int32_t* cnt, int cap, int Nq, int Nk, int Wq, long long total,
+                                                       uint32_t* bitmap, unsigned int* status) {
+    const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const int e = (int)(p % cap);
+    const long long row = p / cap;  // bh * Nq + i
+    const int i = (int)(row % Nq);
+    const long long bh = row / Nq;
+    if (e >= min(max(cnt[row], 0), cap)) return;
+    const int j = idx[p];
+    if ((unsigned)j < (unsigned)Nk) atomicOr(&bitmap[(bh * Nk + j) * Wq + (i >> 5)], 1u << (i & 31));
+    else if (atomicCAS(status, 0u, kStatusBadBlockIndex) == 0u) {
+        status[1] = (unsigned)bh;
+        status[2] = i;
+        status[3] = e;
+    }
+}
+
+__global__ void __launch_bounds__(256) bwd_count_kernel(const uint32_t* bitmap, int Wq, long long rows, int32_t* tcnt) {
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // bh * Nk + j
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    int n = 0;
+    for (int w = lane; w < Wq; w += 32) n += __popc(bitmap[row * Wq + w]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    if (lane == 0) tcnt[row] = n;
+}
+
+// one CTA per (batch, head): toff[j] = sum of tcnt[0 .. j), toff[Nk] = the total
+__global__ void __launch_bounds__(256) bwd_scan_kernel(const int32_t* tcnt, int Nk, int32_t* toff) {
+    __shared__ int part[256];
     const int bh = blockIdx.x, tid = threadIdx.x;
-    const int32_t* my_idx = idx + (long long)bh * Nq * cap;
-    const int32_t* my_cnt = cnt + (long long)bh * Nq;
-    int32_t* my_tcnt = tcnt + (long long)bh * Nk;
-    int32_t* my_toff = toff + (long long)bh * (Nk + 1);
-    int32_t* my_tidx = tidx + (long long)bh * Nq * cap;
-    for (int j = tid; j < Nk; j += blockDim.x) cursor[j] = 0;
+    const int32_t* c = tcnt + (long long)bh * Nk;
+    int32_t* o = toff + (long long)bh * (Nk + 1);
+    const int per = (Nk + 255) / 256, lo = tid * per, hi = min(lo + per, Nk);
+    int sum = 0;
+    for (int j = lo; j < hi; ++j) sum += c[j];
+    part[tid] = sum;
     __syncthreads();
-    for (long long p = tid; p < (long long)Nq * cap; p += blockDim.x) {
-        const int i = (int)(p / cap), e = (int)(p % cap);
-        const int n = min(max(my_cnt[i], 0), cap);
-        if (e < n) {
-            const int j = my_idx[p];
-            if ((unsigned)j < (unsigned)Nk) atomicAdd(&cursor[j], 1);
-            else if (atomicCAS(status, 0u, kStatusBadBlockIndex) == 0u) {
-                status[1] = bh;
-                status[2] = i;
-                status[3] = e;
-            }
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {  // Nk is a few thousand at most: a serial scan costs microseconds
+    if (tid == 0) {
         int run = 0;
-        for (int j = 0; j < Nk; ++j) {
-            const int c = cursor[j];
-            my_tcnt[j] = c;
-            my_toff[j] = run;
-            cursor[j] = run;
-            run += c;
+        for (int t = 0; t < 256; ++t) {
+            const int v = part[t];
+            part[t] = run;
+            run += v;
         }
-        my_toff[Nk] = run;
+        o[Nk] = run;
     }
     __syncthreads();
-    for (int i = 0; i < Nq; ++i) {
-        const int n = min(max(my_cnt[i], 0), cap);
-        for (int e = tid; e < n; e += blockDim.x) {
-            const int j = my_idx[(long long)i * cap + e];
-            // the key blocks of one list are distinct, so no two threads of this step touch the same cursor
-            // (a caller's list with a repeated entry still gets distinct places)
-            if ((unsigned)j < (unsigned)Nk) my_tidx[atomicAdd(&cursor[j], 1)] = i;
+    int run = part[tid];
+    for (int j = lo; j < hi; ++j) {
+        o[j] = run;
+        run += c[j];
+    }
+}
+
+__global__ void __launch_bounds__(256) bwd_emit_kernel(const uint32_t* bitmap, int Wq, int Nk, int Nq, int cap, long long rows, const int32_t* toff,
+                                                       int32_t* tidx) {
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // bh * Nk + j
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const long long bh = row / Nk;
+    const int j = (int)(row % Nk);
+    int32_t* out = tidx + bh * Nq * cap;
+    int base = toff[bh * (Nk + 1) + j];
+    for (int w0 = 0; w0 < Wq; w0 += 32) {
+        const int w = w0 + lane;
+        uint32_t bits = w < Wq ? bitmap[row * Wq + w] : 0u;
+        const int n = __popc(bits);
+        int incl = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
         }
-        __syncthreads();
+        int pos = base + incl - n;
+        while (bits) {
+            const int b = __ffs(bits) - 1;
+            out[pos++] = 32 * w + b;
+            bits &= bits - 1;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
     }
 }
 
@@ -136,19 +175,59 @@ __global__ void __launch_bounds__(256) bwd_transpose_kernel(const int32_t* idx, 
 template <typename T, int D, int LD>
 __device__ __forceinline__ void load_rows(T* tile, unsigned char* present, const T* head, long long ss, const Geom& g, const BwdSlot* tab, int blk,
                                           int slot0, int tid) {
-    constexpr int CPR = D / 8;  // 16-byte chunks per row
+    constexpr int CPR = D / 8;                           // 16-byte chunks per row
+    constexpr int kPer = kTile * CPR / kBwdThreads;      // chunks per thread: all of them in flight before the first store
     int bt, bh, bw;
     block_coords(g, blk, bt, bh, bw);
     const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
     const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
-    for (int v = tid; v < kTile * CPR; v += kBwdThreads) {
-        const int row = v / CPR, c = v % CPR;
+    uint4 val[kPer];
+    bool ok[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
         const BwdSlot e = tab[slot0 + row];
-        const bool ok = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (ok) val = *reinterpret_cast<const uint4*>(head + (origin + e.off) * ss + c * 8);
-        *reinterpret_cast<uint4*>(tile + row * LD + c * 8) = val;
-        if (c == 0 && present != nullptr) present[row] = ok ? 1 : 0;
+        ok[u] = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
+        val[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok[u]) val[u] = __ldg(reinterpret_cast<const uint4*>(head + (origin + e.off) * ss + c * 8));
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
+        *reinterpret_cast<uint4*>(tile + row * LD + c * 8) = val[u];
+        if (c == 0 && present != nullptr) present[row] = ok[u] ? 1 : 0;
+    }
+}
+
+// The same for two tensors that share geometry and slots (K and V of a key tile): both tiles' loads are in flight together.
+template <typename T, int D, int LD>
+__device__ __forceinline__ void load_rows2(T* tile0, T* tile1, unsigned char* present, const T* head0, long long ss0, const T* head1,
+                                           long long ss1, const Geom& g, const BwdSlot* tab, int blk, int slot0, int tid) {
+    constexpr int CPR = D / 8;
+    constexpr int kPer = kTile * CPR / kBwdThreads;
+    int bt, bh, bw;
+    block_coords(g, blk, bt, bh, bw);
+    const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
+    const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
+    uint4 va[kPer], vb[kPer];
+    bool ok[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
+        const BwdSlot e = tab[slot0 + row];
+        ok[u] = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
+        va[u] = vb[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok[u]) {
+            va[u] = __ldg(reinterpret_cast<const uint4*>(head0 + (origin + e.off) * ss0 + c * 8));
+            vb[u] = __ldg(reinterpret_cast<const uint4*>(head1 + (origin + e.off) * ss1 + c * 8));
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
+        *reinterpret_cast<uint4*>(tile0 + row * LD + c * 8) = va[u];
+        *reinterpret_cast<uint4*>(tile1 + row * LD + c * 8) = vb[u];
+        if (c == 0) present[row] = ok[u] ? 1 : 0;
     }
 }
 
@@ -239,28 +318,47 @@ struct BwdSmem {
     static constexpr size_t bytes_no_tab = off_sc + 2 * kTile * sizeof(float) + 2 * kTile;
 };
 
-// P and dS of the 16 query rows of one warp from its S and dP rows (fp32) -> T, written over the same rows: a step of
-// the loop reads 32 consecutive fp32 values of a row (128 bytes) and then writes 32 values of T into the first 64 bytes
-// of the span it has just read (the second step of a row writes bytes 64 .. 127, which the first step has read).
+// P and dS of the 16 query rows of one warp from its S and dP rows (fp32) -> T, written over the same rows.  A lane owns
+// half a row (32 keys): it reads its 32 values of S and of dP into registers, the warp synchronises (the bytes a lane
+// writes belong to the span its neighbour reads), then it writes 32 values of P and of dS.
 template <typename T, int LDF, int LDP>
 __device__ __forceinline__ void warp_softmax_grad_rows(float* sf, float* dpf, const float* lse, const float* delta, const unsigned char* q_ok,
                                                        const unsigned char* k_ok, float sm_scale, int row0, int lane) {
     const float scale2 = sm_scale * 1.4426950408889634f;
-    T* ps = reinterpret_cast<T*>(sf);
-    T* dss = reinterpret_cast<T*>(dpf);
-    for (int e = lane; e < 16 * kTile; e += 32) {
-        const int r = row0 + e / kTile, c = e % kTile;
-        const float sv = sf[r * LDF + c], dv = dpf[r * LDF + c];
-        __syncwarp();  // every lane has read before any lane writes into the same bytes
-        float p = 0.f, ds = 0.f;
-        if (q_ok[r] && k_ok[c]) {
-            p = exp2f(sv * scale2 - lse[r] * 1.4426950408889634f);
-            ds = p * (dv - delta[r]) * sm_scale;
-        }
-        ps[r * LDP + c] = DType<T>::from_f32(p);
-        dss[r * LDP + c] = DType<T>::from_f32(ds);
-        __syncwarp();
+    const int r = row0 + (lane >> 1), c0 = (lane & 1) * 32;
+    float sv[32], dv[32];
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const float4 a = *reinterpret_cast<const float4*>(sf + r * LDF + c0 + 4 * x);
+        const float4 b = *reinterpret_cast<const float4*>(dpf + r * LDF + c0 + 4 * x);
+        sv[4 * x] = a.x; sv[4 * x + 1] = a.y; sv[4 * x + 2] = a.z; sv[4 * x + 3] = a.w;
+        dv[4 * x] = b.x; dv[4 * x + 1] = b.y; dv[4 * x + 2] = b.z; dv[4 * x + 3] = b.w;
     }
+    const float l2 = lse[r] * 1.4426950408889634f, dl = delta[r];
+    const bool row_ok = q_ok[r] != 0;
+    uint32_t kf[8];  // presence flags of this lane's 32 keys, four per word
+#pragma unroll
+    for (int x = 0; x < 8; ++x) kf[x] = *reinterpret_cast<const uint32_t*>(k_ok + c0 + 4 * x);
+    __syncwarp();
+    T* ps = reinterpret_cast<T*>(sf) + r * LDP + c0;
+    T* dss = reinterpret_cast<T*>(dpf) + r * LDP + c0;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        uint4 pw, dw;
+        T* p8 = reinterpret_cast<T*>(&pw);
+        T* d8 = reinterpret_cast<T*>(&dw);
+#pragma unroll
+        for (int y = 0; y < 8; ++y) {
+            const int c = 8 * x + y;
+            const bool ok = row_ok && ((kf[c >> 2] >> (8 * (c & 3))) & 0xffu) != 0;
+            const float p = ok ? exp2f(sv[c] * scale2 - l2) : 0.f;
+            p8[y] = DType<T>::from_f32(p);
+            d8[y] = DType<T>::from_f32(p * (dv[c] - dl) * sm_scale);
+        }
+        *reinterpret_cast<uint4*>(ps + 8 * x) = pw;
+        *reinterpret_cast<uint4*>(dss + 8 * x) = dw;
+    }
+    __syncwarp();
 }
 
 // ------------------------------------------------------------------------------------------ dQ
@@ -317,8 +415,7 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
         if ((unsigned)kb >= (unsigned)a.gk.nblk) continue;  // flagged by the transpose kernel; uniform over the CTA
         for (int ksub = 0; ksub < tiles_k; ++ksub) {
             __syncthreads();  // the previous tile's K and V have been read by every warp
-            load_rows<T, D, SM::LD>(ks, k_ok, kh, a.k.ss, a.gk, ktab, kb, ksub * kTile, tid);
-            load_rows<T, D, SM::LD>(vs, nullptr, vh, a.v.ss, a.gk, ktab, kb, ksub * kTile, tid);
+            load_rows2<T, D, SM::LD>(ks, vs, k_ok, kh, a.k.ss, vh, a.v.ss, a.gk, ktab, kb, ksub * kTile, tid);
             __syncthreads();
             const int row0 = 16 * warp;
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
@@ -457,16 +554,15 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         if (e != cudaSuccess) return e;
     }
     {
-        const size_t cursor_bytes = (size_t)a.gk.nblk * sizeof(int32_t);
-        if (cursor_bytes > 200 * 1024) { *why = "more than 51200 key blocks"; return cudaErrorInvalidValue; }
-        static bool attr_t = false;  // raising the limit twice is harmless
-        if (cursor_bytes > 48 * 1024 && !attr_t) {
-            cudaError_t e = cudaFuncSetAttribute(bwd_transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e != cudaSuccess) return e;
-            attr_t = true;
-        }
-        bwd_transpose_kernel<<<BH, 256, cursor_bytes, st>>>(a.idx, a.cnt, a.cap, a.gq.nblk, a.gk.nblk, a.tcnt, a.toff, a.tidx, a.status);
-        cudaError_t e = cudaGetLastError();
+        const int Nq = a.gq.nblk, Nk = a.gk.nblk, Wq = (Nq + 31) / 32;
+        const long long rows_k = (long long)BH * Nk, entries = (long long)BH * Nq * a.cap;
+        cudaError_t e = cudaMemsetAsync(a.bitmap, 0, (size_t)rows_k * Wq * sizeof(uint32_t), st);
+        if (e != cudaSuccess) return e;
+        bwd_mark_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, Nq, Nk, Wq, entries, a.bitmap, a.status);
+        bwd_count_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, rows_k, a.tcnt);
+        bwd_scan_kernel<<<BH, 256, 0, st>>>(a.tcnt, Nk, a.toff);
+        bwd_emit_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, Nk, Nq, a.cap, rows_k, a.toff, a.tidx);
+        e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
     const size_t smem = SM::bytes_no_tab + (size_t)(a.gq.bs + a.gk.bs) * sizeof(BwdSlot);
@@ -499,7 +595,7 @@ bool attn_bwd_supported(const BwdArgs& a, const char** why) {
 size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap) {
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     return up((size_t)BH * Sq * sizeof(float)) + up((size_t)BH * Nk * sizeof(int32_t)) + up((size_t)BH * (Nk + 1) * sizeof(int32_t)) +
-           up((size_t)BH * Nq * cap * sizeof(int32_t));
+           up((size_t)BH * Nq * cap * sizeof(int32_t)) + up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t));
 }
 
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why) {
@@ -513,6 +609,8 @@ cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const c
     a.toff = reinterpret_cast<int32_t*>(w);
     w += up((size_t)BH * (a.gk.nblk + 1) * sizeof(int32_t));
     a.tidx = reinterpret_cast<int32_t*>(w);
+    w += up((size_t)BH * a.gq.nblk * a.cap * sizeof(int32_t));
+    a.bitmap = reinterpret_cast<uint32_t*>(w);
     if (a.dtype == LCBSA_BF16) return a.D == 128 ? run_bwd<__nv_bfloat16, 128>(a, st, why) : run_bwd<__nv_bfloat16, 64>(a, st, why);
     return a.D == 128 ? run_bwd<__half, 128>(a, st, why) : run_bwd<__half, 64>(a, st, why);
 }

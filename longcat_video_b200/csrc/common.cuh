@@ -146,6 +146,7 @@ struct BwdArgs {
     int32_t* tcnt;        // [B*H, Nk]       query blocks per key block
     int32_t* toff;        // [B*H, Nk + 1]   exclusive prefix of tcnt
     int32_t* tidx;        // [B*H, Nq * cap] query blocks of key block j at toff[j] .. toff[j + 1], ascending
+    uint32_t* bitmap;     // [B*H, Nk, ceil(Nq / 32)] bit i of row j: query block i selected key block j
 };
 bool attn_bwd_supported(const BwdArgs& a, const char** why);
 size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap);
