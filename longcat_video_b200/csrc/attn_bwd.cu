@@ -199,35 +199,44 @@ __device__ __forceinline__ void load_rows(T* tile, unsigned char* present, const
     }
 }
 
-// The same for two tensors that share geometry and slots (K and V of a key tile): both tiles' loads are in flight together.
-template <typename T, int D, int LD>
-__device__ __forceinline__ void load_rows2(T* tile0, T* tile1, unsigned char* present, const T* head0, long long ss0, const T* head1,
-                                           long long ss1, const Geom& g, const BwdSlot* tab, int blk, int slot0, int tid) {
+// Two tensors that share geometry and slots (K and V of a key tile), in two steps: fetch_rows2 issues every load of the
+// thread into registers, commit_rows2 writes them to the shared tiles.  The dQ kernel fetches tile i + 1 before it
+// computes on tile i, so the global-memory latency is spent under the contractions.  valid == false: a tile of zeros.
+template <int D>
+struct RowRegs2 {
+    static constexpr int kPer = kTile * (D / 8) / kBwdThreads;
+    uint4 a[kPer], b[kPer];
+    bool ok[kPer];
+};
+template <typename T, int D>
+__device__ __forceinline__ void fetch_rows2(RowRegs2<D>& r, const T* head0, long long ss0, const T* head1, long long ss1, const Geom& g,
+                                            const BwdSlot* tab, int blk, int slot0, bool valid, int tid) {
     constexpr int CPR = D / 8;
-    constexpr int kPer = kTile * CPR / kBwdThreads;
     int bt, bh, bw;
-    block_coords(g, blk, bt, bh, bw);
+    block_coords(g, valid ? blk : 0, bt, bh, bw);
     const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
     const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
-    uint4 va[kPer], vb[kPer];
-    bool ok[kPer];
 #pragma unroll
-    for (int u = 0; u < kPer; ++u) {
+    for (int u = 0; u < RowRegs2<D>::kPer; ++u) {
         const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
         const BwdSlot e = tab[slot0 + row];
-        ok[u] = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
-        va[u] = vb[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (ok[u]) {
-            va[u] = __ldg(reinterpret_cast<const uint4*>(head0 + (origin + e.off) * ss0 + c * 8));
-            vb[u] = __ldg(reinterpret_cast<const uint4*>(head1 + (origin + e.off) * ss1 + c * 8));
+        r.ok[u] = valid && (!g.ragged || slot_in_grid(g, e.packed, t0, h0, w0));
+        r.a[u] = r.b[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (r.ok[u]) {
+            r.a[u] = __ldg(reinterpret_cast<const uint4*>(head0 + (origin + e.off) * ss0 + c * 8));
+            r.b[u] = __ldg(reinterpret_cast<const uint4*>(head1 + (origin + e.off) * ss1 + c * 8));
         }
     }
+}
+template <typename T, int D, int LD>
+__device__ __forceinline__ void commit_rows2(const RowRegs2<D>& r, T* tile0, T* tile1, unsigned char* present, int tid) {
+    constexpr int CPR = D / 8;
 #pragma unroll
-    for (int u = 0; u < kPer; ++u) {
+    for (int u = 0; u < RowRegs2<D>::kPer; ++u) {
         const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
-        *reinterpret_cast<uint4*>(tile0 + row * LD + c * 8) = va[u];
-        *reinterpret_cast<uint4*>(tile1 + row * LD + c * 8) = vb[u];
-        if (c == 0) present[row] = ok[u] ? 1 : 0;
+        *reinterpret_cast<uint4*>(tile0 + row * LD + c * 8) = r.a[u];
+        *reinterpret_cast<uint4*>(tile1 + row * LD + c * 8) = r.b[u];
+        if (c == 0) present[row] = r.ok[u] ? 1 : 0;
     }
 }
 
@@ -410,13 +419,21 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
 
     const int32_t* list = a.idx + ((long long)bh * a.gq.nblk + qb) * a.cap;
     const int n_list = min(max(a.cnt[(long long)bh * a.gq.nblk + qb], 0), a.cap);
-    for (int e = 0; e < n_list; ++e) {
-        const int kb = list[e];
-        if ((unsigned)kb >= (unsigned)a.gk.nblk) continue;  // flagged by the transpose kernel; uniform over the CTA
-        for (int ksub = 0; ksub < tiles_k; ++ksub) {
-            __syncthreads();  // the previous tile's K and V have been read by every warp
-            load_rows2<T, D, SM::LD>(ks, vs, k_ok, kh, a.k.ss, vh, a.v.ss, a.gk, ktab, kb, ksub * kTile, tid);
-            __syncthreads();
+    // tiles of the listed key blocks, one after the other; tile it + 1 is fetched into registers while tile it is
+    // computed on.  An entry outside [0, Nk) (flagged by the mark kernel) is a tile of absent keys.
+    const int n_tiles = n_list * tiles_k;
+    RowRegs2<D> regs;
+    auto fetch = [&](int it) {
+        const int kb = list[it / tiles_k];
+        fetch_rows2<T, D>(regs, kh, a.k.ss, vh, a.v.ss, a.gk, ktab, kb, (it % tiles_k) * kTile, (unsigned)kb < (unsigned)a.gk.nblk, tid);
+    };
+    if (n_tiles > 0) fetch(0);
+    for (int it = 0; it < n_tiles; ++it) {
+        __syncthreads();  // the previous tile's K and V have been read by every warp
+        commit_rows2<T, D, SM::LD>(regs, ks, vs, k_ok, tid);
+        __syncthreads();
+        if (it + 1 < n_tiles) fetch(it + 1);
+        {
             const int row0 = 16 * warp;
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
             warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(dpf + row0 * SM::LDF, dos + row0 * SM::LD, vs);
