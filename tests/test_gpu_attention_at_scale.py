@@ -83,9 +83,12 @@ def _run_config(wl, n_sample, allow_ragged=False):
 
 
 @pytest.mark.parametrize("name,n_sample", [("480p_legal", 80), ("720p_legal", 60), ("720p_bucket", 60), ("720p_ragged", 60),
-                                           ("480p_ragged", 80), ("vc_legal", 60), ("vc_ragged", 60)])
+                                           ("480p_ragged", 80), ("vc_legal", 60), ("vc_ragged", 60),
+                                           ("480p_blocks128", 40), ("720p_blocks128", 30), ("720p_defaults", 30)])
 def test_one_head_of_benchmark_configs(name, n_sample):
-    """k = 39 (480p), 90 (720p legal and ragged), 82 (720p bucket); the vc shapes have Tq = 12 / 11 against Tk = 24."""
+    """k = 39 (480p), 90 (720p legal and ragged), 82 (720p bucket); the vc shapes have Tq = 12 / 11 against Tk = 24.  The
+    last three run the 128-token kernel: [4, 4, 8] blocks at the headline's sparsity (21 of 336, 45 of 720 blocks) and with
+    every parameter of the entry point at its default (90 of 720)."""
     wl = _one_head(WORKLOADS[name])
     ragged = any(g % c for grid in (wl.grid_q, wl.grid_k) for g, c in zip(grid, wl.chunk))
     _run_config(wl, n_sample, allow_ragged=ragged)

@@ -81,3 +81,19 @@ def test_identity_without_context_parallel():
     assert a is q and b is q and c is q and U.ulysses_a2a_out(q) is q
     assert U.all_to_all(q, 1, 2) is q  # process group not initialised
     assert cpu_.get_optimal_split(2) == [1, 2] and cpu_.get_optimal_split(4) == [2, 2] and cpu_.get_optimal_split(8) == [2, 4]
+
+
+def test_stage_plan_of_the_context_parallel_op():
+    """Host logic of flash_attn_bsa_3d_ulysses: the head ranges of the stages partition the rank's heads for every group
+    size; the first stage is never larger than two heads; on eight ranks the first four heads go one by one."""
+    from longcat_video_b200.context_parallel.bsa_context_parallel import _stages_scattered
+
+    for n in (2, 4, 8):
+        for hn in (1, 2, 3, 4, 5, 6, 8, 12, 16, 32):
+            st = _stages_scattered(hn, n)
+            assert st[0][0] == 0 and st[-1][1] == hn
+            assert all(a[1] == b[0] for a, b in zip(st, st[1:])) and all(lo < hi for lo, hi in st)
+            assert st[0][1] - st[0][0] <= 2
+    assert _stages_scattered(4, 8) == [(0, 1), (1, 2), (2, 3), (3, 4)]
+    assert _stages_scattered(8, 4) == [(0, 1), (1, 4), (4, 8)]
+    assert _stages_scattered(16, 2) == [(0, 2), (2, 8), (8, 16)]
