@@ -14,37 +14,20 @@
 //   bwd_delta_kernel      delta for every query row (fp32), one pass over dO and O;
 //   bwd_mark / count / scan / emit   for every key block the query blocks that selected it, in ascending order (the
 //                         lists hold for every query block its key blocks), through a bitmap: four small launches;
-//   bwd_dq_kernel         one CTA per 64 query rows, walks the forward lists;
-//   bwd_dkdv_kernel       one CTA per 64 keys, walks the transposed lists.
+//   bwd_dq_mma_kernel     one CTA per 64 query rows, walks the forward lists;
+//   bwd_dkdv_mma_kernel   one CTA per 64 keys, walks the transposed lists.
 // Tiles are 64 x 64 whatever the block sizes (multiples of 64 tokens): a block of 128 or more tokens is a run of
-// 64-row tiles in slot order.  The contractions run on the tensor cores through warp-level mma (wmma, fp32
-// accumulation); P and dS are rounded to the input dtype before they enter a contraction, as in the forward.
-// This is the first, plain version of the backward: its roofline is the mma.sync rate, not tcgen05's.
-#include <mma.h>
-
-#include "common.cuh"
+// 64-row tiles in slot order.  The contractions run on the tensor cores through warp-level mma (mma.sync m16n8k16 fed by
+// ldmatrix, fp32 accumulation); P and dS are rounded to the input dtype before they enter a contraction, as in the
+// forward.  This is the plain version of the backward: its roofline is the mma.sync rate, not tcgen05's.
+#include "mma_common.cuh"
 
 namespace lcbsa {
 
 namespace {
 
-using namespace nvcuda;
-
 constexpr int kTile = 64;      // rows and keys per tile
 constexpr int kBwdThreads = 128;
-
-struct BwdSlot {
-    int off;     // token offset of the slot relative to the block's first token
-    int packed;  // lt | lh << 10 | lw << 20
-};
-
-template <typename T> struct Wm;
-template <> struct Wm<__nv_bfloat16> { using type = __nv_bfloat16; };
-template <> struct Wm<__half> { using type = half; };
-
-__device__ __forceinline__ bool slot_in_grid(const Geom& g, int packed, int t0, int h0, int w0) {
-    return (t0 + (packed & 1023) < g.T) && (h0 + ((packed >> 10) & 1023) < g.H) && (w0 + (packed >> 20) < g.W);
-}
 
 // ------------------------------------------------------------------------------------------ delta
 
@@ -168,237 +151,140 @@ __global__ void __launch_bounds__(256) bwd_emit_kernel(const uint32_t* bitmap, i
     }
 }
 
-// ------------------------------------------------------------------------------------------ tile helpers
+// ------------------------------------------------------------------------------------------ dQ and dK/dV
+//
+// Both passes run on mma.sync m16n8k16 with ldmatrix from 128-byte-row swizzled tiles (the machinery of the generic
+// forward, attn_mma.cu).  S, dP, P and dS never leave registers: the accumulator layout of one contraction is
+// the A-operand layout of the next (as P is for P V in the forward).  64 x 64 tiles, four warps of 16 rows, the
+// streamed tiles double-buffered with cp.async, two CTAs per SM.
 
-// Gather 64 slots (slot0 ..) of block `blk` of a [S, D] head into a [64][LD] shared tile; absent tokens read as zero.
-// present[r] says whether row r exists.  Called by all threads of the CTA.
-template <typename T, int D, int LD>
-__device__ __forceinline__ void load_rows(T* tile, unsigned char* present, const T* head, long long ss, const Geom& g, const BwdSlot* tab, int blk,
-                                          int slot0, int tid) {
-    constexpr int CPR = D / 8;                           // 16-byte chunks per row
-    constexpr int kPer = kTile * CPR / kBwdThreads;      // chunks per thread: all of them in flight before the first store
-    int bt, bh, bw;
-    block_coords(g, blk, bt, bh, bw);
-    const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
-    const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
-    uint4 val[kPer];
-    bool ok[kPer];
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
-        const BwdSlot e = tab[slot0 + row];
-        ok[u] = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
-        val[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (ok[u]) val[u] = __ldg(reinterpret_cast<const uint4*>(head + (origin + e.off) * ss + c * 8));
-    }
-#pragma unroll
-    for (int u = 0; u < kPer; ++u) {
-        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
-        *reinterpret_cast<uint4*>(tile + row * LD + c * 8) = val[u];
-        if (c == 0 && present != nullptr) present[row] = ok[u] ? 1 : 0;
-    }
-}
-
-// Two tensors that share geometry and slots (K and V of a key tile), in two steps: fetch_rows2 issues every load of the
-// thread into registers, commit_rows2 writes them to the shared tiles.  The dQ kernel fetches tile i + 1 before it
-// computes on tile i, so the global-memory latency is spent under the contractions.  valid == false: a tile of zeros.
-template <int D>
-struct RowRegs2 {
-    static constexpr int kPer = kTile * (D / 8) / kBwdThreads;
-    uint4 a[kPer], b[kPer];
-    bool ok[kPer];
-};
+// 16 rows x 64 columns (fp32 accumulators, 8 n-tiles) = A[16 x D] * B[64 x D]^T with A already in registers
 template <typename T, int D>
-__device__ __forceinline__ void fetch_rows2(RowRegs2<D>& r, const T* head0, long long ss0, const T* head1, long long ss1, const Geom& g,
-                                            const BwdSlot* tab, int blk, int slot0, bool valid, int tid) {
-    constexpr int CPR = D / 8;
-    int bt, bh, bw;
-    block_coords(g, valid ? blk : 0, bt, bh, bw);
-    const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
-    const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
+__device__ __forceinline__ void mma_abt(float (&acc)[8][4], const uint32_t (&af)[D / 16][4], uint32_t b_tile, int lane) {
 #pragma unroll
-    for (int u = 0; u < RowRegs2<D>::kPer; ++u) {
-        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
-        const BwdSlot e = tab[slot0 + row];
-        r.ok[u] = valid && (!g.ragged || slot_in_grid(g, e.packed, t0, h0, w0));
-        r.a[u] = r.b[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (r.ok[u]) {
-            r.a[u] = __ldg(reinterpret_cast<const uint4*>(head0 + (origin + e.off) * ss0 + c * 8));
-            r.b[u] = __ldg(reinterpret_cast<const uint4*>(head1 + (origin + e.off) * ss1 + c * 8));
+    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            const int mid = lane >> 3;
+            const int row = np * 16 + (lane & 7) + (mid >> 1) * 8;
+            const int c = 2 * ks + (mid & 1);
+            uint32_t bf[4];
+            mm::ldsm_x4(bf, b_tile + row * (D * 2) + ((c ^ (row & 7)) << 4));
+            mm::mma16816<T>(acc[2 * np], af[ks], bf[0], bf[1]);
+            mm::mma16816<T>(acc[2 * np + 1], af[ks], bf[2], bf[3]);
         }
     }
 }
-template <typename T, int D, int LD>
-__device__ __forceinline__ void commit_rows2(const RowRegs2<D>& r, T* tile0, T* tile1, unsigned char* present, int tid) {
-    constexpr int CPR = D / 8;
+
+// A fragments (16 rows of this warp, all of D) of a swizzled [64][D] tile
+template <int D>
+__device__ __forceinline__ void load_a_frags(uint32_t (&af)[D / 16][4], uint32_t tile, int warp, int lane) {
+    const int row = warp * 16 + (lane & 15);
 #pragma unroll
-    for (int u = 0; u < RowRegs2<D>::kPer; ++u) {
-        const int v = tid + u * kBwdThreads, row = v / CPR, c = v % CPR;
-        *reinterpret_cast<uint4*>(tile0 + row * LD + c * 8) = r.a[u];
-        *reinterpret_cast<uint4*>(tile1 + row * LD + c * 8) = r.b[u];
-        if (c == 0) present[row] = r.ok[u] ? 1 : 0;
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int c = 2 * ks + (lane >> 4);
+        mm::ldsm_x4(af[ks], tile + row * (D * 2) + ((c ^ (row & 7)) << 4));
     }
 }
 
-// fp32 per-row values (lse or delta) of the same 64 slots; absent rows read as zero.
-__device__ __forceinline__ void load_row_scalars(float* dst, const float* src, const Geom& g, const BwdSlot* tab, int blk, int slot0, int tid) {
-    int bt, bh, bw;
-    block_coords(g, blk, bt, bh, bw);
-    const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
-    const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
-    for (int r = tid; r < kTile; r += kBwdThreads) {
-        const BwdSlot e = tab[slot0 + r];
-        const bool ok = !g.ragged || slot_in_grid(g, e.packed, t0, h0, w0);
-        dst[r] = ok ? src[origin + e.off] : 0.f;
+// out[16 x D] += X[16 x 64] * B[64 x D], X given as fp32 accumulators of the layout mma_abt produces (rounded to T here)
+template <typename T, int D>
+__device__ __forceinline__ void mma_xb(float (&out)[D / 8][4], const float (&x)[8][4], uint32_t b_tile, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        uint32_t pa[4];
+        pa[0] = mm::pack2(T(), x[2 * kk][0], x[2 * kk][1]);
+        pa[1] = mm::pack2(T(), x[2 * kk][2], x[2 * kk][3]);
+        pa[2] = mm::pack2(T(), x[2 * kk + 1][0], x[2 * kk + 1][1]);
+        pa[3] = mm::pack2(T(), x[2 * kk + 1][2], x[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            const int mid = lane >> 3;
+            const int row = kk * 16 + (lane & 7) + (mid & 1) * 8;
+            const int c = 2 * dp + (mid >> 1);
+            uint32_t bf[4];
+            mm::ldsm_x4_t(bf, b_tile + row * (D * 2) + ((c ^ (row & 7)) << 4));
+            mm::mma16816<T>(out[2 * dp], pa, bf[0], bf[1]);
+            mm::mma16816<T>(out[2 * dp + 1], pa, bf[2], bf[3]);
+        }
     }
 }
 
-// Write a [64][D] fp32 tile (leading dimension LDF) as T into the rows of the block that exist.
-template <typename T, int D, int LDF>
-__device__ __forceinline__ void store_rows(const float* tile, T* head, long long ss, const Geom& g, const BwdSlot* tab, int blk, int slot0, int tid) {
-    constexpr int CPR = D / 8;
+// fp32 accumulators of this warp's 16 rows (all of D) -> a swizzled [64][D] tile in T
+template <typename T, int D>
+__device__ __forceinline__ void stage_rows(unsigned char* tile, const float (&o)[D / 8][4], int warp, int lane) {
+    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        const int col = i * 8 + 2 * (lane & 3);
+        const int c = col >> 3, within = (col & 7) * 2;
+        *reinterpret_cast<uint32_t*>(tile + r0 * (D * 2) + ((c ^ (r0 & 7)) << 4) + within) = mm::pack2(T(), o[i][0], o[i][1]);
+        *reinterpret_cast<uint32_t*>(tile + r1 * (D * 2) + ((c ^ (r1 & 7)) << 4) + within) = mm::pack2(T(), o[i][2], o[i][3]);
+    }
+}
+
+// rows of a swizzled [64][D] tile -> the rows of the block that exist
+template <typename T, int D>
+__device__ __forceinline__ void write_rows(const unsigned char* tile, T* head, long long ss, const Geom& g, const mm::SlotEntry* tab, int blk,
+                                           int slot0, int tid) {
+    constexpr int CPR = D * 2 / 16;
     int bt, bh, bw;
     block_coords(g, blk, bt, bh, bw);
     const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
     const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
     for (int v = tid; v < kTile * CPR; v += kBwdThreads) {
         const int row = v / CPR, c = v % CPR;
-        const BwdSlot e = tab[slot0 + row];
-        if (g.ragged && !slot_in_grid(g, e.packed, t0, h0, w0)) continue;
-        uint4 val;
-        T* v8 = reinterpret_cast<T*>(&val);
-#pragma unroll
-        for (int x = 0; x < 8; ++x) v8[x] = DType<T>::from_f32(tile[row * LDF + c * 8 + x]);
-        *reinterpret_cast<uint4*>(head + (origin + e.off) * ss + c * 8) = val;
+        const mm::SlotEntry e = tab[slot0 + row];
+        if (g.ragged && !mm::slot_present(g, e.packed, t0, h0, w0)) continue;
+        *reinterpret_cast<uint4*>(head + (origin + e.off) * ss + c * 8) =
+            *reinterpret_cast<const uint4*>(tile + row * (D * 2) + ((c ^ (row & 7)) << 4));
     }
 }
 
-__device__ __forceinline__ void fill_slot_table(BwdSlot* tab, const Geom& g, int tid) {
+// lse (scaled to log2), delta and presence of 64 rows of a query block -> shared arrays
+__device__ __forceinline__ void load_q_scalars(float* lse2, float* delta, unsigned char* ok, const float* lse_head, const float* delta_head,
+                                               const Geom& g, const mm::SlotEntry* tab, int blk, int slot0, int tid) {
+    int bt, bh, bw;
+    block_coords(g, blk, bt, bh, bw);
+    const int t0 = bt * g.ct, h0 = bh * g.ch, w0 = bw * g.cw;
+    const long long origin = ((long long)t0 * g.H + h0) * g.W + w0;
+    for (int r = tid; r < kTile; r += kBwdThreads) {
+        const mm::SlotEntry e = tab[slot0 + r];
+        const bool p = !g.ragged || mm::slot_present(g, e.packed, t0, h0, w0);
+        lse2[r] = p ? lse_head[origin + e.off] * 1.4426950408889634f : 0.f;
+        delta[r] = p ? delta_head[origin + e.off] : 0.f;
+        ok[r] = p ? 1 : 0;
+    }
+}
+
+__device__ __forceinline__ void fill_slots(mm::SlotEntry* tab, const Geom& g, int tid) {
     for (int r = tid; r < g.bs; r += kBwdThreads) {
         int lt, lh, lw;
         slot_coords(g, r, lt, lh, lw);
-        tab[r] = BwdSlot{(lt * g.H + lh) * g.W + lw, lt | (lh << 10) | (lw << 20)};
+        tab[r] = mm::SlotEntry{(lt * g.H + lh) * g.W + lw, lt | (lh << 10) | (lw << 20)};
     }
 }
-
-// One warp: C[16 x 64] (fp32, into `out` with leading dimension LDO) = A[16 x D] * B[64 x D]^T.
-template <typename T, int D, int LDA, int LDB, int LDO>
-__device__ __forceinline__ void warp_abt_16x64(float* out, const T* a_rows, const T* b_rows) {
-    using W = typename Wm<T>::type;
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) wmma::fill_fragment(acc[n], 0.f);
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, W, wmma::row_major> fa;
-        wmma::load_matrix_sync(fa, reinterpret_cast<const W*>(a_rows) + kk * 16, LDA);
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, W, wmma::col_major> fb;  // B(k, n) = b_rows[n][k]
-            wmma::load_matrix_sync(fb, reinterpret_cast<const W*>(b_rows) + n * 16 * LDB + kk * 16, LDB);
-            wmma::mma_sync(acc[n], fa, fb, acc[n]);
-        }
-    }
-#pragma unroll
-    for (int n = 0; n < 4; ++n) wmma::store_matrix_sync(out + n * 16, acc[n], LDO, wmma::mem_row_major);
-}
-
-// ------------------------------------------------------------------------------------------ shared-memory plan
-
-// About 106 KB for head_dim 128, so that two CTAs share an SM.  P and dS (input dtype) are written over the rows of S and
-// dP (fp32) they were computed from, and the fp32 staging of a finished [64][D] result lies over the two operand tiles
-// that are dead by then.
-template <typename T, int D>
-struct BwdSmem {
-    static constexpr int LD = D + 8;        // operand tiles, in elements (row stride 16 bytes off a bank period)
-    static constexpr int LDF = kTile + 4;   // fp32 S / dP tiles
-    static constexpr int LDP = 2 * LDF;     // the same rows seen as T: P / dS in place
-    static constexpr int LDO = D + 4;       // fp32 staging of a [64][D] result
-    static constexpr size_t tile_bytes = (size_t)kTile * LD * sizeof(T);
-    static constexpr size_t f_bytes = (size_t)kTile * LDF * sizeof(float);
-    static constexpr size_t stage_bytes = (size_t)kTile * LDO * sizeof(float);
-    static_assert(stage_bytes <= 2 * tile_bytes, "the staging tile lies over operand tiles c and d");
-    // a, b, c, d: four operand tiles; sf, dpf: fp32 (then P, dS); scalars: lse, delta (fp32 x 64 each), flags (2 x 64 bytes)
-    static constexpr size_t off_a = 0, off_b = tile_bytes, off_c = 2 * tile_bytes, off_d = 3 * tile_bytes;
-    static constexpr size_t off_sf = 4 * tile_bytes;
-    static constexpr size_t off_dpf = off_sf + f_bytes;
-    static constexpr size_t off_sc = off_dpf + f_bytes;
-    static constexpr size_t off_stage = off_c;
-    static constexpr size_t bytes_no_tab = off_sc + 2 * kTile * sizeof(float) + 2 * kTile;
-};
-
-// P and dS of the 16 query rows of one warp from its S and dP rows (fp32) -> T, written over the same rows.  A lane owns
-// half a row (32 keys): it reads its 32 values of S and of dP into registers, the warp synchronises (the bytes a lane
-// writes belong to the span its neighbour reads), then it writes 32 values of P and of dS.
-template <typename T, int LDF, int LDP>
-__device__ __forceinline__ void warp_softmax_grad_rows(float* sf, float* dpf, const float* lse, const float* delta, const unsigned char* q_ok,
-                                                       const unsigned char* k_ok, float sm_scale, int row0, int lane) {
-    const float scale2 = sm_scale * 1.4426950408889634f;
-    const int r = row0 + (lane >> 1), c0 = (lane & 1) * 32;
-    float sv[32], dv[32];
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-        const float4 a = *reinterpret_cast<const float4*>(sf + r * LDF + c0 + 4 * x);
-        const float4 b = *reinterpret_cast<const float4*>(dpf + r * LDF + c0 + 4 * x);
-        sv[4 * x] = a.x; sv[4 * x + 1] = a.y; sv[4 * x + 2] = a.z; sv[4 * x + 3] = a.w;
-        dv[4 * x] = b.x; dv[4 * x + 1] = b.y; dv[4 * x + 2] = b.z; dv[4 * x + 3] = b.w;
-    }
-    const float l2 = lse[r] * 1.4426950408889634f, dl = delta[r];
-    const bool row_ok = q_ok[r] != 0;
-    uint32_t kf[8];  // presence flags of this lane's 32 keys, four per word
-#pragma unroll
-    for (int x = 0; x < 8; ++x) kf[x] = *reinterpret_cast<const uint32_t*>(k_ok + c0 + 4 * x);
-    __syncwarp();
-    T* ps = reinterpret_cast<T*>(sf) + r * LDP + c0;
-    T* dss = reinterpret_cast<T*>(dpf) + r * LDP + c0;
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-        uint4 pw, dw;
-        T* p8 = reinterpret_cast<T*>(&pw);
-        T* d8 = reinterpret_cast<T*>(&dw);
-#pragma unroll
-        for (int y = 0; y < 8; ++y) {
-            const int c = 8 * x + y;
-            const bool ok = row_ok && ((kf[c >> 2] >> (8 * (c & 3))) & 0xffu) != 0;
-            const float p = ok ? exp2f(sv[c] * scale2 - l2) : 0.f;
-            p8[y] = DType<T>::from_f32(p);
-            d8[y] = DType<T>::from_f32(p * (dv[c] - dl) * sm_scale);
-        }
-        *reinterpret_cast<uint4*>(ps + 8 * x) = pw;
-        *reinterpret_cast<uint4*>(dss + 8 * x) = dw;
-    }
-    __syncwarp();
-}
-
-// ------------------------------------------------------------------------------------------ dQ
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_constant__ BwdArgs a) {
-    using SM = BwdSmem<T, D>;
-    using W = typename Wm<T>::type;
+__global__ void __launch_bounds__(kBwdThreads, 2) bwd_dq_mma_kernel(const __grid_constant__ BwdArgs a) {
+    constexpr int kTB = kTile * D * 2;  // bytes of a tile
     extern __shared__ __align__(128) unsigned char smem[];
-    T* qs = reinterpret_cast<T*>(smem + SM::off_a);
-    T* dos = reinterpret_cast<T*>(smem + SM::off_b);
-    T* ks = reinterpret_cast<T*>(smem + SM::off_c);
-    T* vs = reinterpret_cast<T*>(smem + SM::off_d);
-    float* sf = reinterpret_cast<float*>(smem + SM::off_sf);
-    float* dpf = reinterpret_cast<float*>(smem + SM::off_dpf);
-    T* ps = reinterpret_cast<T*>(sf);     // P and dS replace S and dP row by row
-    T* dss = reinterpret_cast<T*>(dpf);
-    float* lse = reinterpret_cast<float*>(smem + SM::off_sc);
-    float* delta = lse + kTile;
-    unsigned char* q_ok = reinterpret_cast<unsigned char*>(delta + kTile);
-    unsigned char* k_ok = q_ok + kTile;
-    float* stage = reinterpret_cast<float*>(smem + SM::off_stage);
-    BwdSlot* qtab = reinterpret_cast<BwdSlot*>(smem + SM::bytes_no_tab);
-    BwdSlot* ktab = qtab + a.gq.bs;
+    unsigned char* q_s = smem;                 // Q rows, later the staged dQ
+    unsigned char* do_s = q_s + kTB;
+    unsigned char* k_s = do_s + kTB;           // [2]
+    unsigned char* v_s = k_s + 2 * kTB;        // [2]
+    unsigned char* k_ok = v_s + 2 * kTB;       // [2][64] presence of the keys of a tile
+    mm::SlotEntry* qtab = reinterpret_cast<mm::SlotEntry*>(k_ok + 2 * kTile);
+    mm::SlotEntry* ktab = qtab + a.gq.bs;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tiles_q = a.gq.bs / kTile, tiles_k = a.gk.bs / kTile;
     const int qb = blockIdx.x / tiles_q, qsub = blockIdx.x % tiles_q;
     const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-    fill_slot_table(qtab, a.gq, tid);
-    fill_slot_table(ktab, a.gk, tid);
+    fill_slots(qtab, a.gq, tid);
+    fill_slots(ktab, a.gk, tid);
     __syncthreads();
 
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
@@ -408,90 +294,116 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(const __grid_consta
     const T* doh = reinterpret_cast<const T*>(a.dout.data) + (long long)b * a.dout.sb + (long long)h * a.dout.sh;
     T* dqh = reinterpret_cast<T*>(const_cast<void*>(a.dq.data)) + (long long)b * a.dq.sb + (long long)h * a.dq.sh;
 
-    load_rows<T, D, SM::LD>(qs, q_ok, qh, a.q.ss, a.gq, qtab, qb, qsub * kTile, tid);
-    load_rows<T, D, SM::LD>(dos, nullptr, doh, a.dout.ss, a.gq, qtab, qb, qsub * kTile, tid);
-    load_row_scalars(lse, a.lse + (long long)bh * Sq, a.gq, qtab, qb, qsub * kTile, tid);
-    load_row_scalars(delta, a.delta + (long long)bh * Sq, a.gq, qtab, qb, qsub * kTile, tid);
-
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[D / 16];  // dQ rows 16 * warp .. of this tile
-#pragma unroll
-    for (int n = 0; n < D / 16; ++n) wmma::fill_fragment(acc[n], 0.f);
-
     const int32_t* list = a.idx + ((long long)bh * a.gq.nblk + qb) * a.cap;
     const int n_list = min(max(a.cnt[(long long)bh * a.gq.nblk + qb], 0), a.cap);
-    // tiles of the listed key blocks, one after the other; tile it + 1 is fetched into registers while tile it is
-    // computed on.  An entry outside [0, Nk) (flagged by the mark kernel) is a tile of absent keys.
     const int n_tiles = n_list * tiles_k;
-    RowRegs2<D> regs;
-    auto fetch = [&](int it) {
-        const int kb = list[it / tiles_k];
-        fetch_rows2<T, D>(regs, kh, a.k.ss, vh, a.v.ss, a.gk, ktab, kb, (it % tiles_k) * kTile, (unsigned)kb < (unsigned)a.gk.nblk, tid);
+
+    // presence of the keys of a tile (all absent for a list entry outside [0, Nk), which the mark kernel has flagged)
+    auto key_flags = [&](unsigned char* dst, int blk, int slot0) {
+        const bool blk_ok = (unsigned)blk < (unsigned)a.gk.nblk;
+        int bt, bhh, bw;
+        block_coords(a.gk, blk_ok ? blk : 0, bt, bhh, bw);
+        const int t0 = bt * a.gk.ct, h0 = bhh * a.gk.ch, w0 = bw * a.gk.cw;
+        for (int r = tid; r < kTile; r += kBwdThreads)
+            dst[r] = (blk_ok && (!a.gk.ragged || mm::slot_present(a.gk, ktab[slot0 + r].packed, t0, h0, w0))) ? 1 : 0;
     };
-    if (n_tiles > 0) fetch(0);
-    for (int it = 0; it < n_tiles; ++it) {
-        __syncthreads();  // the previous tile's K and V have been read by every warp
-        commit_rows2<T, D, SM::LD>(regs, ks, vs, k_ok, tid);
-        __syncthreads();
-        if (it + 1 < n_tiles) fetch(it + 1);
-        {
-            const int row0 = 16 * warp;
-            warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
-            warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(dpf + row0 * SM::LDF, dos + row0 * SM::LD, vs);
-            __syncwarp();
-            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
-            __syncwarp();
-            // dQ[16 x D] += dS[16 x 64] * K[64 x D]
+
+    mm::load_tile<T, D, kTile, kBwdThreads>(q_s, qh, a.q.ss, a.gq, qtab, qb, qsub * kTile, tid);
+    mm::load_tile<T, D, kTile, kBwdThreads>(do_s, doh, a.dout.ss, a.gq, qtab, qb, qsub * kTile, tid);
+    mm::cp_async_commit();
+    if (n_tiles > 0) {
+        mm::load_tile<T, D, kTile, kBwdThreads>(k_s, kh, a.k.ss, a.gk, ktab, list[0], 0, tid);
+        mm::load_tile<T, D, kTile, kBwdThreads>(v_s, vh, a.v.ss, a.gk, ktab, list[0], 0, tid);
+        key_flags(k_ok, list[0], 0);
+    }
+    mm::cp_async_commit();
+    mm::cp_async_wait<1>();
+    __syncthreads();
+
+    uint32_t qf[D / 16][4], dof[D / 16][4];
+    load_a_frags<D>(qf, mm::smem_u32(q_s), warp, lane);
+    load_a_frags<D>(dof, mm::smem_u32(do_s), warp, lane);
+
+    // per-row constants of this thread's two rows
+    float lse2[2], dl[2];
+    bool rok[2];
+    {
+        int bt, bhh, bw;
+        block_coords(a.gq, qb, bt, bhh, bw);
+        const int t0 = bt * a.gq.ct, h0 = bhh * a.gq.ch, w0 = bw * a.gq.cw;
+        const long long origin = ((long long)t0 * a.gq.H + h0) * a.gq.W + w0;
 #pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, W, wmma::row_major> fa;
-                wmma::load_matrix_sync(fa, reinterpret_cast<const W*>(dss) + row0 * SM::LDP + kk * 16, SM::LDP);
-#pragma unroll
-                for (int n = 0; n < D / 16; ++n) {
-                    wmma::fragment<wmma::matrix_b, 16, 16, 16, W, wmma::row_major> fb;
-                    wmma::load_matrix_sync(fb, reinterpret_cast<const W*>(ks) + kk * 16 * SM::LD + n * 16, SM::LD);
-                    wmma::mma_sync(acc[n], fa, fb, acc[n]);
-                }
-            }
+        for (int e = 0; e < 2; ++e) {
+            const mm::SlotEntry se = qtab[qsub * kTile + warp * 16 + (lane >> 2) + 8 * e];
+            rok[e] = !a.gq.ragged || mm::slot_present(a.gq, se.packed, t0, h0, w0);
+            lse2[e] = rok[e] ? a.lse[(long long)bh * Sq + origin + se.off] * 1.4426950408889634f : 0.f;
+            dl[e] = rok[e] ? a.delta[(long long)bh * Sq + origin + se.off] : 0.f;
         }
     }
-    // every warp stages its 16 rows (its own region of the staging tile, which lies over the K and V tiles), then the
-    // CTA writes the rows that exist
-    __syncthreads();
+    const float scale2 = a.sm_scale * 1.4426950408889634f;
+
+    float dq[D / 8][4];
 #pragma unroll
-    for (int n = 0; n < D / 16; ++n) wmma::store_matrix_sync(stage + 16 * warp * SM::LDO + n * 16, acc[n], SM::LDO, wmma::mem_row_major);
+    for (int i = 0; i < D / 8; ++i) dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_tiles) {
+            const int nblk = list[(it + 1) / tiles_k], nsub = (it + 1) % tiles_k;
+            mm::load_tile<T, D, kTile, kBwdThreads>(k_s + (buf ^ 1) * kTB, kh, a.k.ss, a.gk, ktab, nblk, nsub * kTile, tid);
+            mm::load_tile<T, D, kTile, kBwdThreads>(v_s + (buf ^ 1) * kTB, vh, a.v.ss, a.gk, ktab, nblk, nsub * kTile, tid);
+            key_flags(k_ok + (buf ^ 1) * kTile, nblk, nsub * kTile);
+        }
+        mm::cp_async_commit();
+        mm::cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kt = mm::smem_u32(k_s) + buf * kTB, vt = mm::smem_u32(v_s) + buf * kTB;
+        const unsigned char* kok = k_ok + buf * kTile;
+
+        float s[8][4], dp[8][4];
+        mma_abt<T, D>(s, qf, kt, lane);
+        mma_abt<T, D>(dp, dof, vt, lane);
+        // dS in place of dP: ds = p * (dp - delta) * scale, p = 2^(s * scale2 - lse2); absent keys and rows give 0
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = nt * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+                const bool ok = rok[r] && kok[col];
+                const float p = ok ? mm::ex2(fmaf(s[nt][e], scale2, -lse2[r])) : 0.f;
+                dp[nt][e] = p * (dp[nt][e] - dl[r]) * a.sm_scale;
+            }
+        }
+        mma_xb<T, D>(dq, dp, kt, lane);  // dQ += dS K
+        __syncthreads();
+    }
+    mm::cp_async_wait<0>();
     __syncthreads();
-    store_rows<T, D, SM::LDO>(stage, dqh, a.dq.ss, a.gq, qtab, qb, qsub * kTile, tid);
+    stage_rows<T, D>(q_s, dq, warp, lane);
+    __syncthreads();
+    write_rows<T, D>(q_s, dqh, a.dq.ss, a.gq, qtab, qb, qsub * kTile, tid);
 }
 
-// ------------------------------------------------------------------------------------------ dK, dV
-
 template <typename T, int D>
-__global__ void __launch_bounds__(kBwdThreads) bwd_dkdv_kernel(const __grid_constant__ BwdArgs a) {
-    using SM = BwdSmem<T, D>;
-    using W = typename Wm<T>::type;
+__global__ void __launch_bounds__(kBwdThreads, 2) bwd_dkdv_mma_kernel(const __grid_constant__ BwdArgs a) {
+    constexpr int kTB = kTile * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
-    T* ks = reinterpret_cast<T*>(smem + SM::off_a);
-    T* vs = reinterpret_cast<T*>(smem + SM::off_b);
-    T* qs = reinterpret_cast<T*>(smem + SM::off_c);
-    T* dos = reinterpret_cast<T*>(smem + SM::off_d);
-    float* sf = reinterpret_cast<float*>(smem + SM::off_sf);
-    float* dpf = reinterpret_cast<float*>(smem + SM::off_dpf);
-    T* ps = reinterpret_cast<T*>(sf);     // P and dS replace S and dP row by row
-    T* dss = reinterpret_cast<T*>(dpf);
-    float* lse = reinterpret_cast<float*>(smem + SM::off_sc);
-    float* delta = lse + kTile;
-    unsigned char* q_ok = reinterpret_cast<unsigned char*>(delta + kTile);
-    unsigned char* k_ok = q_ok + kTile;
-    float* stage = reinterpret_cast<float*>(smem + SM::off_stage);
-    BwdSlot* qtab = reinterpret_cast<BwdSlot*>(smem + SM::bytes_no_tab);
-    BwdSlot* ktab = qtab + a.gq.bs;
+    unsigned char* k_s = smem;                 // K rows of this tile, later the staged dK
+    unsigned char* v_s = k_s + kTB;            // V rows, later the staged dV
+    unsigned char* q_s = v_s + kTB;            // [2]
+    unsigned char* do_s = q_s + 2 * kTB;       // [2]
+    float* lse2 = reinterpret_cast<float*>(do_s + 2 * kTB);  // [2][64]
+    float* delta = lse2 + 2 * kTile;                         // [2][64]
+    unsigned char* q_ok = reinterpret_cast<unsigned char*>(delta + 2 * kTile);  // [2][64]
+    mm::SlotEntry* qtab = reinterpret_cast<mm::SlotEntry*>(q_ok + 2 * kTile);
+    mm::SlotEntry* ktab = qtab + a.gq.bs;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tiles_q = a.gq.bs / kTile, tiles_k = a.gk.bs / kTile;
     const int kb = blockIdx.x / tiles_k, ksub = blockIdx.x % tiles_k;
     const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-    fill_slot_table(qtab, a.gq, tid);
-    fill_slot_table(ktab, a.gk, tid);
+    fill_slots(qtab, a.gq, tid);
+    fill_slots(ktab, a.gk, tid);
     __syncthreads();
 
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
@@ -501,65 +413,102 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dkdv_kernel(const __grid_cons
     const T* doh = reinterpret_cast<const T*>(a.dout.data) + (long long)b * a.dout.sb + (long long)h * a.dout.sh;
     T* dkh = reinterpret_cast<T*>(const_cast<void*>(a.dk.data)) + (long long)b * a.dk.sb + (long long)h * a.dk.sh;
     T* dvh = reinterpret_cast<T*>(const_cast<void*>(a.dv.data)) + (long long)b * a.dv.sb + (long long)h * a.dv.sh;
+    const float* lse_h = a.lse + (long long)bh * Sq;
+    const float* delta_h = a.delta + (long long)bh * Sq;
 
-    load_rows<T, D, SM::LD>(ks, k_ok, kh, a.k.ss, a.gk, ktab, kb, ksub * kTile, tid);
-    load_rows<T, D, SM::LD>(vs, nullptr, vh, a.v.ss, a.gk, ktab, kb, ksub * kTile, tid);
-
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc_k[D / 16], acc_v[D / 16];  // key rows 16 * warp .. of this tile
-#pragma unroll
-    for (int n = 0; n < D / 16; ++n) {
-        wmma::fill_fragment(acc_k[n], 0.f);
-        wmma::fill_fragment(acc_v[n], 0.f);
-    }
     const int32_t* tl = a.tidx + (long long)bh * a.gq.nblk * a.cap;
     const int t_lo = a.toff[(long long)bh * (a.gk.nblk + 1) + kb], t_hi = a.toff[(long long)bh * (a.gk.nblk + 1) + kb + 1];
-    for (int t = t_lo; t < t_hi; ++t) {
-        const int qb = tl[t];
-        for (int qsub = 0; qsub < tiles_q; ++qsub) {
-            __syncthreads();  // the previous tile's Q, dO, P and dS have been read by every warp
-            load_rows<T, D, SM::LD>(qs, q_ok, qh, a.q.ss, a.gq, qtab, qb, qsub * kTile, tid);
-            load_rows<T, D, SM::LD>(dos, nullptr, doh, a.dout.ss, a.gq, qtab, qb, qsub * kTile, tid);
-            load_row_scalars(lse, a.lse + (long long)bh * Sq, a.gq, qtab, qb, qsub * kTile, tid);
-            load_row_scalars(delta, a.delta + (long long)bh * Sq, a.gq, qtab, qb, qsub * kTile, tid);
-            __syncthreads();
-            const int row0 = 16 * warp;  // query rows of this warp for S, dP, P, dS
-            warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(sf + row0 * SM::LDF, qs + row0 * SM::LD, ks);
-            warp_abt_16x64<T, D, SM::LD, SM::LD, SM::LDF>(dpf + row0 * SM::LDF, dos + row0 * SM::LD, vs);
-            __syncwarp();
-            warp_softmax_grad_rows<T, SM::LDF, SM::LDP>(sf, dpf, lse, delta, q_ok, k_ok, a.sm_scale, row0, lane);
-            __syncthreads();  // all 64 query rows of P and dS are needed by every warp now
-            // key rows 16 * warp ..:  dV += P^T dO,  dK += dS^T Q   (A = P^T: column-major view of the [q][k] tile)
+    const int n_tiles = (t_hi - t_lo) * tiles_q;
+
+    mm::load_tile<T, D, kTile, kBwdThreads>(k_s, kh, a.k.ss, a.gk, ktab, kb, ksub * kTile, tid);
+    mm::load_tile<T, D, kTile, kBwdThreads>(v_s, vh, a.v.ss, a.gk, ktab, kb, ksub * kTile, tid);
+    mm::cp_async_commit();
+    if (n_tiles > 0) {
+        const int qb0 = tl[t_lo];
+        mm::load_tile<T, D, kTile, kBwdThreads>(q_s, qh, a.q.ss, a.gq, qtab, qb0, 0, tid);
+        mm::load_tile<T, D, kTile, kBwdThreads>(do_s, doh, a.dout.ss, a.gq, qtab, qb0, 0, tid);
+        load_q_scalars(lse2, delta, q_ok, lse_h, delta_h, a.gq, qtab, qb0, 0, tid);
+    }
+    mm::cp_async_commit();
+    mm::cp_async_wait<1>();
+    __syncthreads();
+
+    // presence of this thread's two key rows
+    bool kok[2];
+    {
+        int bt, bhh, bw;
+        block_coords(a.gk, kb, bt, bhh, bw);
+        const int t0 = bt * a.gk.ct, h0 = bhh * a.gk.ch, w0 = bw * a.gk.cw;
 #pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, W, wmma::col_major> fp, fs;
-                wmma::load_matrix_sync(fp, reinterpret_cast<const W*>(ps) + kk * 16 * SM::LDP + row0, SM::LDP);
-                wmma::load_matrix_sync(fs, reinterpret_cast<const W*>(dss) + kk * 16 * SM::LDP + row0, SM::LDP);
+        for (int e = 0; e < 2; ++e)
+            kok[e] = !a.gk.ragged || mm::slot_present(a.gk, ktab[ksub * kTile + warp * 16 + (lane >> 2) + 8 * e].packed, t0, h0, w0);
+    }
+    const float scale2 = a.sm_scale * 1.4426950408889634f;
+
+    float dk[D / 8][4], dv[D / 8][4];
 #pragma unroll
-                for (int n = 0; n < D / 16; ++n) {
-                    wmma::fragment<wmma::matrix_b, 16, 16, 16, W, wmma::row_major> fb;
-                    wmma::load_matrix_sync(fb, reinterpret_cast<const W*>(dos) + kk * 16 * SM::LD + n * 16, SM::LD);
-                    wmma::mma_sync(acc_v[n], fp, fb, acc_v[n]);
-                    wmma::load_matrix_sync(fb, reinterpret_cast<const W*>(qs) + kk * 16 * SM::LD + n * 16, SM::LD);
-                    wmma::mma_sync(acc_k[n], fs, fb, acc_k[n]);
-                }
+    for (int i = 0; i < D / 8; ++i) {
+        dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f;
+        dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f;
+    }
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_tiles) {
+            const int nqb = tl[t_lo + (it + 1) / tiles_q], nsub = (it + 1) % tiles_q;
+            mm::load_tile<T, D, kTile, kBwdThreads>(q_s + (buf ^ 1) * kTB, qh, a.q.ss, a.gq, qtab, nqb, nsub * kTile, tid);
+            mm::load_tile<T, D, kTile, kBwdThreads>(do_s + (buf ^ 1) * kTB, doh, a.dout.ss, a.gq, qtab, nqb, nsub * kTile, tid);
+            load_q_scalars(lse2 + (buf ^ 1) * kTile, delta + (buf ^ 1) * kTile, q_ok + (buf ^ 1) * kTile, lse_h, delta_h, a.gq, qtab, nqb,
+                           nsub * kTile, tid);
+        }
+        mm::cp_async_commit();
+        mm::cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t qt = mm::smem_u32(q_s) + buf * kTB, dot = mm::smem_u32(do_s) + buf * kTB;
+        const float* l2 = lse2 + buf * kTile;
+        const float* dl = delta + buf * kTile;
+        const unsigned char* qok = q_ok + buf * kTile;
+
+        // S^T = K Q^T for this warp's 16 keys: rows are keys, columns are the 64 query rows of the tile
+        uint32_t af[D / 16][4];
+        float st[8][4];
+        load_a_frags<D>(af, mm::smem_u32(k_s), warp, lane);
+        mma_abt<T, D>(st, af, qt, lane);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = nt * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
+                st[nt][e] = (kok[r] && qok[col]) ? mm::ex2(fmaf(st[nt][e], scale2, -l2[col])) : 0.f;  // P^T
             }
         }
+        mma_xb<T, D>(dv, st, dot, lane);  // dV += P^T dO
+        // dP^T = V dO^T, then dS^T = P^T o (dP^T - delta) * scale
+        float dpt[8][4];
+        load_a_frags<D>(af, mm::smem_u32(v_s), warp, lane);
+        mma_abt<T, D>(dpt, af, dot, lane);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = nt * 8 + 2 * (lane & 3) + (e & 1);
+                dpt[nt][e] = st[nt][e] * (dpt[nt][e] - dl[col]) * a.sm_scale;
+            }
+        }
+        mma_xb<T, D>(dk, dpt, qt, lane);  // dK += dS^T Q
+        __syncthreads();
     }
+    mm::cp_async_wait<0>();
     __syncthreads();
-#pragma unroll
-    for (int n = 0; n < D / 16; ++n) wmma::store_matrix_sync(stage + 16 * warp * SM::LDO + n * 16, acc_k[n], SM::LDO, wmma::mem_row_major);
+    stage_rows<T, D>(k_s, dk, warp, lane);
+    stage_rows<T, D>(v_s, dv, warp, lane);
     __syncthreads();
-    store_rows<T, D, SM::LDO>(stage, dkh, a.dk.ss, a.gk, ktab, kb, ksub * kTile, tid);
-    __syncthreads();
-#pragma unroll
-    for (int n = 0; n < D / 16; ++n) wmma::store_matrix_sync(stage + 16 * warp * SM::LDO + n * 16, acc_v[n], SM::LDO, wmma::mem_row_major);
-    __syncthreads();
-    store_rows<T, D, SM::LDO>(stage, dvh, a.dv.ss, a.gk, ktab, kb, ksub * kTile, tid);
+    write_rows<T, D>(k_s, dkh, a.dk.ss, a.gk, ktab, kb, ksub * kTile, tid);
+    write_rows<T, D>(v_s, dvh, a.dv.ss, a.gk, ktab, kb, ksub * kTile, tid);
 }
 
 template <typename T, int D>
 cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
-    using SM = BwdSmem<T, D>;
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
     const long long rows = (long long)a.B * a.H * Sq;
     const int BH = a.B * a.H;
@@ -582,17 +531,19 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    const size_t smem = SM::bytes_no_tab + (size_t)(a.gq.bs + a.gk.bs) * sizeof(BwdSlot);
-    if (smem > 227 * 1024) { *why = "block sizes too large for the backward's slot tables"; return cudaErrorInvalidValue; }
+    const size_t tabs = (size_t)(a.gq.bs + a.gk.bs) * sizeof(mm::SlotEntry);
+    const size_t smem_dq = 6 * (size_t)kTile * D * 2 + 2 * kTile + tabs;
+    const size_t smem_kv = 6 * (size_t)kTile * D * 2 + 2 * 2 * kTile * sizeof(float) + 2 * kTile + tabs;
+    if (smem_kv > 227 * 1024) { *why = "block sizes too large for the backward's slot tables"; return cudaErrorInvalidValue; }
     // the attribute is per device and per kernel; setting it on every call costs a microsecond and keeps this stateless
-    cudaError_t e = cudaFuncSetAttribute(bwd_dq_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(bwd_dq_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(bwd_dkdv_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(bwd_dkdv_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
     if (e != cudaSuccess) return e;
-    bwd_dq_kernel<T, D><<<dim3((unsigned)(a.gq.nblk * (a.gq.bs / kTile)), (unsigned)BH), kBwdThreads, smem, st>>>(a);
+    bwd_dq_mma_kernel<T, D><<<dim3((unsigned)(a.gq.nblk * (a.gq.bs / kTile)), (unsigned)BH), kBwdThreads, smem_dq, st>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    bwd_dkdv_kernel<T, D><<<dim3((unsigned)(a.gk.nblk * (a.gk.bs / kTile)), (unsigned)BH), kBwdThreads, smem, st>>>(a);
+    bwd_dkdv_mma_kernel<T, D><<<dim3((unsigned)(a.gk.nblk * (a.gk.bs / kTile)), (unsigned)BH), kBwdThreads, smem_kv, st>>>(a);
     return cudaGetLastError();
 }
 
