@@ -178,6 +178,71 @@ __device__ __forceinline__ void mma_abt(float (&acc)[8][4], const uint32_t (&af)
     }
 }
 
+// Two such products at once (S and dP of the same tile pair): two independent accumulation chains in one instruction
+// stream, which is what hides the ldmatrix -> mma latency with only two warps per scheduler.
+template <typename T, int D>
+__device__ __forceinline__ void mma_abt2(float (&acc0)[8][4], float (&acc1)[8][4], const uint32_t (&a0)[D / 16][4],
+                                         const uint32_t (&a1)[D / 16][4], uint32_t b0_tile, uint32_t b1_tile, int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        acc0[i][0] = acc0[i][1] = acc0[i][2] = acc0[i][3] = 0.f;
+        acc1[i][0] = acc1[i][1] = acc1[i][2] = acc1[i][3] = 0.f;
+    }
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            const int mid = lane >> 3;
+            const int row = np * 16 + (lane & 7) + (mid >> 1) * 8;
+            const int c = 2 * ks + (mid & 1);
+            const uint32_t off = row * (D * 2) + ((c ^ (row & 7)) << 4);
+            uint32_t bf0[4], bf1[4];
+            mm::ldsm_x4(bf0, b0_tile + off);
+            mm::ldsm_x4(bf1, b1_tile + off);
+            mm::mma16816<T>(acc0[2 * np], a0[ks], bf0[0], bf0[1]);
+            mm::mma16816<T>(acc1[2 * np], a1[ks], bf1[0], bf1[1]);
+            mm::mma16816<T>(acc0[2 * np + 1], a0[ks], bf0[2], bf0[3]);
+            mm::mma16816<T>(acc1[2 * np + 1], a1[ks], bf1[2], bf1[3]);
+        }
+    }
+}
+
+// The same with the A operands read from shared tiles step by step (this warp's 16 rows of a0_tile and a1_tile)
+template <typename T, int D>
+__device__ __forceinline__ void mma_abt2_sa(float (&acc0)[8][4], float (&acc1)[8][4], uint32_t a0_tile, uint32_t a1_tile, uint32_t b0_tile,
+                                            uint32_t b1_tile, int warp, int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        acc0[i][0] = acc0[i][1] = acc0[i][2] = acc0[i][3] = 0.f;
+        acc1[i][0] = acc1[i][1] = acc1[i][2] = acc1[i][3] = 0.f;
+    }
+    const int arow = warp * 16 + (lane & 15);
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t a0[4], a1[4];
+        {
+            const int c = 2 * ks + (lane >> 4);
+            const uint32_t off = arow * (D * 2) + ((c ^ (arow & 7)) << 4);
+            mm::ldsm_x4(a0, a0_tile + off);
+            mm::ldsm_x4(a1, a1_tile + off);
+        }
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            const int mid = lane >> 3;
+            const int row = np * 16 + (lane & 7) + (mid >> 1) * 8;
+            const int c = 2 * ks + (mid & 1);
+            const uint32_t off = row * (D * 2) + ((c ^ (row & 7)) << 4);
+            uint32_t bf0[4], bf1[4];
+            mm::ldsm_x4(bf0, b0_tile + off);
+            mm::ldsm_x4(bf1, b1_tile + off);
+            mm::mma16816<T>(acc0[2 * np], a0, bf0[0], bf0[1]);
+            mm::mma16816<T>(acc1[2 * np], a1, bf1[0], bf1[1]);
+            mm::mma16816<T>(acc0[2 * np + 1], a0, bf0[2], bf0[3]);
+            mm::mma16816<T>(acc1[2 * np + 1], a1, bf1[2], bf1[3]);
+        }
+    }
+}
+
 // A fragments (16 rows of this warp, all of D) of a swizzled [64][D] tile
 template <int D>
 __device__ __forceinline__ void load_a_frags(uint32_t (&af)[D / 16][4], uint32_t tile, int warp, int lane) {
@@ -208,6 +273,38 @@ __device__ __forceinline__ void mma_xb(float (&out)[D / 8][4], const float (&x)[
             mm::ldsm_x4_t(bf, b_tile + row * (D * 2) + ((c ^ (row & 7)) << 4));
             mm::mma16816<T>(out[2 * dp], pa, bf[0], bf[1]);
             mm::mma16816<T>(out[2 * dp + 1], pa, bf[2], bf[3]);
+        }
+    }
+}
+
+// Two of those at once: out0 += X0 * B0 and out1 += X1 * B1 (dV and dK of one tile pair)
+template <typename T, int D>
+__device__ __forceinline__ void mma_xb2(float (&out0)[D / 8][4], const float (&x0)[8][4], uint32_t b0_tile, float (&out1)[D / 8][4],
+                                        const float (&x1)[8][4], uint32_t b1_tile, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        uint32_t pa0[4], pa1[4];
+        pa0[0] = mm::pack2(T(), x0[2 * kk][0], x0[2 * kk][1]);
+        pa0[1] = mm::pack2(T(), x0[2 * kk][2], x0[2 * kk][3]);
+        pa0[2] = mm::pack2(T(), x0[2 * kk + 1][0], x0[2 * kk + 1][1]);
+        pa0[3] = mm::pack2(T(), x0[2 * kk + 1][2], x0[2 * kk + 1][3]);
+        pa1[0] = mm::pack2(T(), x1[2 * kk][0], x1[2 * kk][1]);
+        pa1[1] = mm::pack2(T(), x1[2 * kk][2], x1[2 * kk][3]);
+        pa1[2] = mm::pack2(T(), x1[2 * kk + 1][0], x1[2 * kk + 1][1]);
+        pa1[3] = mm::pack2(T(), x1[2 * kk + 1][2], x1[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            const int mid = lane >> 3;
+            const int row = kk * 16 + (lane & 7) + (mid & 1) * 8;
+            const int c = 2 * dp + (mid >> 1);
+            const uint32_t off = row * (D * 2) + ((c ^ (row & 7)) << 4);
+            uint32_t bf0[4], bf1[4];
+            mm::ldsm_x4_t(bf0, b0_tile + off);
+            mm::ldsm_x4_t(bf1, b1_tile + off);
+            mm::mma16816<T>(out0[2 * dp], pa0, bf0[0], bf0[1]);
+            mm::mma16816<T>(out1[2 * dp], pa1, bf1[0], bf1[1]);
+            mm::mma16816<T>(out0[2 * dp + 1], pa0, bf0[2], bf0[3]);
+            mm::mma16816<T>(out1[2 * dp + 1], pa1, bf1[2], bf1[3]);
         }
     }
 }
@@ -361,8 +458,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) bwd_dq_mma_kernel(const __grid
         const unsigned char* kok = k_ok + buf * kTile;
 
         float s[8][4], dp[8][4];
-        mma_abt<T, D>(s, qf, kt, lane);
-        mma_abt<T, D>(dp, dof, vt, lane);
+        mma_abt2<T, D>(s, dp, qf, dof, kt, vt, lane);
         // dS in place of dP: ds = p * (dp - delta) * scale, p = 2^(s * scale2 - lse2); absent keys and rows give 0
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -469,33 +565,20 @@ __global__ void __launch_bounds__(kBwdThreads, 2) bwd_dkdv_mma_kernel(const __gr
         const float* dl = delta + buf * kTile;
         const unsigned char* qok = q_ok + buf * kTile;
 
-        // S^T = K Q^T for this warp's 16 keys: rows are keys, columns are the 64 query rows of the tile
-        uint32_t af[D / 16][4];
-        float st[8][4];
-        load_a_frags<D>(af, mm::smem_u32(k_s), warp, lane);
-        mma_abt<T, D>(st, af, qt, lane);
+        // S^T = K Q^T and dP^T = V dO^T for this warp's 16 keys: rows are keys, columns are the 64 query rows of the tile
+        float st[8][4], dpt[8][4];
+        mma_abt2_sa<T, D>(st, dpt, mm::smem_u32(k_s), mm::smem_u32(v_s), qt, dot, warp, lane);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int col = nt * 8 + 2 * (lane & 3) + (e & 1), r = e >> 1;
-                st[nt][e] = (kok[r] && qok[col]) ? mm::ex2(fmaf(st[nt][e], scale2, -l2[col])) : 0.f;  // P^T
+                const float p = (kok[r] && qok[col]) ? mm::ex2(fmaf(st[nt][e], scale2, -l2[col])) : 0.f;  // P^T
+                st[nt][e] = p;
+                dpt[nt][e] = p * (dpt[nt][e] - dl[col]) * a.sm_scale;                                       // dS^T
             }
         }
-        mma_xb<T, D>(dv, st, dot, lane);  // dV += P^T dO
-        // dP^T = V dO^T, then dS^T = P^T o (dP^T - delta) * scale
-        float dpt[8][4];
-        load_a_frags<D>(af, mm::smem_u32(v_s), warp, lane);
-        mma_abt<T, D>(dpt, af, dot, lane);
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int col = nt * 8 + 2 * (lane & 3) + (e & 1);
-                dpt[nt][e] = st[nt][e] * (dpt[nt][e] - dl[col]) * a.sm_scale;
-            }
-        }
-        mma_xb<T, D>(dk, dpt, qt, lane);  // dK += dS^T Q
+        mma_xb2<T, D>(dv, st, dot, dk, dpt, qt, lane);  // dV += P^T dO,  dK += dS^T Q
         __syncthreads();
     }
     mm::cp_async_wait<0>();
