@@ -22,7 +22,7 @@
 // -> tcgen05.ld, exp2 online softmax in registers, P in the input dtype over the first half of the same buffer ->
 // O_g += P V (M128 N128 K64, A from TMEM).  The two warpgroups keep separate maxima, row sums and accumulators and
 // are merged once per work item.  K and V rings: six slots of one 64-key tile (16 KiB) each.  The finished O
-// (128 rows x 256 B) is staged in the two V slots of the item's last key block and leaves by TMA store.
+// (128 rows x 256 B) is staged in the V slots of the item's last two units and leaves by TMA store.
 //
 // Every wait on an mbarrier is bounded, as in attn_tc.cu.
 #include "tc_common.cuh"
@@ -36,15 +36,15 @@ using namespace tc;
 
 constexpr int kD = 128;
 constexpr int kQRows = 128;                        // tokens per query block: one M=128 tile
-constexpr int kBlk = 64;                           // keys per unit: half a 128-token key block
+constexpr int kBlk = 64;                           // keys per unit: a key block is 2, 4 or 8 units
 constexpr int kQTileBytes = kQRows * kD * 2;       // 32 KiB: the Q tile, and the staged O tile
 constexpr int kQHalfBytes = kQTileBytes / 2;       // one 64-column half of it: 128 rows x 128 B, 128B-swizzled
 constexpr int kTileBytes = kBlk * kD * 2;          // 16 KiB: one K or V tile of 64 keys
 constexpr int kHalfBytes = kTileBytes / 2;         // one 64-column half: 64 rows x 128 B
 constexpr int kSlotBytes = kTileBytes;             // a ring slot holds one unit's tile
 constexpr int kMaxUnits = 8;                       // units of 64 keys per key block: blocks of up to 512 tokens
-constexpr int kKSlots = 6, kVSlots = 6;            // even: the two units of a key block sit in a slot pair
-constexpr int kKLead = 4;                   // K blocks requested ahead of V: S runs two rounds of each warpgroup ahead
+constexpr int kKSlots = 6, kVSlots = 6;            // even, like the number of units of an item: the last two units sit in a slot pair
+constexpr int kKLead = 4;                          // K units requested ahead of V: S runs two rounds of each warpgroup ahead
 constexpr int kThreads = 384;
 // setmaxnreg per warpgroup: (208 + 208 + 88) * 128 threads <= the 64 K registers of the SM
 constexpr int kRegsSoftmax = 208, kRegsOther = 88;
@@ -88,7 +88,7 @@ struct TcParams {
     // (sub_t[u], sub_h[u], sub_w[u]) tokens into it.  lg_units = log2 of the units per block.
     int lg_units;
     int sub_t[kMaxUnits], sub_h[kMaxUnits], sub_w[kMaxUnits];
-    Geom gu;                // the key geometry with that axis of the block halved: slot order inside a unit
+    Geom gu;                // the key geometry with the block shape replaced by the unit's: slot order inside a unit
 };
 
 // ------------------------------------------------------------------------------------------ kernel
