@@ -15,7 +15,7 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB = os.path.join(CSRC, "liblcbsa.so")
-SOURCES = ["api.cu", "pool.cu", "select.cu", "select_gemm.cu", "select_cdf.cu", "attn_mma.cu", "attn_tc.cu", "attn_tc128.cu", "attn_bwd.cu", "noalloc.cu", "norm_rope.cu"]
+SOURCES = ["api.cu", "pool.cu", "select.cu", "select_gemm.cu", "select_cdf.cu", "attn_mma.cu", "attn_tc.cu", "attn_tc128.cu", "attn_bwd.cu", "attn_bwd_tc.cu", "noalloc.cu", "norm_rope.cu"]
 HEADERS = ["common.cuh", "select_common.cuh", "tc_common.cuh", "mma_common.cuh", os.path.join("..", "..", "include", "lcbsa.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

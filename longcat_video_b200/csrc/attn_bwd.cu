@@ -614,6 +614,7 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
+    if (attn_bwd_tc_supported(a)) return launch_attn_bwd_tc(a, st, why);
     const size_t tabs = (size_t)(a.gq.bs + a.gk.bs) * sizeof(mm::SlotEntry);
     const size_t smem_dq = 6 * (size_t)kTile * D * 2 + 2 * kTile + tabs;
     const size_t smem_kv = 6 * (size_t)kTile * D * 2 + 2 * 2 * kTile * sizeof(float) + 2 * kTile + tabs;
@@ -646,7 +647,8 @@ bool attn_bwd_supported(const BwdArgs& a, const char** why) {
 size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap) {
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     return up((size_t)BH * Sq * sizeof(float)) + up((size_t)BH * Nk * sizeof(int32_t)) + up((size_t)BH * (Nk + 1) * sizeof(int32_t)) +
-           up((size_t)BH * Nq * cap * sizeof(int32_t)) + up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t));
+           up((size_t)BH * Nq * cap * sizeof(int32_t)) + up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t)) +
+           up((size_t)BH * Sq * 2 * sizeof(float));
 }
 
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why) {
@@ -662,6 +664,8 @@ cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const c
     a.tidx = reinterpret_cast<int32_t*>(w);
     w += up((size_t)BH * a.gq.nblk * a.cap * sizeof(int32_t));
     a.bitmap = reinterpret_cast<uint32_t*>(w);
+    w += up((size_t)BH * a.gk.nblk * ((a.gq.nblk + 31) / 32) * sizeof(uint32_t));
+    a.stats = reinterpret_cast<float*>(w);
     if (a.dtype == LCBSA_BF16) return a.D == 128 ? run_bwd<__nv_bfloat16, 128>(a, st, why) : run_bwd<__nv_bfloat16, 64>(a, st, why);
     return a.D == 128 ? run_bwd<__half, 128>(a, st, why) : run_bwd<__half, 64>(a, st, why);
 }

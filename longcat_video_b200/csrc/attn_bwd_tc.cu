@@ -1,0 +1,507 @@
+// Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128 and 64-token query and key blocks on whole
+// grids: the dQ pass and the dK/dV pass of attn_bwd.cu (which keeps every other shape on warp-level MMAs), after its
+// delta kernel and its transposition of the block lists.  Stands in for the Triton kernels _attn_bwd_dq_bsa_varlen_align
+// and _attn_bwd_dkdv_bsa_varlen_align (longcat_video/block_sparse_attention/flash_attn_bsa_varlen_mask.py:289-945).
+//
+// Both passes are one kernel with the roles of the operands exchanged.  A CTA owns one 64-row tile pair (A1, A2) and walks
+// a list of tile pairs (B1, B2); per list entry
+//
+//   dQ pass   (CTA = query block i, list = its key blocks j):  A1 = Q_i  A2 = dO_i  B1 = K_j  B2 = V_j
+//       S  = A1 B1^T        dP  = A2 B2^T        dS  = P o (dP - delta_i) * scale        dQ_i += dS B1
+//   dK/dV pass (CTA = key block j, list = the query blocks i that selected it):  A1 = K_j  A2 = V_j  B1 = Q_i  B2 = dO_i
+//       S^T = A1 B1^T       dP^T = A2 B2^T       P^T, dS^T as above, transposed          dV_j += P^T B2   dK_j += dS^T B1
+//
+// with P = exp2(S * scale * log2(e) - lse * log2(e)).  S and dP are M64 N64 K128 MMAs with both operands in shared memory
+// (fp32 in TMEM); P and dS are written back to TMEM in the input dtype and are the A operands of the M64 N128 K64 MMAs
+// that accumulate the gradients in TMEM over the whole list, with the streamed tile as MN-major B operand: a tile is
+// loaded once (two 5-D TMA boxes of 64 columns, 128-byte swizzle) and serves as K-major operand of the first
+// contraction and as MN-major operand of the last.  Nothing is recomputed within a pass, nothing goes through shared
+// memory between the contractions, and no gradient is accumulated with atomics.
+//
+//   warps 0-3, 4-7 : two arithmetic warpgroups, list entries alternate between them (entry s -> warpgroup s & 1, which owns
+//                    S/dP buffer s & 1); a thread serves one TMEM lane = one row of the 64 x 64 tile (lanes 0-15 of
+//                    every 32-lane quadrant hold an M=64 accumulator)
+//   warp 8         : TMA producer: the CTA's own tiles once, then a ring of five (B1, B2) slots; in the dK/dV pass
+//                    also the query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the
+//                    same barrier (bwd_stats_kernel lays them out per block)
+//   warp 9         : issues every MMA, in list order, one elected lane
+//
+// Order of the MMAs.  dQ pass: SS(0) SS(1) then, per entry s: TS(s) SS(s + 2); dS has TMEM columns of its own, so the
+// S/dP buffer of entry s is free as soon as the warpgroup has read it.  dK/dV pass: TMEM is full (two 128-column
+// accumulators, two S/dP buffers), P^T and dS^T overwrite the buffer they were computed from, and the buffer is only
+// given to SS(s + 2) when TS(s) is known to have finished (a commit barrier): TS(s) TS(s+1) SS(s+2) SS(s+3).
+// Every mbarrier wait is bounded; when one runs out the CTA flags the status word, drains its copies, frees TMEM, returns.
+#include <cstdlib>
+#include <cstring>
+
+#include "tc_common.cuh"
+
+namespace lcbsa {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kD = 128;
+constexpr int kBlk = 64;
+constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB
+constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128 B, 128B-swizzled
+constexpr int kSlots = 5;                   // ring of (B1, B2) tile pairs
+constexpr int kSlotBytes = 2 * kTileBytes;
+constexpr int kStatsFloats = 2 * kBlk;      // per query block: lse * log2(e) [64], delta [64]
+constexpr int kStatsBytes = kStatsFloats * 4;
+constexpr int kThreads = 384;
+constexpr int kRegsMath = 208, kRegsOther = 88;  // setmaxnreg: (208 + 208 + 88) * 128 <= 64 K registers
+
+constexpr int kOffA = 0;                                   // A1, A2
+constexpr int kOffB = kOffA + 2 * kTileBytes;              // kSlots x (B1, B2)
+constexpr int kOffStats = kOffB + kSlots * kSlotBytes;     // kSlots x (lse2[64], delta[64])
+constexpr int kOffBar = kOffStats + kSlots * kStatsBytes;
+// barriers: a_full, full[kSlots], empty[kSlots], s_full[2], x_full[2], ts_done[2], acc_done
+constexpr int kNumBars = 1 + 2 * kSlots + 2 + 2 + 2 + 1;
+constexpr int kOffMisc = kOffBar + kNumBars * 8;           // abort flag, TMEM base
+constexpr int kSmemBytes = kOffMisc + 64;
+
+// TMEM columns.  dQ pass: dQ 0..127, S[buf] 128 + 128 buf, dP[buf] 192 + 128 buf, dS[buf] 384 + 32 buf (16-bit pairs).
+// dK/dV pass: dK 0..127, dV 128..255, S^T[buf] 256 + 128 buf (P^T over its first 32 columns), dP^T[buf] 320 + 128 buf
+// (dS^T over its first 32 columns).
+template <int kMode> struct Cols;
+template <> struct Cols<0> {
+    static constexpr uint32_t acc1 = 0, acc2 = 0;
+    __device__ static __forceinline__ uint32_t s(int buf) { return 128u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t dp(int buf) { return 192u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t xp(int buf) { return 384u + 32u * buf; }  // unused in this pass
+    __device__ static __forceinline__ uint32_t xd(int buf) { return 384u + 32u * buf; }
+};
+template <> struct Cols<1> {
+    static constexpr uint32_t acc1 = 0, acc2 = 128;
+    __device__ static __forceinline__ uint32_t s(int buf) { return 256u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t dp(int buf) { return 320u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t xp(int buf) { return 256u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t xd(int buf) { return 320u + 128u * buf; }
+};
+
+struct BwdTcParams {
+    CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
+    const int32_t* list;   // dQ pass: idx [BH][Nq][cap]; dK/dV pass: tidx [BH][Nq * cap]
+    const int32_t* cnt;    // dQ pass: [BH][Nq]
+    const int32_t* toff;   // dK/dV pass: [BH][Nk + 1]
+    const float* stats;    // [BH][Nq][2][64]
+    unsigned int* status;
+    void* out1;            // dQ pass: dq; dK/dV pass: dk
+    void* out2;            // dK/dV pass: dv
+    long long o1_sb, o1_sh, o1_ss, o2_sb, o2_sh, o2_ss;  // element strides
+    int cap, nq, nk, heads;
+    int merge_a1, merge_a2, merge_b1, merge_b2;  // how the batch axis is folded into each map
+    Geom ga, gb;           // grid of the CTA's own tiles, grid of the streamed tiles
+    float scale, scale2;   // sm_scale, sm_scale * log2(e)
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// the two 64-column boxes of one [64 tokens x 128] tile
+__device__ __forceinline__ void load_tile_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, const Coord& c) {
+    tma_load_5d(dst, tm, bar, 0, c.c1, c.c2, c.c3, c.c4);
+    tma_load_5d(dst + kHalfBytes, tm, bar, 64, c.c1, c.c2, c.c3, c.c4);
+}
+
+// lse * log2(e) and delta of every query row, laid out per 64-token block in slot order, so that a block's 128 values are
+// one contiguous 512-byte piece (whole grids only)
+__global__ void __launch_bounds__(256) bwd_stats_kernel(const float* lse, const float* delta, Geom g, long long Sq, long long total,
+                                                        float* stats) {
+    const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const int r = (int)(p % kBlk);
+    const long long rest = p / kBlk;
+    const int blk = (int)(rest % g.nblk);
+    const long long bh = rest / g.nblk;
+    int lt, lh, lw, bt, bhh, bw;
+    slot_coords(g, r, lt, lh, lw);
+    block_coords(g, blk, bt, bhh, bw);
+    const long long tok = ((long long)(bt * g.ct + lt) * g.H + (bhh * g.ch + lh)) * g.W + (bw * g.cw + lw);
+    float* dst = stats + (bh * g.nblk + blk) * kStatsFloats;
+    dst[r] = lse[bh * Sq + tok] * 1.4426950408889634f;
+    dst[kBlk + r] = delta[bh * Sq + tok];
+}
+
+// 32 columns of this thread's accumulator row -> 64 bytes of the row in global memory (input dtype)
+template <bool kBf16>
+__device__ __forceinline__ void store_row32(unsigned char* row_ptr, int col0, const uint32_t (&r)[32]) {
+#pragma unroll
+    for (int q8 = 0; q8 < 4; ++q8) {
+        uint4 pk;
+        pk.x = pack2(kBf16, __uint_as_float(r[q8 * 8 + 0]), __uint_as_float(r[q8 * 8 + 1]));
+        pk.y = pack2(kBf16, __uint_as_float(r[q8 * 8 + 2]), __uint_as_float(r[q8 * 8 + 3]));
+        pk.z = pack2(kBf16, __uint_as_float(r[q8 * 8 + 4]), __uint_as_float(r[q8 * 8 + 5]));
+        pk.w = pack2(kBf16, __uint_as_float(r[q8 * 8 + 6]), __uint_as_float(r[q8 * 8 + 7]));
+        *reinterpret_cast<uint4*>(row_ptr + (col0 + q8 * 8) * 2) = pk;
+    }
+}
+
+// kMode 0: dQ pass, 1: dK/dV pass.  Grid: (blocks of the CTA's own grid, batch * heads).
+template <bool kBf16, int kMode>
+__global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
+    using C = Cols<kMode>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + kOffBar;
+    const uint32_t bar_a_full = bar0;
+    auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (1 + kSlots + s); };
+    auto bar_s_full = [&](int buf) { return bar0 + 8u * (1 + 2 * kSlots + buf); };
+    auto bar_x_full = [&](int buf) { return bar0 + 8u * (3 + 2 * kSlots + buf); };
+    auto bar_ts_done = [&](int buf) { return bar0 + 8u * (5 + 2 * kSlots + buf); };
+    const uint32_t bar_acc_done = bar0 + 8u * (7 + 2 * kSlots);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
+    const Ctl ctl{abort_flag, P.status};
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // provably warp-uniform
+    const int own = blockIdx.x;                              // block of the CTA's own grid
+    const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
+
+    // this CTA's list
+    const int32_t* list;
+    int n;
+    if (kMode == 0) {
+        list = P.list + ((long long)bh * P.nq + own) * P.cap;
+        n = min(max(P.cnt[(long long)bh * P.nq + own], 0), P.cap);
+    } else {
+        const int lo = P.toff[(long long)bh * (P.nk + 1) + own], hi = P.toff[(long long)bh * (P.nk + 1) + own + 1];
+        list = P.list + (long long)bh * P.nq * P.cap + lo;
+        n = max(hi - lo, 0);
+    }
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(bar_a_full, 1);
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int buf = 0; buf < 2; ++buf) {
+            mbar_init(bar_s_full(buf), 1);
+            mbar_init(bar_x_full(buf), 4);  // one elected arrival per warp of the warpgroup
+            mbar_init(bar_ts_done(buf), 1);
+        }
+        mbar_init(bar_acc_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the tiles are 128B-swizzled, which ties their layout to address bits 7-9: refuse to run on an unaligned base
+        if (sbase & 1023u) {
+            *abort_flag = 1;
+            if (atomicCAS(P.status, 0u, 1u) == 0u) {
+                P.status[1] = blockIdx.x;
+                P.status[2] = sbase;
+                P.status[3] = 0;
+            }
+        }
+    }
+    if (warp == 9) {  // TMEM: all 512 columns, allocated and freed by the issuing warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    if (*abort_flag != 0) n = -1;  // nothing runs, nothing is written
+
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+        if (warp == 8 && n > 0) {
+            // ================================================================== TMA producer
+            if (lane == 0) {
+                mbar_arrive_tx(bar_a_full, 2 * kTileBytes);
+                load_tile_pair(sbase + kOffA, &P.tm_a1, bar_a_full, block_coord(P.ga, own, b, h, P.heads, P.merge_a1, P.ga.T));
+                load_tile_pair(sbase + kOffA + kTileBytes, &P.tm_a2, bar_a_full, block_coord(P.ga, own, b, h, P.heads, P.merge_a2, P.ga.T));
+            }
+            bool ok = true;
+            int win = 0, issued = 0;
+            for (int s = 0; s < n; ++s) {
+                if ((s & 31) == 0) win = (s + lane < n) ? list[s + lane] : 0;
+                const int blk = __shfl_sync(0xffffffffu, win, s & 31);
+                const int slot = s % kSlots;
+                ok = mbar_wait_warp(bar_empty(slot), ((s / kSlots) & 1) ^ 1, ctl, 210 + kMode, s);
+                if (!ok) break;
+                ++issued;
+                if (lane == 0) {
+                    mbar_arrive_tx(bar_full(slot), 2 * kTileBytes + (kMode == 1 ? kStatsBytes : 0));
+                    Coord c1, c2;
+                    if ((unsigned)blk < (unsigned)P.gb.nblk) {
+                        c1 = block_coord(P.gb, blk, b, h, P.heads, P.merge_b1, P.gb.T);
+                        c2 = block_coord(P.gb, blk, b, h, P.heads, P.merge_b2, P.gb.T);
+                    } else {
+                        // an entry outside the grid never becomes an address: the box is placed at w = W, wholly outside
+                        // the map, and TMA fills the tiles with zeros (the list transposition has flagged the call)
+                        c1 = Coord{P.gb.W, 0, 0, 0};
+                        c2 = c1;
+                    }
+                    const uint32_t dst = sbase + kOffB + slot * kSlotBytes;
+                    load_tile_pair(dst, &P.tm_b1, bar_full(slot), c1);
+                    load_tile_pair(dst + kTileBytes, &P.tm_b2, bar_full(slot), c2);
+                    if (kMode == 1)  // transposed lists only hold blocks of the grid
+                        bulk_load(sbase + kOffStats + slot * kStatsBytes, P.stats + ((long long)bh * P.nq + blk) * kStatsFloats, kStatsBytes,
+                                  bar_full(slot));
+                }
+                __syncwarp();
+            }
+            if (!ok && lane == 0) {
+                // drain: give the copies this warp issued a bounded time to land before the CTA exits
+                const long long t0 = clock64();
+                while (!mbar_try(bar_a_full, 0) && clock64() - t0 < 40000000ll) {
+                }
+                for (int r = issued > kSlots ? issued - kSlots : 0; r < issued; ++r)
+                    while (!mbar_try(bar_full(r % kSlots), (r / kSlots) & 1) && clock64() - t0 < 40000000ll) {
+                    }
+            }
+        } else if (warp == 9 && n > 0) {
+            // ================================================================== MMA issuer
+            const uint32_t idesc_ss = instr_desc(kBf16, 64, 64, 0), idesc_ts = instr_desc(kBf16, 64, 128, 1);
+            const uint64_t a1d = smem_desc(sbase + kOffA, 16, 1024), a2d = smem_desc(sbase + kOffA + kTileBytes, 16, 1024);
+            bool ok = mbar_wait_warp(bar_a_full, 0, ctl, 220 + kMode, 0);
+            // S (or S^T) and dP (or dP^T) of entry s into buffer s & 1
+            auto issue_ss = [&](int s) -> bool {
+                const int slot = s % kSlots, buf = s & 1;
+                if (!mbar_wait_warp(bar_full(slot), (s / kSlots) & 1, ctl, 222 + kMode, s)) return false;
+                tc_fence_after();
+                const uint32_t tile = sbase + kOffB + slot * kSlotBytes;
+                const uint64_t b1d = smem_desc(tile, 16, 1024), b2d = smem_desc(tile + kTileBytes, 16, 1024);
+#pragma unroll
+                for (int j = 0; j < kD / 16; ++j) {
+                    // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
+                    const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
+                    tc_mma(tmem + C::s(buf), a1d + off, b1d + off, idesc_ss, j > 0);
+                }
+#pragma unroll
+                for (int j = 0; j < kD / 16; ++j) {
+                    const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
+                    tc_mma(tmem + C::dp(buf), a2d + off, b2d + off, idesc_ss, j > 0);
+                }
+                tc_commit(bar_s_full(buf));
+                return true;
+            };
+            // the gradient MMAs of entry e: A from TMEM (8 columns per 16-row step), B the streamed tile, MN-major
+            // (64-column halves 8 KiB apart = LBO, 8-row groups 1 KiB apart = SBO, 16 rows = 2 KiB per step)
+            auto issue_ts = [&](int e) -> bool {
+                const int slot = e % kSlots, buf = e & 1;
+                if (!mbar_wait_warp(bar_x_full(buf), (e >> 1) & 1, ctl, 224 + kMode, e)) return false;
+                tc_fence_after();
+                const uint32_t tile = sbase + kOffB + slot * kSlotBytes;
+                const uint64_t b1m = smem_desc(tile, kHalfBytes, 1024), b2m = smem_desc(tile + kTileBytes, kHalfBytes, 1024);
+                if (kMode == 1) {
+#pragma unroll
+                    for (int j = 0; j < kBlk / 16; ++j)  // dV += P^T dO
+                        tc_mma_ts(tmem + C::acc2, tmem + C::xp(buf) + 8u * j, b2m + (uint64_t)((j * 2048) >> 4), idesc_ts, (e > 0 || j > 0) ? 1u : 0u);
+                }
+#pragma unroll
+                for (int j = 0; j < kBlk / 16; ++j)  // dQ += dS K, or dK += dS^T Q
+                    tc_mma_ts(tmem + C::acc1, tmem + C::xd(buf) + 8u * j, b1m + (uint64_t)((j * 2048) >> 4), idesc_ts, (e > 0 || j > 0) ? 1u : 0u);
+                tc_commit(bar_empty(slot));  // the streamed tiles are free once these MMAs have read them
+                if (kMode == 1) tc_commit(bar_ts_done(buf));
+                if (e == n - 1) tc_commit(bar_acc_done);
+                return true;
+            };
+            for (int s = 0; s < 2 && s < n && ok; ++s) ok = issue_ss(s);
+            if (kMode == 0) {
+                for (int i = 0; i < n && ok; ++i) {
+                    ok = issue_ts(i);
+                    if (ok && i + 2 < n) ok = issue_ss(i + 2);
+                }
+            } else {
+                for (int i = 0; i < n && ok; i += 2) {
+                    for (int e = i; e < i + 2 && e < n && ok; ++e) ok = issue_ts(e);
+                    for (int e = i + 2; e < i + 4 && e < n && ok; ++e) {
+                        // P^T and dS^T of entry e - 2 sit in the buffer this S^T and dP^T go to
+                        ok = mbar_wait_warp(bar_ts_done(e & 1), ((e - 2) >> 1) & 1, ctl, 226, e);
+                        if (ok) ok = issue_ss(e);
+                    }
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
+        // ================================================================== arithmetic warpgroups
+        const int wg = warp >> 2;  // takes entries wg, wg + 2, ... and owns S/dP buffer wg
+        const int wq = warp & 3;   // TMEM quadrant of this warp
+        const int row = wq * 16 + (lane & 15);  // row of the 64 x 64 tile (lanes 16-31 shadow lanes 0-15; their TMEM lanes are unused)
+        const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
+        const uint32_t t_s = tmem + C::s(wg) + t_lane, t_dp = tmem + C::dp(wg) + t_lane;
+        const uint32_t t_xp = tmem + C::xp(wg) + t_lane, t_xd = tmem + C::xd(wg) + t_lane;
+        // dQ pass: this thread's query row has one lse and one delta for the whole list
+        float my_l2 = 0.f, my_dl = 0.f;
+        if (kMode == 0 && n > 0) {
+            const float* st = P.stats + ((long long)bh * P.nq + own) * kStatsFloats;
+            my_l2 = st[row];
+            my_dl = st[kBlk + row];
+        }
+        bool ok = true;
+        unsigned r = 0;
+        for (int i = wg; i < n && ok; i += 2, ++r) {
+            const int slot = i % kSlots;
+            ok = mbar_wait_warp(bar_s_full(wg), r & 1, ctl, 230 + 2 * kMode + wg, i);
+            // the slot's lse and delta values came with its tiles (a completed phase answers at once)
+            if (ok && kMode == 1) ok = mbar_wait_warp(bar_full(slot), (i / kSlots) & 1, ctl, 234 + wg, i);
+            if (!ok) break;
+            tc_fence_after();
+            const float4* st4 = reinterpret_cast<const float4*>(smem + kOffStats + slot * kStatsBytes);
+            uint32_t xp[32], xd[32];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t sr[32], dr[32];
+                tc_ld32(t_s + 32 * half, sr);
+                tc_ld32(t_dp + 32 * half, dr);
+                tc_wait_ld();
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    float4 l2 = make_float4(my_l2, my_l2, my_l2, my_l2), dl = make_float4(my_dl, my_dl, my_dl, my_dl);
+                    if (kMode == 1) {  // columns are query rows: their values come from the slot
+                        l2 = st4[half * 8 + c4];
+                        dl = st4[16 + half * 8 + c4];
+                    }
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 0]), P.scale2, -l2.x));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 1]), P.scale2, -l2.y));
+                    const float p2 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 2]), P.scale2, -l2.z));
+                    const float p3 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 3]), P.scale2, -l2.w));
+                    const float g0 = p0 * (__uint_as_float(dr[4 * c4 + 0]) - dl.x) * P.scale;
+                    const float g1 = p1 * (__uint_as_float(dr[4 * c4 + 1]) - dl.y) * P.scale;
+                    const float g2 = p2 * (__uint_as_float(dr[4 * c4 + 2]) - dl.z) * P.scale;
+                    const float g3 = p3 * (__uint_as_float(dr[4 * c4 + 3]) - dl.w) * P.scale;
+                    if (kMode == 1) {
+                        xp[half * 16 + 2 * c4] = pack2(kBf16, p0, p1);
+                        xp[half * 16 + 2 * c4 + 1] = pack2(kBf16, p2, p3);
+                    }
+                    xd[half * 16 + 2 * c4] = pack2(kBf16, g0, g1);
+                    xd[half * 16 + 2 * c4 + 1] = pack2(kBf16, g2, g3);
+                }
+            }
+            // both halves of S and dP have been read (tc_wait_ld above) before anything is written over them
+            if (kMode == 1) tc_st32(t_xp, xp);
+            tc_st32(t_xd, xd);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive_elect(bar_x_full(wg));
+        }
+
+        // ---- the accumulated gradients of the CTA's 64 rows: TMEM -> registers -> global memory (rows in T,H,W order)
+        if (n >= 0) {
+            if (n > 0 && ok) {
+                ok = mbar_wait_warp(bar_acc_done, 0, ctl, 240 + kMode, n);
+                tc_fence_after();
+            }
+            if (ok) {
+                int lt, lh, lw, bt, bhh, bw;
+                slot_coords(P.ga, row, lt, lh, lw);
+                block_coords(P.ga, own, bt, bhh, bw);
+                const long long tok = ((long long)(bt * P.ga.ct + lt) * P.ga.H + (bhh * P.ga.ch + lh)) * P.ga.W + (bw * P.ga.cw + lw);
+                // dQ pass: warpgroup g stores columns 64 g .. 64 g + 63 of dQ; dK/dV pass: warpgroup 0 stores dK, 1 dV
+                const bool second = kMode == 1 && wg == 1;
+                unsigned char* base = static_cast<unsigned char*>(second ? P.out2 : P.out1);
+                const long long sb = second ? P.o2_sb : P.o1_sb, sh = second ? P.o2_sh : P.o1_sh, ss = second ? P.o2_ss : P.o1_ss;
+                unsigned char* row_ptr = base + ((long long)b * sb + (long long)h * sh + tok * ss) * 2;
+                const uint32_t t_acc = tmem + (second ? C::acc2 : C::acc1) + t_lane;
+                const int col_lo = kMode == 0 ? 64 * wg : 0, n_chunks = kMode == 0 ? 2 : 4;
+#pragma unroll 1
+                for (int ch = 0; ch < n_chunks; ++ch) {
+                    uint32_t acc[32];
+                    if (n > 0) {
+                        tc_ld32(t_acc + col_lo + 32 * ch, acc);
+                        tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = 0u;  // nothing selected this block: its gradient is zero
+                    }
+                    if (lane < 16) store_row32<kBf16>(row_ptr, col_lo + 32 * ch, acc);
+                }
+            }
+        }
+    }
+
+    // ---- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
+template <bool kBf16, int kMode>
+cudaError_t launch_pass(const BwdTcParams& P, unsigned own_blocks, unsigned BH, cudaStream_t st) {
+    // the attribute is per device and per kernel; setting it on every call costs a microsecond and keeps this stateless
+    cudaError_t e = cudaFuncSetAttribute(bwd_tc_kernel<kBf16, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    bwd_tc_kernel<kBf16, kMode><<<dim3(own_blocks, BH), kThreads, kSmemBytes, st>>>(P);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attn_bwd_tc_supported(const BwdArgs& a) {
+    const char* force = std::getenv("LCBSA_BWD_IMPL");  // "mma" keeps the warp-level kernels (for comparisons)
+    if (force && std::strcmp(force, "mma") == 0) return false;
+    if (a.dtype != LCBSA_BF16 && a.dtype != LCBSA_FP16) return false;
+    if (a.D != kD || a.gq.bs != kBlk || a.gk.bs != kBlk || a.gq.ragged || a.gk.ragged) return false;
+    if (a.gq.ct > 256 || a.gq.ch > 256 || a.gq.cw > 256 || a.gk.ct > 256 || a.gk.ch > 256 || a.gk.cw > 256) return false;
+    if (encode_fn() == nullptr) return false;
+    const View* vs[4] = {&a.q, &a.dout, &a.k, &a.v};
+    const Geom* gs[4] = {&a.gq, &a.gq, &a.gk, &a.gk};
+    for (int i = 0; i < 4; ++i) {
+        if (merge_mode(*vs[i], a.B, a.H, *gs[i]) < 0) return false;
+        if (vs[i]->ss * 2 >= (1ll << 40) || vs[i]->sh * 2 >= (1ll << 40)) return false;
+    }
+    return true;
+}
+
+// a.delta and the transposed lists (a.toff, a.tidx) are ready on the stream; a.stats is scratch of B*H*Sq*2 floats
+cudaError_t launch_attn_bwd_tc(const BwdArgs& a, cudaStream_t st, const char** why) {
+    const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
+    const long long BH = (long long)a.B * a.H;
+    {
+        const long long total = BH * Sq;  // whole grids: every block has its 64 rows
+        bwd_stats_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.lse, a.delta, a.gq, Sq, total, a.stats);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    const int mq = merge_mode(a.q, a.B, a.H, a.gq), mdo = merge_mode(a.dout, a.B, a.H, a.gq);
+    const int mk = merge_mode(a.k, a.B, a.H, a.gk), mv = merge_mode(a.v, a.B, a.H, a.gk);
+    CUtensorMap tq, tdo, tk, tv;
+    if (!make_map(&tq, a.dtype, a.q, a.B, a.H, a.gq, mq) || !make_map(&tdo, a.dtype, a.dout, a.B, a.H, a.gq, mdo) ||
+        !make_map(&tk, a.dtype, a.k, a.B, a.H, a.gk, mk) || !make_map(&tv, a.dtype, a.v, a.B, a.H, a.gk, mv)) {
+        *why = "cuTensorMapEncodeTiled rejected a tensor";
+        return cudaErrorInvalidValue;
+    }
+    BwdTcParams P;
+    std::memset(&P, 0, sizeof(P));
+    P.stats = a.stats;
+    P.status = a.status;
+    P.cap = a.cap; P.nq = a.gq.nblk; P.nk = a.gk.nblk; P.heads = a.H;
+    P.scale = a.sm_scale;
+    P.scale2 = a.sm_scale * 1.4426950408889634f;
+    const bool bf16 = a.dtype == LCBSA_BF16;
+
+    // dQ pass: own tiles Q_i, dO_i; streamed K_j, V_j
+    P.tm_a1 = tq; P.tm_a2 = tdo; P.tm_b1 = tk; P.tm_b2 = tv;
+    P.merge_a1 = mq; P.merge_a2 = mdo; P.merge_b1 = mk; P.merge_b2 = mv;
+    P.ga = a.gq; P.gb = a.gk;
+    P.list = a.idx; P.cnt = a.cnt; P.toff = nullptr;
+    P.out1 = const_cast<void*>(a.dq.data); P.o1_sb = a.dq.sb; P.o1_sh = a.dq.sh; P.o1_ss = a.dq.ss;
+    P.out2 = nullptr;
+    cudaError_t e = bf16 ? launch_pass<true, 0>(P, (unsigned)a.gq.nblk, (unsigned)BH, st) : launch_pass<false, 0>(P, (unsigned)a.gq.nblk, (unsigned)BH, st);
+    if (e != cudaSuccess) return e;
+
+    // dK/dV pass: own tiles K_j, V_j; streamed Q_i, dO_i
+    P.tm_a1 = tk; P.tm_a2 = tv; P.tm_b1 = tq; P.tm_b2 = tdo;
+    P.merge_a1 = mk; P.merge_a2 = mv; P.merge_b1 = mq; P.merge_b2 = mdo;
+    P.ga = a.gk; P.gb = a.gq;
+    P.list = a.tidx; P.cnt = nullptr; P.toff = a.toff;
+    P.out1 = const_cast<void*>(a.dk.data); P.o1_sb = a.dk.sb; P.o1_sh = a.dk.sh; P.o1_ss = a.dk.ss;
+    P.out2 = const_cast<void*>(a.dv.data); P.o2_sb = a.dv.sb; P.o2_sh = a.dv.sh; P.o2_ss = a.dv.ss;
+    return bf16 ? launch_pass<true, 1>(P, (unsigned)a.gk.nblk, (unsigned)BH, st) : launch_pass<false, 1>(P, (unsigned)a.gk.nblk, (unsigned)BH, st);
+}
+
+}  // namespace lcbsa
