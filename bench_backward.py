@@ -67,7 +67,7 @@ def main():
     line = {"bench": "bsa_backward", "workload": wl.name, "heads": args.heads, "block": list(wl.chunk), "selected_blocks": nsel,
             "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
             "ms_forward_attention": ms_fwd, "ms_backward": ms_bwd, "backward_tflops": 2.5 * fwd_flops / ms_bwd / 1e9,
-            "forward_tflops": fwd_flops / ms_fwd / 1e9, "gpu_launches_per_backward": 7}
+            "forward_tflops": fwd_flops / ms_fwd / 1e9, "gpu_launches_per_backward": 8 if (wl.head_dim == 128 and bs == 64 and os.environ.get("LCBSA_BWD_IMPL") != "mma") else 7}
     if not args.skip_gpu_reference:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_gpu as R

@@ -18,18 +18,21 @@
 // contraction and as MN-major operand of the last.  Nothing is recomputed within a pass, nothing goes through shared
 // memory between the contractions, and no gradient is accumulated with atomics.
 //
-//   warps 0-3, 4-7 : two arithmetic warpgroups, list entries alternate between them (entry s -> warpgroup s & 1, which owns
-//                    S/dP buffer s & 1); a thread serves one TMEM lane = one row of the 64 x 64 tile (lanes 0-15 of
-//                    every 32-lane quadrant hold an M=64 accumulator)
-//   warp 8         : TMA producer: the CTA's own tiles once, then a ring of five (B1, B2) slots; in the dK/dV pass
-//                    also the query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the
-//                    same barrier (bwd_stats_kernel lays them out per block)
-//   warp 9         : issues every MMA, in list order, one elected lane
+//   warps 0-7 : arithmetic.  A thread serves one TMEM lane = one row of the 64 x 64 tile (lanes 0-15 of every 32-lane
+//               quadrant hold an M=64 accumulator)
+//   warp 8    : TMA producer: the CTA's own tiles once, then a ring of five (B1, B2) slots; in the dK/dV pass also the
+//               query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the same barrier
+//               (bwd_stats_kernel lays them out per block)
+//   warp 9    : issues every MMA, one elected lane
 //
-// Order of the MMAs.  dQ pass: SS(0) SS(1) then, per entry s: TS(s) SS(s + 2); dS has TMEM columns of its own, so the
-// S/dP buffer of entry s is free as soon as the warpgroup has read it.  dK/dV pass: TMEM is full (two 128-column
-// accumulators, two S/dP buffers), P^T and dS^T overwrite the buffer they were computed from, and the buffer is only
-// given to SS(s + 2) when TS(s) is known to have finished (a commit barrier): TS(s) TS(s+1) SS(s+2) SS(s+3).
+// TMEM and the order of the MMAs.  P and dS (16-bit pairs) have columns of their own, twice, in both passes: the values
+// of entry s + 2 go where those of entry s were and are written after s_full(s + 2), a commit the issuer makes behind
+// TS(s), so no buffer is rewritten while an MMA may still read it.
+//   dQ pass (448 columns): S and dP have two buffers; warps 0-3 take the even entries, warps 4-7 the odd ones.
+//       SS(0) SS(1) | TS(0) SS(2) | TS(1) SS(3) | ...        TS(s) after x_full(s), which also frees S/dP of entry s
+//   dK/dV pass (512 columns, two accumulators): S^T and dP^T have ONE buffer; all eight warps work on every entry (warps
+//       0-3 columns 0-31, warps 4-7 columns 32-63) and release the buffer as soon as they hold it in registers (s_free).
+//       SS(0) | SS(1) TS(0) | SS(2) TS(1) | ...               SS(s+1) after s_free(s),  TS(s) after x_full(s)
 // Every mbarrier wait is bounded; when one runs out the CTA flags the status word, drains its copies, frees TMEM, returns.
 #include <cstdlib>
 #include <cstring>
@@ -57,14 +60,13 @@ constexpr int kOffA = 0;                                   // A1, A2
 constexpr int kOffB = kOffA + 2 * kTileBytes;              // kSlots x (B1, B2)
 constexpr int kOffStats = kOffB + kSlots * kSlotBytes;     // kSlots x (lse2[64], delta[64])
 constexpr int kOffBar = kOffStats + kSlots * kStatsBytes;
-// barriers: a_full, full[kSlots], empty[kSlots], s_full[2], x_full[2], ts_done[2], acc_done
-constexpr int kNumBars = 1 + 2 * kSlots + 2 + 2 + 2 + 1;
+// barriers: a_full, full[kSlots], empty[kSlots], s_full[2], s_free, x_full[2], acc_done
+constexpr int kNumBars = 1 + 2 * kSlots + 2 + 1 + 2 + 1;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;           // abort flag, TMEM base
 constexpr int kSmemBytes = kOffMisc + 64;
 
-// TMEM columns.  dQ pass: dQ 0..127, S[buf] 128 + 128 buf, dP[buf] 192 + 128 buf, dS[buf] 384 + 32 buf (16-bit pairs).
-// dK/dV pass: dK 0..127, dV 128..255, S^T[buf] 256 + 128 buf (P^T over its first 32 columns), dP^T[buf] 320 + 128 buf
-// (dS^T over its first 32 columns).
+// TMEM columns.  dQ pass: dQ 0..127, S[buf] 128 + 128 buf, dP[buf] 192 + 128 buf, dS[buf] 384 + 32 buf.
+// dK/dV pass: dK 0..127, dV 128..255, S^T 256..319, dP^T 320..383, P^T[buf] 384 + 64 buf, dS^T[buf] 416 + 64 buf.
 template <int kMode> struct Cols;
 template <> struct Cols<0> {
     static constexpr uint32_t acc1 = 0, acc2 = 0;
@@ -75,10 +77,10 @@ template <> struct Cols<0> {
 };
 template <> struct Cols<1> {
     static constexpr uint32_t acc1 = 0, acc2 = 128;
-    __device__ static __forceinline__ uint32_t s(int buf) { return 256u + 128u * buf; }
-    __device__ static __forceinline__ uint32_t dp(int buf) { return 320u + 128u * buf; }
-    __device__ static __forceinline__ uint32_t xp(int buf) { return 256u + 128u * buf; }
-    __device__ static __forceinline__ uint32_t xd(int buf) { return 320u + 128u * buf; }
+    __device__ static __forceinline__ uint32_t s(int) { return 256u; }
+    __device__ static __forceinline__ uint32_t dp(int) { return 320u; }
+    __device__ static __forceinline__ uint32_t xp(int buf) { return 384u + 64u * buf; }
+    __device__ static __forceinline__ uint32_t xd(int buf) { return 416u + 64u * buf; }
 };
 
 struct BwdTcParams {
@@ -152,10 +154,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
     const uint32_t bar_a_full = bar0;
     auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (1 + kSlots + s); };
-    auto bar_s_full = [&](int buf) { return bar0 + 8u * (1 + 2 * kSlots + buf); };
-    auto bar_x_full = [&](int buf) { return bar0 + 8u * (3 + 2 * kSlots + buf); };
-    auto bar_ts_done = [&](int buf) { return bar0 + 8u * (5 + 2 * kSlots + buf); };
-    const uint32_t bar_acc_done = bar0 + 8u * (7 + 2 * kSlots);
+    auto bar_s_full = [&](int buf) { return bar0 + 8u * (1 + 2 * kSlots + (kMode == 0 ? buf : 0)); };
+    const uint32_t bar_s_free = bar0 + 8u * (3 + 2 * kSlots);
+    auto bar_x_full = [&](int buf) { return bar0 + 8u * (4 + 2 * kSlots + buf); };
+    const uint32_t bar_acc_done = bar0 + 8u * (6 + 2 * kSlots);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffMisc + 8);
     const Ctl ctl{abort_flag, P.status};
@@ -184,11 +186,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             mbar_init(bar_full(s), 1);
             mbar_init(bar_empty(s), 1);
         }
-        for (int buf = 0; buf < 2; ++buf) {
-            mbar_init(bar_s_full(buf), 1);
-            mbar_init(bar_x_full(buf), 4);  // one elected arrival per warp of the warpgroup
-            mbar_init(bar_ts_done(buf), 1);
-        }
+        mbar_init(bar0 + 8u * (1 + 2 * kSlots), 1);  // s_full[0], s_full[1]
+        mbar_init(bar0 + 8u * (2 + 2 * kSlots), 1);
+        mbar_init(bar_s_free, 8);  // one elected arrival per arithmetic warp
+        mbar_init(bar_x_full(0), kMode == 0 ? 4 : 8);  // the warps that work on an entry
+        mbar_init(bar_x_full(1), kMode == 0 ? 4 : 8);
         mbar_init(bar_acc_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // the tiles are 128B-swizzled, which ties their layout to address bits 7-9: refuse to run on an unaligned base
@@ -264,10 +266,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             const uint32_t idesc_ss = instr_desc(kBf16, 64, 64, 0), idesc_ts = instr_desc(kBf16, 64, 128, 1);
             const uint64_t a1d = smem_desc(sbase + kOffA, 16, 1024), a2d = smem_desc(sbase + kOffA + kTileBytes, 16, 1024);
             bool ok = mbar_wait_warp(bar_a_full, 0, ctl, 220 + kMode, 0);
-            // S (or S^T) and dP (or dP^T) of entry s into buffer s & 1
+            // S (or S^T) and dP (or dP^T) of entry s
             auto issue_ss = [&](int s) -> bool {
                 const int slot = s % kSlots, buf = s & 1;
                 if (!mbar_wait_warp(bar_full(slot), (s / kSlots) & 1, ctl, 222 + kMode, s)) return false;
+                // dK/dV pass: the arithmetic warps hold S^T and dP^T of entry s - 1 in registers.  (dQ pass: the buffer
+                // was entry s - 2's, whose x_full the issuer has seen before TS(s - 2).)
+                if (kMode == 1 && s > 0 && !mbar_wait_warp(bar_s_free, (s - 1) & 1, ctl, 226, s)) return false;
                 tc_fence_after();
                 const uint32_t tile = sbase + kOffB + slot * kSlotBytes;
                 const uint64_t b1d = smem_desc(tile, 16, 1024), b2d = smem_desc(tile + kTileBytes, 16, 1024);
@@ -302,36 +307,30 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
                 for (int j = 0; j < kBlk / 16; ++j)  // dQ += dS K, or dK += dS^T Q
                     tc_mma_ts(tmem + C::acc1, tmem + C::xd(buf) + 8u * j, b1m + (uint64_t)((j * 2048) >> 4), idesc_ts, (e > 0 || j > 0) ? 1u : 0u);
                 tc_commit(bar_empty(slot));  // the streamed tiles are free once these MMAs have read them
-                if (kMode == 1) tc_commit(bar_ts_done(buf));
                 if (e == n - 1) tc_commit(bar_acc_done);
                 return true;
             };
-            for (int s = 0; s < 2 && s < n && ok; ++s) ok = issue_ss(s);
+            if (ok) ok = issue_ss(0);
             if (kMode == 0) {
+                if (ok && n > 1) ok = issue_ss(1);
                 for (int i = 0; i < n && ok; ++i) {
                     ok = issue_ts(i);
                     if (ok && i + 2 < n) ok = issue_ss(i + 2);
                 }
             } else {
-                for (int i = 0; i < n && ok; i += 2) {
-                    for (int e = i; e < i + 2 && e < n && ok; ++e) ok = issue_ts(e);
-                    for (int e = i + 2; e < i + 4 && e < n && ok; ++e) {
-                        // P^T and dS^T of entry e - 2 sit in the buffer this S^T and dP^T go to
-                        ok = mbar_wait_warp(bar_ts_done(e & 1), ((e - 2) >> 1) & 1, ctl, 226, e);
-                        if (ok) ok = issue_ss(e);
-                    }
+                for (int i = 0; i < n && ok; ++i) {
+                    if (i + 1 < n) ok = issue_ss(i + 1);
+                    if (ok) ok = issue_ts(i);
                 }
             }
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMath));
-        // ================================================================== arithmetic warpgroups
-        const int wg = warp >> 2;  // takes entries wg, wg + 2, ... and owns S/dP buffer wg
+        // ================================================================== arithmetic warps
+        const int wg = warp >> 2;  // dQ pass: entries wg, wg + 2, ...; dK/dV pass: columns 32 wg .. 32 wg + 31 of every entry
         const int wq = warp & 3;   // TMEM quadrant of this warp
         const int row = wq * 16 + (lane & 15);  // row of the 64 x 64 tile (lanes 16-31 shadow lanes 0-15; their TMEM lanes are unused)
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
-        const uint32_t t_s = tmem + C::s(wg) + t_lane, t_dp = tmem + C::dp(wg) + t_lane;
-        const uint32_t t_xp = tmem + C::xp(wg) + t_lane, t_xd = tmem + C::xd(wg) + t_lane;
         // dQ pass: this thread's query row has one lse and one delta for the whole list
         float my_l2 = 0.f, my_dl = 0.f;
         if (kMode == 0 && n > 0) {
@@ -339,52 +338,77 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             my_l2 = st[row];
             my_dl = st[kBlk + row];
         }
-        bool ok = true;
-        unsigned r = 0;
-        for (int i = wg; i < n && ok; i += 2, ++r) {
-            const int slot = i % kSlots;
-            ok = mbar_wait_warp(bar_s_full(wg), r & 1, ctl, 230 + 2 * kMode + wg, i);
-            // the slot's lse and delta values came with its tiles (a completed phase answers at once)
-            if (ok && kMode == 1) ok = mbar_wait_warp(bar_full(slot), (i / kSlots) & 1, ctl, 234 + wg, i);
-            if (!ok) break;
-            tc_fence_after();
-            const float4* st4 = reinterpret_cast<const float4*>(smem + kOffStats + slot * kStatsBytes);
-            uint32_t xp[32], xd[32];
+        // 32 columns of S and dP -> 16 columns of P and of dS in the input dtype.  st4: the slot's lse and delta values
+        // of those 32 columns (dK/dV pass, where columns are query rows)
+        auto columns32 = [&](const uint32_t (&sr)[32], const uint32_t (&dr)[32], const float4* l4, const float4* d4, uint32_t* xp, uint32_t* xd) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t sr[32], dr[32];
-                tc_ld32(t_s + 32 * half, sr);
-                tc_ld32(t_dp + 32 * half, dr);
-                tc_wait_ld();
-#pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    float4 l2 = make_float4(my_l2, my_l2, my_l2, my_l2), dl = make_float4(my_dl, my_dl, my_dl, my_dl);
-                    if (kMode == 1) {  // columns are query rows: their values come from the slot
-                        l2 = st4[half * 8 + c4];
-                        dl = st4[16 + half * 8 + c4];
-                    }
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 0]), P.scale2, -l2.x));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 1]), P.scale2, -l2.y));
-                    const float p2 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 2]), P.scale2, -l2.z));
-                    const float p3 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 3]), P.scale2, -l2.w));
-                    const float g0 = p0 * (__uint_as_float(dr[4 * c4 + 0]) - dl.x) * P.scale;
-                    const float g1 = p1 * (__uint_as_float(dr[4 * c4 + 1]) - dl.y) * P.scale;
-                    const float g2 = p2 * (__uint_as_float(dr[4 * c4 + 2]) - dl.z) * P.scale;
-                    const float g3 = p3 * (__uint_as_float(dr[4 * c4 + 3]) - dl.w) * P.scale;
-                    if (kMode == 1) {
-                        xp[half * 16 + 2 * c4] = pack2(kBf16, p0, p1);
-                        xp[half * 16 + 2 * c4 + 1] = pack2(kBf16, p2, p3);
-                    }
-                    xd[half * 16 + 2 * c4] = pack2(kBf16, g0, g1);
-                    xd[half * 16 + 2 * c4 + 1] = pack2(kBf16, g2, g3);
+            for (int c4 = 0; c4 < 8; ++c4) {
+                float4 l2 = make_float4(my_l2, my_l2, my_l2, my_l2), dl = make_float4(my_dl, my_dl, my_dl, my_dl);
+                if (kMode == 1) {
+                    l2 = l4[c4];
+                    dl = d4[c4];
                 }
+                const float p0 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 0]), P.scale2, -l2.x));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 1]), P.scale2, -l2.y));
+                const float p2 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 2]), P.scale2, -l2.z));
+                const float p3 = ex2(fmaf(__uint_as_float(sr[4 * c4 + 3]), P.scale2, -l2.w));
+                const float g0 = p0 * (__uint_as_float(dr[4 * c4 + 0]) - dl.x) * P.scale;
+                const float g1 = p1 * (__uint_as_float(dr[4 * c4 + 1]) - dl.y) * P.scale;
+                const float g2 = p2 * (__uint_as_float(dr[4 * c4 + 2]) - dl.z) * P.scale;
+                const float g3 = p3 * (__uint_as_float(dr[4 * c4 + 3]) - dl.w) * P.scale;
+                if (kMode == 1) {
+                    xp[2 * c4] = pack2(kBf16, p0, p1);
+                    xp[2 * c4 + 1] = pack2(kBf16, p2, p3);
+                }
+                xd[2 * c4] = pack2(kBf16, g0, g1);
+                xd[2 * c4 + 1] = pack2(kBf16, g2, g3);
             }
-            // both halves of S and dP have been read (tc_wait_ld above) before anything is written over them
-            if (kMode == 1) tc_st32(t_xp, xp);
-            tc_st32(t_xd, xd);
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive_elect(bar_x_full(wg));
+        };
+        bool ok = true;
+        if (kMode == 0) {
+            unsigned r = 0;
+            for (int i = wg; i < n && ok; i += 2, ++r) {  // buffer i & 1 = wg
+                ok = mbar_wait_warp(bar_s_full(wg), r & 1, ctl, 230 + wg, i);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t xd[32];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t sr[32], dr[32];
+                    tc_ld32(tmem + C::s(wg) + 32u * half + t_lane, sr);
+                    tc_ld32(tmem + C::dp(wg) + 32u * half + t_lane, dr);
+                    tc_wait_ld();
+                    columns32(sr, dr, nullptr, nullptr, nullptr, xd + 16 * half);
+                }
+                tc_st32(tmem + C::xd(wg) + t_lane, xd);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive_elect(bar_x_full(wg));
+            }
+        } else {
+            for (int i = 0; i < n && ok; ++i) {
+                const int slot = i % kSlots, buf = i & 1;
+                ok = mbar_wait_warp(bar_s_full(0), i & 1, ctl, 232 + wg, i);
+                // the slot's lse and delta values came with its tiles (a completed phase answers at once)
+                if (ok) ok = mbar_wait_warp(bar_full(slot), (i / kSlots) & 1, ctl, 234 + wg, i);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sr[32], dr[32];
+                tc_ld32(tmem + C::s(0) + 32u * wg + t_lane, sr);
+                tc_ld32(tmem + C::dp(0) + 32u * wg + t_lane, dr);
+                tc_wait_ld();
+                tc_fence_before();
+                mbar_arrive_elect(bar_s_free);  // S^T and dP^T may be overwritten by the next entry's
+                const float4* st4 = reinterpret_cast<const float4*>(smem + kOffStats + slot * kStatsBytes);
+                uint32_t xp[16], xd[16];
+                columns32(sr, dr, st4 + wg * 8, st4 + 16 + wg * 8, xp, xd);
+                // 32 columns of the tile are 16 columns of 16-bit pairs
+                tc_st16(tmem + C::xp(buf) + 16u * wg + t_lane, xp);
+                tc_st16(tmem + C::xd(buf) + 16u * wg + t_lane, xd);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive_elect(bar_x_full(buf));
+            }
         }
 
         // ---- the accumulated gradients of the CTA's 64 rows: TMEM -> registers -> global memory (rows in T,H,W order)
