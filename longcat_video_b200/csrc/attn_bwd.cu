@@ -19,7 +19,8 @@
 // Tiles are 64 x 64 whatever the block sizes (multiples of 64 tokens): a block of 128 or more tokens is a run of
 // 64-row tiles in slot order.  The contractions run on the tensor cores through warp-level mma (mma.sync m16n8k16 fed by
 // ldmatrix, fp32 accumulation); P and dS are rounded to the input dtype before they enter a contraction, as in the
-// forward.  This is the plain version of the backward: its roofline is the mma.sync rate, not tcgen05's.
+// forward.  The two passes of this file serve every supported shape; head_dim 128 with 64-token blocks on whole grids is
+// taken by the tcgen05 passes of attn_bwd_tc.cu instead (same delta, same transposed lists, same bits).
 #include "mma_common.cuh"
 
 namespace lcbsa {
