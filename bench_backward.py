@@ -64,10 +64,14 @@ def main():
     ms_bwd = _time(lambda: B.attn_bwd_bsa_varlen(do, q, k, v, o, lse, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk),
                    args.steps, args.warmup)
     L.check(L.lib().lcbsa_check_device_status())
+    # delta, four list-transposition kernels, two passes; the tcgen05 passes add the per-block lse/delta layout and, for
+    # blocks above 64 tokens, the rewriting of the lists per 64-token unit
+    tc = wl.head_dim == 128 and os.environ.get("LCBSA_BWD_IMPL") != "mma"
+    launches = 7 + (1 if tc else 0) + (1 if tc and bs > 64 else 0)
     line = {"bench": "bsa_backward", "workload": wl.name, "heads": args.heads, "block": list(wl.chunk), "selected_blocks": nsel,
             "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
             "ms_forward_attention": ms_fwd, "ms_backward": ms_bwd, "backward_tflops": 2.5 * fwd_flops / ms_bwd / 1e9,
-            "forward_tflops": fwd_flops / ms_fwd / 1e9, "gpu_launches_per_backward": 8 if (wl.head_dim == 128 and bs == 64 and os.environ.get("LCBSA_BWD_IMPL") != "mma") else 7}
+            "forward_tflops": fwd_flops / ms_fwd / 1e9, "gpu_launches_per_backward": launches}
     if not args.skip_gpu_reference:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_gpu as R

@@ -387,7 +387,7 @@ size_t lcbsa_attn_bwd_workspace_bytes(const LcbsaTensor* q, const LcbsaGrid* gq,
     for (int i = 0; i < 4; ++i)
         if (q->size[i] < 0) return 0;
     const lcbsa::Geom a = lcbsa::make_geom(*gq), b = lcbsa::make_geom(*gk);
-    return lcbsa::attn_bwd_workspace_bytes((long long)q->size[0] * q->size[1], (long long)a.T * a.H * a.W, a.nblk, b.nblk, cap);
+    return lcbsa::attn_bwd_workspace_bytes((long long)q->size[0] * q->size[1], a, b, cap);
 }
 
 int lcbsa_attn_bwd(const LcbsaTensor* q, const LcbsaTensor* k, const LcbsaTensor* v, const LcbsaTensor* out, const LcbsaTensor* dout,

@@ -19,8 +19,8 @@
 // Tiles are 64 x 64 whatever the block sizes (multiples of 64 tokens): a block of 128 or more tokens is a run of
 // 64-row tiles in slot order.  The contractions run on the tensor cores through warp-level mma (mma.sync m16n8k16 fed by
 // ldmatrix, fp32 accumulation); P and dS are rounded to the input dtype before they enter a contraction, as in the
-// forward.  The two passes of this file serve every supported shape; head_dim 128 with 64-token blocks on whole grids is
-// taken by the tcgen05 passes of attn_bwd_tc.cu instead (same delta, same transposed lists, same bits).
+// forward.  The two passes of this file serve every supported shape; head_dim 128 on whole grids is taken by the tcgen05
+// passes of attn_bwd_tc.cu instead (same delta kernel, same transposition; blocks above 64 tokens as 64-token units).
 #include "mma_common.cuh"
 
 namespace lcbsa {
@@ -591,6 +591,65 @@ __global__ void __launch_bounds__(kBwdThreads, 2) bwd_dkdv_mma_kernel(const __gr
     write_rows<T, D>(v_s, dvh, a.dv.ss, a.gk, ktab, kb, ksub * kTile, tid);
 }
 
+// ------------------------------------------------------------------------------------------ blocks as 64-token units
+//
+// The backward has no per-block state (no running maximum: lse is given), so a block of 128, 256 or 512 tokens is just
+// the union of 64-token pieces, and on whole grids those pieces are the blocks of a finer grid over the same tokens.
+// The tcgen05 passes work on 64-token blocks only; larger blocks reach them as that finer grid with the lists rewritten:
+// a query unit takes the list of its block, every selected key block becomes its units.
+
+struct UnitSplit {
+    Geom gu;         // the grid with the unit as block
+    int rt, rh, rw;  // units per block along t, h, w
+    int units;
+};
+
+// halves the block (w first, then h, then t) until 64 tokens are left; false when that cannot be done
+bool split_units64(const Geom& g, UnitSplit* out) {
+    if (g.ragged || g.bs < kTile) return false;
+    int ut = g.ct, uh = g.ch, uw = g.cw;
+    while (ut * uh * uw > kTile) {
+        if (uw % 2 == 0) uw /= 2;
+        else if (uh % 2 == 0) uh /= 2;
+        else if (ut % 2 == 0) ut /= 2;
+        else return false;
+    }
+    if (ut * uh * uw != kTile) return false;
+    LcbsaGrid lg;
+    lg.T = g.T; lg.H = g.H; lg.W = g.W;
+    lg.ct = ut; lg.ch = uh; lg.cw = uw;
+    out->gu = make_geom(lg);
+    out->rt = g.ct / ut; out->rh = g.ch / uh; out->rw = g.cw / uw;
+    out->units = out->rt * out->rh * out->rw;
+    return true;
+}
+
+// one thread per (batch*head, query unit, list position): the units of that key block, in (t, h, w) order
+__global__ void __launch_bounds__(256) bwd_expand_lists_kernel(const int32_t* idx, const int32_t* cnt, int cap, Geom gq, UnitSplit sq, Geom gk,
+                                                               UnitSplit sk, long long total, int32_t* idx_u, int32_t* cnt_u) {
+    const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const int e = (int)(p % cap);
+    const long long rest = p / cap;
+    const int qu = (int)(rest % sq.gu.nblk);
+    const long long bh = rest / sq.gu.nblk;
+    int ut, uh, uw;
+    block_coords(sq.gu, qu, ut, uh, uw);
+    const int q = ((ut / sq.rt) * gq.Nh + uh / sq.rh) * gq.Nw + uw / sq.rw;
+    const int n = min(max(cnt[bh * gq.nblk + q], 0), cap);
+    if (e == 0) cnt_u[bh * sq.gu.nblk + qu] = n * sk.units;
+    if (e >= n) return;
+    const int j = idx[(bh * gq.nblk + q) * cap + e];
+    int32_t* dst = idx_u + ((bh * sq.gu.nblk + qu) * cap + e) * sk.units;
+    const bool in_grid = (unsigned)j < (unsigned)gk.nblk;  // an entry outside the grid stays outside: flagged later, never an address
+    int bt, bhh, bw;
+    block_coords(gk, in_grid ? j : 0, bt, bhh, bw);
+    for (int u = 0; u < sk.units; ++u) {
+        const int sw = u % sk.rw, sh = (u / sk.rw) % sk.rh, stt = u / (sk.rw * sk.rh);
+        dst[u] = in_grid ? ((bt * sk.rt + stt) * sk.gu.Nh + (bhh * sk.rh + sh)) * sk.gu.Nw + (bw * sk.rw + sw) : -1;
+    }
+}
+
 template <typename T, int D>
 cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
@@ -603,19 +662,44 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
+    // head_dim 128 on whole grids: the tcgen05 passes, on the blocks themselves (64 tokens) or on their 64-token units
+    BwdArgs u = a;
+    bool use_tc = false;
+    if (D == 128) {
+        UnitSplit sq, sk;
+        if (split_units64(a.gq, &sq) && split_units64(a.gk, &sk)) {
+            u.gq = sq.gu;
+            u.gk = sk.gu;
+            const bool split = sq.units * sk.units > 1;
+            if (split) {
+                u.idx = a.idx_u;
+                u.cnt = a.cnt_u;
+                u.cap = a.cap * sk.units;
+            }
+            use_tc = attn_bwd_tc_supported(u);
+            if (use_tc && split) {
+                const long long total = (long long)BH * sq.gu.nblk * a.cap;
+                bwd_expand_lists_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, a.gq, sq, a.gk, sk, total, a.idx_u,
+                                                                                       a.cnt_u);
+                cudaError_t e = cudaGetLastError();
+                if (e != cudaSuccess) return e;
+            }
+        }
+    }
     {
-        const int Nq = a.gq.nblk, Nk = a.gk.nblk, Wq = (Nq + 31) / 32;
-        const long long rows_k = (long long)BH * Nk, entries = (long long)BH * Nq * a.cap;
-        cudaError_t e = cudaMemsetAsync(a.bitmap, 0, (size_t)rows_k * Wq * sizeof(uint32_t), st);
+        const BwdArgs& t = use_tc ? u : a;  // the lists that the dK/dV pass needs per key block
+        const int Nq = t.gq.nblk, Nk = t.gk.nblk, Wq = (Nq + 31) / 32;
+        const long long rows_k = (long long)BH * Nk, entries = (long long)BH * Nq * t.cap;
+        cudaError_t e = cudaMemsetAsync(t.bitmap, 0, (size_t)rows_k * Wq * sizeof(uint32_t), st);
         if (e != cudaSuccess) return e;
-        bwd_mark_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, Nq, Nk, Wq, entries, a.bitmap, a.status);
-        bwd_count_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, rows_k, a.tcnt);
-        bwd_scan_kernel<<<BH, 256, 0, st>>>(a.tcnt, Nk, a.toff);
-        bwd_emit_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, Nk, Nq, a.cap, rows_k, a.toff, a.tidx);
+        bwd_mark_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(t.idx, t.cnt, t.cap, Nq, Nk, Wq, entries, t.bitmap, t.status);
+        bwd_count_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(t.bitmap, Wq, rows_k, t.tcnt);
+        bwd_scan_kernel<<<BH, 256, 0, st>>>(t.tcnt, Nk, t.toff);
+        bwd_emit_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(t.bitmap, Wq, Nk, Nq, t.cap, rows_k, t.toff, t.tidx);
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    if (attn_bwd_tc_supported(a)) return launch_attn_bwd_tc(a, st, why);
+    if (use_tc) return launch_attn_bwd_tc(u, st, why);
     const size_t tabs = (size_t)(a.gq.bs + a.gk.bs) * sizeof(mm::SlotEntry);
     const size_t smem_dq = 6 * (size_t)kTile * D * 2 + 2 * kTile + tabs;
     const size_t smem_kv = 6 * (size_t)kTile * D * 2 + 2 * 2 * kTile * sizeof(float) + 2 * kTile + tabs;
@@ -645,28 +729,47 @@ bool attn_bwd_supported(const BwdArgs& a, const char** why) {
     return true;
 }
 
-size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap) {
+namespace {
+
+// The workspace is laid out for the finest form the lists can take: 64-token units (a block of 64 * U tokens counts U times).
+struct BwdLayout {
+    size_t delta, tcnt, toff, tidx, bitmap, stats, idx_u, cnt_u, total;
+};
+
+BwdLayout bwd_layout(long long BH, const Geom& gq, const Geom& gk, int cap) {
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-    return up((size_t)BH * Sq * sizeof(float)) + up((size_t)BH * Nk * sizeof(int32_t)) + up((size_t)BH * (Nk + 1) * sizeof(int32_t)) +
-           up((size_t)BH * Nq * cap * sizeof(int32_t)) + up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t)) +
-           up((size_t)BH * Sq * 2 * sizeof(float));
+    const size_t Sq = (size_t)gq.T * gq.H * gq.W;
+    const size_t Uq = gq.bs >= kTile ? gq.bs / kTile : 1, Uk = gk.bs >= kTile ? gk.bs / kTile : 1;
+    const size_t Nq = (size_t)gq.nblk * Uq, Nk = (size_t)gk.nblk * Uk, capu = (size_t)cap * Uk;
+    BwdLayout l;
+    size_t off = 0;
+    l.delta = off;  off += up((size_t)BH * Sq * sizeof(float));
+    l.tcnt = off;   off += up((size_t)BH * Nk * sizeof(int32_t));
+    l.toff = off;   off += up((size_t)BH * (Nk + 1) * sizeof(int32_t));
+    l.tidx = off;   off += up((size_t)BH * Nq * capu * sizeof(int32_t));
+    l.bitmap = off; off += up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t));
+    l.stats = off;  off += up((size_t)BH * Sq * 2 * sizeof(float));
+    l.idx_u = off;  off += up((size_t)BH * Nq * capu * sizeof(int32_t));
+    l.cnt_u = off;  off += up((size_t)BH * Nq * sizeof(int32_t));
+    l.total = off;
+    return l;
 }
 
+}  // namespace
+
+size_t attn_bwd_workspace_bytes(long long BH, const Geom& gq, const Geom& gk, int cap) { return bwd_layout(BH, gq, gk, cap).total; }
+
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why) {
-    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-    const long long BH = (long long)a.B * a.H, Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
+    const BwdLayout l = bwd_layout((long long)a.B * a.H, a.gq, a.gk, a.cap);
     unsigned char* w = static_cast<unsigned char*>(workspace);
-    a.delta = reinterpret_cast<float*>(w);
-    w += up((size_t)BH * Sq * sizeof(float));
-    a.tcnt = reinterpret_cast<int32_t*>(w);
-    w += up((size_t)BH * a.gk.nblk * sizeof(int32_t));
-    a.toff = reinterpret_cast<int32_t*>(w);
-    w += up((size_t)BH * (a.gk.nblk + 1) * sizeof(int32_t));
-    a.tidx = reinterpret_cast<int32_t*>(w);
-    w += up((size_t)BH * a.gq.nblk * a.cap * sizeof(int32_t));
-    a.bitmap = reinterpret_cast<uint32_t*>(w);
-    w += up((size_t)BH * a.gk.nblk * ((a.gq.nblk + 31) / 32) * sizeof(uint32_t));
-    a.stats = reinterpret_cast<float*>(w);
+    a.delta = reinterpret_cast<float*>(w + l.delta);
+    a.tcnt = reinterpret_cast<int32_t*>(w + l.tcnt);
+    a.toff = reinterpret_cast<int32_t*>(w + l.toff);
+    a.tidx = reinterpret_cast<int32_t*>(w + l.tidx);
+    a.bitmap = reinterpret_cast<uint32_t*>(w + l.bitmap);
+    a.stats = reinterpret_cast<float*>(w + l.stats);
+    a.idx_u = reinterpret_cast<int32_t*>(w + l.idx_u);
+    a.cnt_u = reinterpret_cast<int32_t*>(w + l.cnt_u);
     if (a.dtype == LCBSA_BF16) return a.D == 128 ? run_bwd<__nv_bfloat16, 128>(a, st, why) : run_bwd<__nv_bfloat16, 64>(a, st, why);
     return a.D == 128 ? run_bwd<__half, 128>(a, st, why) : run_bwd<__half, 64>(a, st, why);
 }

@@ -148,9 +148,11 @@ struct BwdArgs {
     int32_t* tidx;        // [B*H, Nq * cap] query blocks of key block j at toff[j] .. toff[j + 1], ascending
     uint32_t* bitmap;     // [B*H, Nk, ceil(Nq / 32)] bit i of row j: query block i selected key block j
     float* stats;         // [B*H, Sq * 2] per 64-token query block: lse * log2(e) [64], delta [64] (tcgen05 passes)
+    int32_t* idx_u;       // [B*H, Nq_u, cap * Uk] the lists per 64-token unit, when blocks are split into units
+    int32_t* cnt_u;       // [B*H, Nq_u]
 };
 bool attn_bwd_supported(const BwdArgs& a, const char** why);
-size_t attn_bwd_workspace_bytes(long long BH, long long Sq, int Nq, int Nk, int cap);
+size_t attn_bwd_workspace_bytes(long long BH, const Geom& gq, const Geom& gk, int cap);
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why);
 // the dQ and dK/dV passes on tcgen05 (attn_bwd_tc.cu): head_dim 128, 64-token blocks, whole grids
 bool attn_bwd_tc_supported(const BwdArgs& a);

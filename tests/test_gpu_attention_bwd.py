@@ -66,15 +66,17 @@ def test_gradients_against_oracle(name):
     print(f"BWD PARITY {name}:", _compare(name, (dq, dk, dv), (rq, rk, rv)))
 
 
-def test_key_blocks_of_another_size_than_query_blocks():
-    wl = Workload("mixed", 6006, 1, 2, 128, (8, 8, 16), (8, 8, 16), (4, 4, 4), 0.5, torch.bfloat16, "normal")
-    chunk_k = (4, 4, 8)
+@pytest.mark.parametrize("chunk_q,chunk_k", [((4, 4, 4), (4, 4, 8)), ((4, 4, 4), (4, 8, 8)), ((4, 4, 8), (4, 4, 4)), ((4, 4, 8), (4, 8, 8)),
+                                             ((2, 8, 8), (4, 4, 8))])
+def test_key_blocks_of_another_size_than_query_blocks(chunk_q, chunk_k):
+    """Blocks of 128 and 256 tokens reach the tcgen05 passes as 64-token units with rewritten lists."""
+    wl = Workload("mixed", 6006, 1, 2, 128, (8, 8, 16), (8, 8, 16), chunk_q, 0.5, torch.bfloat16, "normal")
     q, k, v = make_qkv(wl)
     do = _dout(wl, 18)
     idx, cnt, _, _ = O.block_select(q, k, wl.grid_q, wl.grid_k, wl.sparsity, wl.chunk, chunk_k)
     _, rq, rk, rv = OB.attention_backward(q, k, v, do, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, chunk_k)
     _, dq, dk, dv = _forward_and_backward(wl, q, k, v, do, idx, cnt, chunk_k=chunk_k)
-    print("BWD PARITY mixed:", _compare("mixed", (dq, dk, dv), (rq, rk, rv)))
+    print(f"BWD PARITY q {chunk_q} k {chunk_k}:", _compare("mixed", (dq, dk, dv), (rq, rk, rv)))
 
 
 def test_lists_of_different_lengths_empty_lists_and_unselected_key_blocks():
