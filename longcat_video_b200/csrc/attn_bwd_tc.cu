@@ -1,7 +1,8 @@
 // Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128 and 64-token query and key blocks on whole
 // grids (larger blocks arrive as 64-token units, attn_bwd.cu): the dQ pass and the dK/dV pass, after the delta kernel
-// and the transposition of the block lists of attn_bwd.cu, which keeps head_dim 64 and ragged grids on warp-level MMAs.  Stands in for the Triton kernels _attn_bwd_dq_bsa_varlen_align
-// and _attn_bwd_dkdv_bsa_varlen_align (longcat_video/block_sparse_attention/flash_attn_bsa_varlen_mask.py:289-945).
+// and the transposition of the block lists of attn_bwd.cu, which keeps head_dim 64 and ragged grids on warp-level MMAs.
+// Stands in for the Triton kernels _attn_bwd_dq_bsa_varlen_align and _attn_bwd_dkdv_bsa_varlen_align
+// (longcat_video/block_sparse_attention/flash_attn_bsa_varlen_mask.py:289-945).
 //
 // Both passes are one kernel with the roles of the operands exchanged.  A CTA owns one 64-row tile pair (A1, A2) and walks
 // a list of tile pairs (B1, B2); per list entry
