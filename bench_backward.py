@@ -67,7 +67,7 @@ def main():
     # delta, four list-transposition kernels, two passes; the tcgen05 passes add the per-block lse/delta layout and, for
     # blocks above 64 tokens, the rewriting of the lists per 64-token unit
     tc = wl.head_dim == 128 and os.environ.get("LCBSA_BWD_IMPL") != "mma"
-    launches = 7 + (1 if tc else 0) + (1 if tc and bs > 64 else 0)
+    launches = 7 + (1 if tc else 0) + ((2 if bs == 128 else 1) if tc and bs > 64 else 0)  # 128-token blocks: one rewriting per pass
     line = {"bench": "bsa_backward", "workload": wl.name, "heads": args.heads, "block": list(wl.chunk), "selected_blocks": nsel,
             "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
             "ms_forward_attention": ms_fwd, "ms_backward": ms_bwd, "backward_tflops": 2.5 * fwd_flops / ms_bwd / 1e9,

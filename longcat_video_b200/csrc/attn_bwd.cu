@@ -662,44 +662,69 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    // head_dim 128 on whole grids: the tcgen05 passes, on the blocks themselves (64 tokens) or on their 64-token units
-    BwdArgs u = a;
+    // head_dim 128 on whole grids: the tcgen05 passes.  Their CTAs own a block of 64 or 128 tokens and stream 64-token
+    // units, so the lists are rewritten in those terms: for the dQ pass (own query block -> key units) and for the dK/dV
+    // pass (query unit -> own key block, which is then transposed).
+    BwdTcPlan plan{};
     bool use_tc = false;
+    const int32_t* t_idx = a.idx;  // the lists to transpose
+    const int32_t* t_cnt = a.cnt;
+    int t_cap = a.cap, t_nq = a.gq.nblk, t_nk = a.gk.nblk;
     if (D == 128) {
         UnitSplit sq, sk;
         if (split_units64(a.gq, &sq) && split_units64(a.gk, &sk)) {
-            u.gq = sq.gu;
-            u.gk = sk.gu;
-            const bool split = sq.units * sk.units > 1;
-            if (split) {
-                u.idx = a.idx_u;
-                u.cnt = a.cnt_u;
-                u.cap = a.cap * sk.units;
-            }
-            use_tc = attn_bwd_tc_supported(u);
-            if (use_tc && split) {
-                const long long total = (long long)BH * sq.gu.nblk * a.cap;
-                bwd_expand_lists_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, a.gq, sq, a.gk, sk, total, a.idx_u,
-                                                                                       a.cnt_u);
+            const UnitSplit idq{a.gq, 1, 1, 1, 1}, idk{a.gk, 1, 1, 1, 1};
+            const UnitSplit& q1 = a.gq.bs == 128 ? idq : sq;  // own blocks of the dQ pass
+            const UnitSplit& k2 = a.gk.bs == 128 ? idk : sk;  // own blocks of the dK/dV pass
+            plan.own_q = q1.gu; plan.unit_k = sk.gu;
+            plan.unit_q = sq.gu; plan.own_k = k2.gu;
+            const bool rewrite1 = q1.units * sk.units > 1, rewrite2 = sq.units * k2.units > 1;
+            const bool same = q1.units == sq.units && k2.units == sk.units;  // one rewriting serves both passes
+            plan.list_q = rewrite1 ? a.idx_u : a.idx;
+            plan.cnt_q = rewrite1 ? a.cnt_u : a.cnt;
+            plan.cap_q = a.cap * sk.units;
+            use_tc = attn_bwd_tc_supported(a, plan);
+            if (use_tc) {
+                if (rewrite1) {
+                    const long long total = (long long)BH * q1.gu.nblk * a.cap;
+                    bwd_expand_lists_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, a.gq, q1, a.gk, sk, total, a.idx_u,
+                                                                                           a.cnt_u);
+                }
+                if (rewrite2 && !same) {
+                    const long long total = (long long)BH * sq.gu.nblk * a.cap;
+                    bwd_expand_lists_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.idx, a.cnt, a.cap, a.gq, sq, a.gk, k2, total, a.idx_t,
+                                                                                           a.cnt_t);
+                }
                 cudaError_t e = cudaGetLastError();
                 if (e != cudaSuccess) return e;
+                if (rewrite2) {
+                    t_idx = same ? a.idx_u : a.idx_t;
+                    t_cnt = same ? a.cnt_u : a.cnt_t;
+                }
+                t_cap = a.cap * k2.units;
+                t_nq = sq.gu.nblk;
+                t_nk = k2.gu.nblk;
             }
         }
     }
     {
-        const BwdArgs& t = use_tc ? u : a;  // the lists that the dK/dV pass needs per key block
-        const int Nq = t.gq.nblk, Nk = t.gk.nblk, Wq = (Nq + 31) / 32;
-        const long long rows_k = (long long)BH * Nk, entries = (long long)BH * Nq * t.cap;
-        cudaError_t e = cudaMemsetAsync(t.bitmap, 0, (size_t)rows_k * Wq * sizeof(uint32_t), st);
+        const int Nq = t_nq, Nk = t_nk, Wq = (Nq + 31) / 32;
+        const long long rows_k = (long long)BH * Nk, entries = (long long)BH * Nq * t_cap;
+        cudaError_t e = cudaMemsetAsync(a.bitmap, 0, (size_t)rows_k * Wq * sizeof(uint32_t), st);
         if (e != cudaSuccess) return e;
-        bwd_mark_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(t.idx, t.cnt, t.cap, Nq, Nk, Wq, entries, t.bitmap, t.status);
-        bwd_count_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(t.bitmap, Wq, rows_k, t.tcnt);
-        bwd_scan_kernel<<<BH, 256, 0, st>>>(t.tcnt, Nk, t.toff);
-        bwd_emit_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(t.bitmap, Wq, Nk, Nq, t.cap, rows_k, t.toff, t.tidx);
+        bwd_mark_kernel<<<(unsigned)((entries + 255) / 256), 256, 0, st>>>(t_idx, t_cnt, t_cap, Nq, Nk, Wq, entries, a.bitmap, a.status);
+        bwd_count_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, rows_k, a.tcnt);
+        bwd_scan_kernel<<<BH, 256, 0, st>>>(a.tcnt, Nk, a.toff);
+        bwd_emit_kernel<<<(unsigned)((rows_k * 32 + 255) / 256), 256, 0, st>>>(a.bitmap, Wq, Nk, Nq, t_cap, rows_k, a.toff, a.tidx);
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    if (use_tc) return launch_attn_bwd_tc(u, st, why);
+    if (use_tc) {
+        plan.toff = a.toff;
+        plan.tidx = a.tidx;
+        plan.tidx_stride = (long long)t_nq * t_cap;
+        return launch_attn_bwd_tc(a, plan, st, why);
+    }
     const size_t tabs = (size_t)(a.gq.bs + a.gk.bs) * sizeof(mm::SlotEntry);
     const size_t smem_dq = 6 * (size_t)kTile * D * 2 + 2 * kTile + tabs;
     const size_t smem_kv = 6 * (size_t)kTile * D * 2 + 2 * 2 * kTile * sizeof(float) + 2 * kTile + tabs;
@@ -733,7 +758,7 @@ namespace {
 
 // The workspace is laid out for the finest form the lists can take: 64-token units (a block of 64 * U tokens counts U times).
 struct BwdLayout {
-    size_t delta, tcnt, toff, tidx, bitmap, stats, idx_u, cnt_u, total;
+    size_t delta, tcnt, toff, tidx, bitmap, stats, idx_u, cnt_u, idx_t, cnt_t, total;
 };
 
 BwdLayout bwd_layout(long long BH, const Geom& gq, const Geom& gk, int cap) {
@@ -751,6 +776,8 @@ BwdLayout bwd_layout(long long BH, const Geom& gq, const Geom& gk, int cap) {
     l.stats = off;  off += up((size_t)BH * Sq * 2 * sizeof(float));
     l.idx_u = off;  off += up((size_t)BH * Nq * capu * sizeof(int32_t));
     l.cnt_u = off;  off += up((size_t)BH * Nq * sizeof(int32_t));
+    l.idx_t = off;  off += up((size_t)BH * Nq * capu * sizeof(int32_t));
+    l.cnt_t = off;  off += up((size_t)BH * Nq * sizeof(int32_t));
     l.total = off;
     return l;
 }
@@ -770,6 +797,8 @@ cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const c
     a.stats = reinterpret_cast<float*>(w + l.stats);
     a.idx_u = reinterpret_cast<int32_t*>(w + l.idx_u);
     a.cnt_u = reinterpret_cast<int32_t*>(w + l.cnt_u);
+    a.idx_t = reinterpret_cast<int32_t*>(w + l.idx_t);
+    a.cnt_t = reinterpret_cast<int32_t*>(w + l.cnt_t);
     if (a.dtype == LCBSA_BF16) return a.D == 128 ? run_bwd<__nv_bfloat16, 128>(a, st, why) : run_bwd<__nv_bfloat16, 64>(a, st, why);
     return a.D == 128 ? run_bwd<__half, 128>(a, st, why) : run_bwd<__half, 64>(a, st, why);
 }

@@ -50,21 +50,26 @@ constexpr int kD = 128;
 constexpr int kBlk = 64;
 constexpr int kTileBytes = kBlk * kD * 2;   // 16 KiB
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half: 64 rows x 128 B, 128B-swizzled
-constexpr int kSlots = 5;                   // ring of (B1, B2) tile pairs
-constexpr int kSlotBytes = 2 * kTileBytes;
-constexpr int kStatsFloats = 2 * kBlk;      // per query block: lse * log2(e) [64], delta [64]
+constexpr int kSlotBytes = 2 * kTileBytes;  // a ring slot: the (B1, B2) tiles of one list entry
+constexpr int kStatsFloats = 2 * kBlk;      // per 64-token query block: lse * log2(e) [64], delta [64]
 constexpr int kStatsBytes = kStatsFloats * 4;
 constexpr int kThreads = 384;
 constexpr int kRegsMath = 208, kRegsOther = 88;  // setmaxnreg: (208 + 208 + 88) * 128 <= 64 K registers
 
-constexpr int kOffA = 0;                                   // A1, A2
-constexpr int kOffB = kOffA + 2 * kTileBytes;              // kSlots x (B1, B2)
-constexpr int kOffStats = kOffB + kSlots * kSlotBytes;     // kSlots x (lse2[64], delta[64])
-constexpr int kOffBar = kOffStats + kSlots * kStatsBytes;
-// barriers: a_full, full[kSlots], empty[kSlots], s_full[2], s_free, x_full[2], acc_done
-constexpr int kNumBars = 1 + 2 * kSlots + 2 + 1 + 2 + 1;
-constexpr int kOffMisc = kOffBar + kNumBars * 8;           // abort flag, TMEM base
-constexpr int kSmemBytes = kOffMisc + 64;
+// Shared memory, for own tiles of kM = 64 or 128 rows (the streamed tiles always have 64).
+template <int kM> struct Lay {
+    static constexpr int aTile = kM * kD * 2;        // 16 or 32 KiB: A1, A2
+    static constexpr int aHalf = aTile / 2;          // one 64-column half: kM rows x 128 B, 128B-swizzled
+    static constexpr int slots = kM == 64 ? 5 : 4;   // ring of (B1, B2) tile pairs
+    static constexpr int offA = 0;
+    static constexpr int offB = offA + 2 * aTile;
+    static constexpr int offStats = offB + slots * kSlotBytes;  // per slot: lse2[64], delta[64] of the streamed query block
+    static constexpr int offBar = offStats + slots * kStatsBytes;
+    // barriers: a_full, full[slots], empty[slots], s_full[2], s_free, x_full[2], acc_done
+    static constexpr int numBars = 1 + 2 * slots + 2 + 1 + 2 + 1;
+    static constexpr int offMisc = offBar + numBars * 8;  // abort flag, TMEM base
+    static constexpr int smem = offMisc + 64;
+};
 
 // TMEM columns.  dQ pass: dQ 0..127, S[buf] 128 + 128 buf, dP[buf] 192 + 128 buf, dS[buf] 384 + 32 buf.
 // dK/dV pass: dK 0..127, dV 128..255, S^T 256..319, dP^T 320..383, P^T[buf] 384 + 64 buf, dS^T[buf] 416 + 64 buf.
@@ -86,17 +91,21 @@ template <> struct Cols<1> {
 
 struct BwdTcParams {
     CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
-    const int32_t* list;   // dQ pass: idx [BH][Nq][cap]; dK/dV pass: tidx [BH][Nq * cap]
-    const int32_t* cnt;    // dQ pass: [BH][Nq]
-    const int32_t* toff;   // dK/dV pass: [BH][Nk + 1]
-    const float* stats;    // [BH][Nq][2][64]
+    const int32_t* list;   // dQ pass: [BH][n_own][cap] key units per own block; dK/dV pass: [BH][list_stride] query units, by toff
+    const int32_t* cnt;    // dQ pass: [BH][n_own]
+    const int32_t* toff;   // dK/dV pass: [BH][n_own + 1]
+    long long list_stride;
+    const float* stats;    // dK/dV pass: [BH][n_stream][2][64] of the streamed 64-token query blocks
+    const float* lse;      // dQ pass: [BH][Sq] natural log, of the own rows
+    const float* delta;    // dQ pass: [BH][Sq]
+    long long Sq;
     unsigned int* status;
     void* out1;            // dQ pass: dq; dK/dV pass: dk
     void* out2;            // dK/dV pass: dv
     long long o1_sb, o1_sh, o1_ss, o2_sb, o2_sh, o2_ss;  // element strides
-    int cap, nq, nk, heads;
+    int cap, n_own, n_stream, heads;
     int merge_a1, merge_a2, merge_b1, merge_b2;  // how the batch axis is folded into each map
-    Geom ga, gb;           // grid of the CTA's own tiles, grid of the streamed tiles
+    Geom ga, gb;           // grid of the CTA's own tiles (blocks of 64 or 128 tokens), grid of the streamed 64-token tiles
     float scale, scale2;   // sm_scale, sm_scale * log2(e)
 };
 
@@ -146,9 +155,12 @@ __device__ __forceinline__ void store_row32(unsigned char* row_ptr, int col0, co
 }
 
 // kMode 0: dQ pass, 1: dK/dV pass.  Grid: (blocks of the CTA's own grid, batch * heads).
-template <bool kBf16, int kMode>
+template <bool kBf16, int kMode, int kM>
 __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
     using C = Cols<kMode>;
+    using Ly = Lay<kM>;
+    constexpr int kSlots = Ly::slots, kOffA = Ly::offA, kOffB = Ly::offB, kOffStats = Ly::offStats, kOffBar = Ly::offBar, kOffMisc = Ly::offMisc;
+    constexpr int kATile = Ly::aTile, kAHalf = Ly::aHalf;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + kOffBar;
@@ -172,11 +184,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
     const int32_t* list;
     int n;
     if (kMode == 0) {
-        list = P.list + ((long long)bh * P.nq + own) * P.cap;
-        n = min(max(P.cnt[(long long)bh * P.nq + own], 0), P.cap);
+        list = P.list + ((long long)bh * P.n_own + own) * P.cap;
+        n = min(max(P.cnt[(long long)bh * P.n_own + own], 0), P.cap);
     } else {
-        const int lo = P.toff[(long long)bh * (P.nk + 1) + own], hi = P.toff[(long long)bh * (P.nk + 1) + own + 1];
-        list = P.list + (long long)bh * P.nq * P.cap + lo;
+        const int lo = P.toff[(long long)bh * (P.n_own + 1) + own], hi = P.toff[(long long)bh * (P.n_own + 1) + own + 1];
+        list = P.list + (long long)bh * P.list_stride + lo;
         n = max(hi - lo, 0);
     }
 
@@ -219,9 +231,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
         if (warp == 8 && n > 0) {
             // ================================================================== TMA producer
             if (lane == 0) {
-                mbar_arrive_tx(bar_a_full, 2 * kTileBytes);
-                load_tile_pair(sbase + kOffA, &P.tm_a1, bar_a_full, block_coord(P.ga, own, b, h, P.heads, P.merge_a1, P.ga.T));
-                load_tile_pair(sbase + kOffA + kTileBytes, &P.tm_a2, bar_a_full, block_coord(P.ga, own, b, h, P.heads, P.merge_a2, P.ga.T));
+                // one box of kM rows per 64-column half (the own grid's block is the box)
+                mbar_arrive_tx(bar_a_full, 2 * kATile);
+                const Coord c1 = block_coord(P.ga, own, b, h, P.heads, P.merge_a1, P.ga.T), c2 = block_coord(P.ga, own, b, h, P.heads, P.merge_a2, P.ga.T);
+                tma_load_5d(sbase + kOffA, &P.tm_a1, bar_a_full, 0, c1.c1, c1.c2, c1.c3, c1.c4);
+                tma_load_5d(sbase + kOffA + kAHalf, &P.tm_a1, bar_a_full, 64, c1.c1, c1.c2, c1.c3, c1.c4);
+                tma_load_5d(sbase + kOffA + kATile, &P.tm_a2, bar_a_full, 0, c2.c1, c2.c2, c2.c3, c2.c4);
+                tma_load_5d(sbase + kOffA + kATile + kAHalf, &P.tm_a2, bar_a_full, 64, c2.c1, c2.c2, c2.c3, c2.c4);
             }
             bool ok = true;
             int win = 0, issued = 0;
@@ -248,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
                     load_tile_pair(dst, &P.tm_b1, bar_full(slot), c1);
                     load_tile_pair(dst + kTileBytes, &P.tm_b2, bar_full(slot), c2);
                     if (kMode == 1)  // transposed lists only hold blocks of the grid
-                        bulk_load(sbase + kOffStats + slot * kStatsBytes, P.stats + ((long long)bh * P.nq + blk) * kStatsFloats, kStatsBytes,
+                        bulk_load(sbase + kOffStats + slot * kStatsBytes, P.stats + ((long long)bh * P.n_stream + blk) * kStatsFloats, kStatsBytes,
                                   bar_full(slot));
                 }
                 __syncwarp();
@@ -264,8 +280,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             }
         } else if (warp == 9 && n > 0) {
             // ================================================================== MMA issuer
-            const uint32_t idesc_ss = instr_desc(kBf16, 64, 64, 0), idesc_ts = instr_desc(kBf16, 64, 128, 1);
-            const uint64_t a1d = smem_desc(sbase + kOffA, 16, 1024), a2d = smem_desc(sbase + kOffA + kTileBytes, 16, 1024);
+            const uint32_t idesc_ss = instr_desc(kBf16, kM, 64, 0), idesc_ts = instr_desc(kBf16, kM, 128, 1);
+            const uint64_t a1d = smem_desc(sbase + kOffA, 16, 1024), a2d = smem_desc(sbase + kOffA + kATile, 16, 1024);
             bool ok = mbar_wait_warp(bar_a_full, 0, ctl, 220 + kMode, 0);
             // S (or S^T) and dP (or dP^T) of entry s
             auto issue_ss = [&](int s) -> bool {
@@ -279,14 +295,17 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
                 const uint64_t b1d = smem_desc(tile, 16, 1024), b2d = smem_desc(tile + kTileBytes, 16, 1024);
 #pragma unroll
                 for (int j = 0; j < kD / 16; ++j) {
-                    // 32 bytes per 16-column step inside a 64-column half, halves 8 KiB apart
+                    // 32 bytes per 16-column step inside a 64-column half; the halves are kM x 128 B (own tile) and 8 KiB
+                    // (streamed tile) apart
+                    const uint64_t aoff = (uint64_t)(((j >> 2) * kAHalf + (j & 3) * 32) >> 4);
                     const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
-                    tc_mma(tmem + C::s(buf), a1d + off, b1d + off, idesc_ss, j > 0);
+                    tc_mma(tmem + C::s(buf), a1d + aoff, b1d + off, idesc_ss, j > 0);
                 }
 #pragma unroll
                 for (int j = 0; j < kD / 16; ++j) {
+                    const uint64_t aoff = (uint64_t)(((j >> 2) * kAHalf + (j & 3) * 32) >> 4);
                     const uint64_t off = (uint64_t)(((j >> 2) * kHalfBytes + (j & 3) * 32) >> 4);
-                    tc_mma(tmem + C::dp(buf), a2d + off, b2d + off, idesc_ss, j > 0);
+                    tc_mma(tmem + C::dp(buf), a2d + aoff, b2d + off, idesc_ss, j > 0);
                 }
                 tc_commit(bar_s_full(buf));
                 return true;
@@ -330,14 +349,23 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
         // ================================================================== arithmetic warps
         const int wg = warp >> 2;  // dQ pass: entries wg, wg + 2, ...; dK/dV pass: columns 32 wg .. 32 wg + 31 of every entry
         const int wq = warp & 3;   // TMEM quadrant of this warp
-        const int row = wq * 16 + (lane & 15);  // row of the 64 x 64 tile (lanes 16-31 shadow lanes 0-15; their TMEM lanes are unused)
+        // row of the own tile = TMEM lane.  An M=128 accumulator has row r in lane r; an M=64 one occupies lanes 0-15 of every
+        // 32-lane quadrant (lanes 16-31 of a warp then shadow lanes 0-15 on TMEM lanes that nothing reads)
+        const int row = kM == 128 ? wq * 32 + lane : wq * 16 + (lane & 15);
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
+        // the token of this row (rows of a block are its tokens in t, h, w order)
+        long long tok;
+        {
+            int lt, lh, lw, bt, bhh, bw;
+            slot_coords(P.ga, row, lt, lh, lw);
+            block_coords(P.ga, own, bt, bhh, bw);
+            tok = ((long long)(bt * P.ga.ct + lt) * P.ga.H + (bhh * P.ga.ch + lh)) * P.ga.W + (bw * P.ga.cw + lw);
+        }
         // dQ pass: this thread's query row has one lse and one delta for the whole list
         float my_l2 = 0.f, my_dl = 0.f;
         if (kMode == 0 && n > 0) {
-            const float* st = P.stats + ((long long)bh * P.nq + own) * kStatsFloats;
-            my_l2 = st[row];
-            my_dl = st[kBlk + row];
+            my_l2 = P.lse[(long long)bh * P.Sq + tok] * 1.4426950408889634f;
+            my_dl = P.delta[(long long)bh * P.Sq + tok];
         }
         // 32 columns of S and dP -> 16 columns of P and of dS in the input dtype.  st4: the slot's lse and delta values
         // of those 32 columns (dK/dV pass, where columns are query rows)
@@ -419,10 +447,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
                 tc_fence_after();
             }
             if (ok) {
-                int lt, lh, lw, bt, bhh, bw;
-                slot_coords(P.ga, row, lt, lh, lw);
-                block_coords(P.ga, own, bt, bhh, bw);
-                const long long tok = ((long long)(bt * P.ga.ct + lt) * P.ga.H + (bhh * P.ga.ch + lh)) * P.ga.W + (bw * P.ga.cw + lw);
                 // dQ pass: warpgroup g stores columns 64 g .. 64 g + 63 of dQ; dK/dV pass: warpgroup 0 stores dK, 1 dV
                 const bool second = kMode == 1 && wg == 1;
                 unsigned char* base = static_cast<unsigned char*>(second ? P.out2 : P.out1);
@@ -440,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 32; ++j) acc[j] = 0u;  // nothing selected this block: its gradient is zero
                     }
-                    if (lane < 16) store_row32<kBf16>(row_ptr, col_lo + 32 * ch, acc);
+                    if (kM == 128 || lane < 16) store_row32<kBf16>(row_ptr, col_lo + 32 * ch, acc);
                 }
             }
         }
@@ -455,78 +479,102 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
     }
 }
 
-template <bool kBf16, int kMode>
+template <bool kBf16, int kMode, int kM>
 cudaError_t launch_pass(const BwdTcParams& P, unsigned own_blocks, unsigned BH, cudaStream_t st) {
     // the attribute is per device and per kernel; setting it on every call costs a microsecond and keeps this stateless
-    cudaError_t e = cudaFuncSetAttribute(bwd_tc_kernel<kBf16, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(bwd_tc_kernel<kBf16, kMode, kM>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<kM>::smem);
     if (e != cudaSuccess) return e;
-    bwd_tc_kernel<kBf16, kMode><<<dim3(own_blocks, BH), kThreads, kSmemBytes, st>>>(P);
+    bwd_tc_kernel<kBf16, kMode, kM><<<dim3(own_blocks, BH), kThreads, Lay<kM>::smem, st>>>(P);
     return cudaGetLastError();
+}
+
+template <int kMode>
+cudaError_t launch_pass_any(bool bf16, int rows, const BwdTcParams& P, unsigned own_blocks, unsigned BH, cudaStream_t st) {
+    if (rows == 128) return bf16 ? launch_pass<true, kMode, 128>(P, own_blocks, BH, st) : launch_pass<false, kMode, 128>(P, own_blocks, BH, st);
+    return bf16 ? launch_pass<true, kMode, 64>(P, own_blocks, BH, st) : launch_pass<false, kMode, 64>(P, own_blocks, BH, st);
+}
+
+bool grid_fits(const Geom& g, int rows) {
+    return !g.ragged && g.bs == rows && g.ct <= 256 && g.ch <= 256 && g.cw <= 256;
 }
 
 }  // namespace
 
-bool attn_bwd_tc_supported(const BwdArgs& a) {
+bool attn_bwd_tc_supported(const BwdArgs& a, const BwdTcPlan& p) {
     const char* force = std::getenv("LCBSA_BWD_IMPL");  // "mma" keeps the warp-level kernels (for comparisons)
     if (force && std::strcmp(force, "mma") == 0) return false;
     if (a.dtype != LCBSA_BF16 && a.dtype != LCBSA_FP16) return false;
-    if (a.D != kD || a.gq.bs != kBlk || a.gk.bs != kBlk || a.gq.ragged || a.gk.ragged) return false;
-    if (a.gq.ct > 256 || a.gq.ch > 256 || a.gq.cw > 256 || a.gk.ct > 256 || a.gk.ch > 256 || a.gk.cw > 256) return false;
+    if (a.D != kD) return false;
+    if (!grid_fits(p.unit_q, 64) || !grid_fits(p.unit_k, 64)) return false;
+    if (!grid_fits(p.own_q, 64) && !grid_fits(p.own_q, 128)) return false;
+    if (!grid_fits(p.own_k, 64) && !grid_fits(p.own_k, 128)) return false;
     if (encode_fn() == nullptr) return false;
     const View* vs[4] = {&a.q, &a.dout, &a.k, &a.v};
-    const Geom* gs[4] = {&a.gq, &a.gq, &a.gk, &a.gk};
-    for (int i = 0; i < 4; ++i) {
-        if (merge_mode(*vs[i], a.B, a.H, *gs[i]) < 0) return false;
-        if (vs[i]->ss * 2 >= (1ll << 40) || vs[i]->sh * 2 >= (1ll << 40)) return false;
+    const Geom* gs[8] = {&p.own_q, &p.own_q, &p.own_k, &p.own_k, &p.unit_q, &p.unit_q, &p.unit_k, &p.unit_k};
+    for (int i = 0; i < 8; ++i) {
+        const View& v = *vs[i % 4];
+        if (merge_mode(v, a.B, a.H, *gs[i]) < 0) return false;
+        if (v.ss * 2 >= (1ll << 40) || v.sh * 2 >= (1ll << 40)) return false;
     }
     return true;
 }
 
-// a.delta and the transposed lists (a.toff, a.tidx) are ready on the stream; a.stats is scratch of B*H*Sq*2 floats
-cudaError_t launch_attn_bwd_tc(const BwdArgs& a, cudaStream_t st, const char** why) {
+// a.delta, the lists of the plan and (for the dK/dV pass) their transposition are ready on the stream; a.stats is scratch
+// of B*H*Sq*2 floats
+cudaError_t launch_attn_bwd_tc(const BwdArgs& a, const BwdTcPlan& p, cudaStream_t st, const char** why) {
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
     const long long BH = (long long)a.B * a.H;
     {
-        const long long total = BH * Sq;  // whole grids: every block has its 64 rows
-        bwd_stats_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.lse, a.delta, a.gq, Sq, total, a.stats);
+        const long long total = BH * Sq;  // whole grids: every 64-token query unit has its 64 rows
+        bwd_stats_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.lse, a.delta, p.unit_q, Sq, total, a.stats);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    const int mq = merge_mode(a.q, a.B, a.H, a.gq), mdo = merge_mode(a.dout, a.B, a.H, a.gq);
-    const int mk = merge_mode(a.k, a.B, a.H, a.gk), mv = merge_mode(a.v, a.B, a.H, a.gk);
-    CUtensorMap tq, tdo, tk, tv;
-    if (!make_map(&tq, a.dtype, a.q, a.B, a.H, a.gq, mq) || !make_map(&tdo, a.dtype, a.dout, a.B, a.H, a.gq, mdo) ||
-        !make_map(&tk, a.dtype, a.k, a.B, a.H, a.gk, mk) || !make_map(&tv, a.dtype, a.v, a.B, a.H, a.gk, mv)) {
-        *why = "cuTensorMapEncodeTiled rejected a tensor";
-        return cudaErrorInvalidValue;
-    }
+    // maps: q and dout with the boxes of the dQ pass's own blocks and of the streamed query units; k and v likewise
+    const int m_q_own = merge_mode(a.q, a.B, a.H, p.own_q), m_do_own = merge_mode(a.dout, a.B, a.H, p.own_q);
+    const int m_q_u = merge_mode(a.q, a.B, a.H, p.unit_q), m_do_u = merge_mode(a.dout, a.B, a.H, p.unit_q);
+    const int m_k_own = merge_mode(a.k, a.B, a.H, p.own_k), m_v_own = merge_mode(a.v, a.B, a.H, p.own_k);
+    const int m_k_u = merge_mode(a.k, a.B, a.H, p.unit_k), m_v_u = merge_mode(a.v, a.B, a.H, p.unit_k);
     BwdTcParams P;
     std::memset(&P, 0, sizeof(P));
     P.stats = a.stats;
+    P.lse = a.lse;
+    P.delta = a.delta;
+    P.Sq = Sq;
     P.status = a.status;
-    P.cap = a.cap; P.nq = a.gq.nblk; P.nk = a.gk.nblk; P.heads = a.H;
+    P.heads = a.H;
     P.scale = a.sm_scale;
     P.scale2 = a.sm_scale * 1.4426950408889634f;
     const bool bf16 = a.dtype == LCBSA_BF16;
 
-    // dQ pass: own tiles Q_i, dO_i; streamed K_j, V_j
-    P.tm_a1 = tq; P.tm_a2 = tdo; P.tm_b1 = tk; P.tm_b2 = tv;
-    P.merge_a1 = mq; P.merge_a2 = mdo; P.merge_b1 = mk; P.merge_b2 = mv;
-    P.ga = a.gq; P.gb = a.gk;
-    P.list = a.idx; P.cnt = a.cnt; P.toff = nullptr;
+    // dQ pass: own tiles Q_i, dO_i (a query block of 64 or 128 tokens); streamed K_j, V_j (64-token units)
+    if (!make_map(&P.tm_a1, a.dtype, a.q, a.B, a.H, p.own_q, m_q_own) || !make_map(&P.tm_a2, a.dtype, a.dout, a.B, a.H, p.own_q, m_do_own) ||
+        !make_map(&P.tm_b1, a.dtype, a.k, a.B, a.H, p.unit_k, m_k_u) || !make_map(&P.tm_b2, a.dtype, a.v, a.B, a.H, p.unit_k, m_v_u)) {
+        *why = "cuTensorMapEncodeTiled rejected a tensor";
+        return cudaErrorInvalidValue;
+    }
+    P.merge_a1 = m_q_own; P.merge_a2 = m_do_own; P.merge_b1 = m_k_u; P.merge_b2 = m_v_u;
+    P.ga = p.own_q; P.gb = p.unit_k;
+    P.list = p.list_q; P.cnt = p.cnt_q; P.cap = p.cap_q; P.toff = nullptr; P.list_stride = 0;
+    P.n_own = p.own_q.nblk; P.n_stream = p.unit_k.nblk;
     P.out1 = const_cast<void*>(a.dq.data); P.o1_sb = a.dq.sb; P.o1_sh = a.dq.sh; P.o1_ss = a.dq.ss;
     P.out2 = nullptr;
-    cudaError_t e = bf16 ? launch_pass<true, 0>(P, (unsigned)a.gq.nblk, (unsigned)BH, st) : launch_pass<false, 0>(P, (unsigned)a.gq.nblk, (unsigned)BH, st);
+    cudaError_t e = launch_pass_any<0>(bf16, p.own_q.bs, P, (unsigned)p.own_q.nblk, (unsigned)BH, st);
     if (e != cudaSuccess) return e;
 
-    // dK/dV pass: own tiles K_j, V_j; streamed Q_i, dO_i
-    P.tm_a1 = tk; P.tm_a2 = tv; P.tm_b1 = tq; P.tm_b2 = tdo;
-    P.merge_a1 = mk; P.merge_a2 = mv; P.merge_b1 = mq; P.merge_b2 = mdo;
-    P.ga = a.gk; P.gb = a.gq;
-    P.list = a.tidx; P.cnt = nullptr; P.toff = a.toff;
+    // dK/dV pass: own tiles K_j, V_j (a key block of 64 or 128 tokens); streamed Q_i, dO_i (64-token units)
+    if (!make_map(&P.tm_a1, a.dtype, a.k, a.B, a.H, p.own_k, m_k_own) || !make_map(&P.tm_a2, a.dtype, a.v, a.B, a.H, p.own_k, m_v_own) ||
+        !make_map(&P.tm_b1, a.dtype, a.q, a.B, a.H, p.unit_q, m_q_u) || !make_map(&P.tm_b2, a.dtype, a.dout, a.B, a.H, p.unit_q, m_do_u)) {
+        *why = "cuTensorMapEncodeTiled rejected a tensor";
+        return cudaErrorInvalidValue;
+    }
+    P.merge_a1 = m_k_own; P.merge_a2 = m_v_own; P.merge_b1 = m_q_u; P.merge_b2 = m_do_u;
+    P.ga = p.own_k; P.gb = p.unit_q;
+    P.list = p.tidx; P.cnt = nullptr; P.cap = 0; P.toff = p.toff; P.list_stride = p.tidx_stride;
+    P.n_own = p.own_k.nblk; P.n_stream = p.unit_q.nblk;
     P.out1 = const_cast<void*>(a.dk.data); P.o1_sb = a.dk.sb; P.o1_sh = a.dk.sh; P.o1_ss = a.dk.ss;
     P.out2 = const_cast<void*>(a.dv.data); P.o2_sb = a.dv.sb; P.o2_sh = a.dv.sh; P.o2_ss = a.dv.ss;
-    return bf16 ? launch_pass<true, 1>(P, (unsigned)a.gk.nblk, (unsigned)BH, st) : launch_pass<false, 1>(P, (unsigned)a.gk.nblk, (unsigned)BH, st);
+    return launch_pass_any<1>(bf16, p.own_k.bs, P, (unsigned)p.own_k.nblk, (unsigned)BH, st);
 }
 
 }  // namespace lcbsa

@@ -148,15 +148,28 @@ struct BwdArgs {
     int32_t* tidx;        // [B*H, Nq * cap] query blocks of key block j at toff[j] .. toff[j + 1], ascending
     uint32_t* bitmap;     // [B*H, Nk, ceil(Nq / 32)] bit i of row j: query block i selected key block j
     float* stats;         // [B*H, Sq * 2] per 64-token query block: lse * log2(e) [64], delta [64] (tcgen05 passes)
-    int32_t* idx_u;       // [B*H, Nq_u, cap * Uk] the lists per 64-token unit, when blocks are split into units
+    int32_t* idx_u;       // [B*H, Nq_u, cap * Uk] rewritten lists of the dQ pass (tcgen05 passes, blocks split into units)
     int32_t* cnt_u;       // [B*H, Nq_u]
+    int32_t* idx_t;       // the same for the lists that are transposed for the dK/dV pass
+    int32_t* cnt_t;
 };
 bool attn_bwd_supported(const BwdArgs& a, const char** why);
 size_t attn_bwd_workspace_bytes(long long BH, const Geom& gq, const Geom& gk, int cap);
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why);
-// the dQ and dK/dV passes on tcgen05 (attn_bwd_tc.cu): head_dim 128, 64-token blocks, whole grids
-bool attn_bwd_tc_supported(const BwdArgs& a);
-cudaError_t launch_attn_bwd_tc(const BwdArgs& a, cudaStream_t st, const char** why);
+// the dQ and dK/dV passes on tcgen05 (attn_bwd_tc.cu): head_dim 128, whole grids.  A CTA owns a block of 64 or 128
+// tokens and streams 64-token units; the plan names the grids and the lists in those terms.
+struct BwdTcPlan {
+    Geom own_q, own_k;        // blocks of the CTAs of the dQ pass and of the dK/dV pass (64 or 128 tokens)
+    Geom unit_q, unit_k;      // the 64-token grids of the streamed tiles (query units in the dK/dV pass, key units in the dQ pass)
+    const int32_t* list_q;    // [B*H, own_q.nblk, cap_q] key units of every own query block
+    const int32_t* cnt_q;     // [B*H, own_q.nblk]
+    int cap_q;
+    const int32_t* toff;      // [B*H, own_k.nblk + 1]
+    const int32_t* tidx;      // [B*H, tidx_stride] query units of own key block j at toff[j] .. toff[j + 1]
+    long long tidx_stride;
+};
+bool attn_bwd_tc_supported(const BwdArgs& a, const BwdTcPlan& p);
+cudaError_t launch_attn_bwd_tc(const BwdArgs& a, const BwdTcPlan& p, cudaStream_t st, const char** why);
 
 // the same for 128-token query and key blocks (attn_tc128.cu)
 cudaError_t launch_attn_tc128(const AttnArgs& a, cudaStream_t st, const char** why);
