@@ -595,8 +595,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) bwd_dkdv_mma_kernel(const __gr
 //
 // The backward has no per-block state (no running maximum: lse is given), so a block of 128, 256 or 512 tokens is just
 // the union of 64-token pieces, and on whole grids those pieces are the blocks of a finer grid over the same tokens.
-// The tcgen05 passes work on 64-token blocks only; larger blocks reach them as that finer grid with the lists rewritten:
-// a query unit takes the list of its block, every selected key block becomes its units.
+// The tcgen05 passes stream 64-token tiles and own tiles of 64 or 128 tokens; the lists are rewritten in those terms: on
+// the row side a query unit takes the list of its block, on the value side a selected key block becomes its units.
 
 struct UnitSplit {
     Geom gu;         // the grid with the unit as block

@@ -1,27 +1,28 @@
-// Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128 and 64-token query and key blocks on whole
-// grids (larger blocks arrive as 64-token units, attn_bwd.cu): the dQ pass and the dK/dV pass, after the delta kernel
-// and the transposition of the block lists of attn_bwd.cu, which keeps head_dim 64 and ragged grids on warp-level MMAs.
-// Stands in for the Triton kernels _attn_bwd_dq_bsa_varlen_align and _attn_bwd_dkdv_bsa_varlen_align
+// Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128 on whole grids: the dQ pass and the dK/dV pass,
+// after the delta kernel and the transposition of the block lists of attn_bwd.cu, which keeps head_dim 64 and ragged grids
+// on warp-level MMAs.  A CTA owns a block of 64 or 128 tokens (kM rows: M=64 or M=128 MMAs) and streams 64-token tiles;
+// attn_bwd.cu writes the lists in those terms (larger blocks are taken as 64-token units).  Stands in for the Triton
+// kernels _attn_bwd_dq_bsa_varlen_align and _attn_bwd_dkdv_bsa_varlen_align
 // (longcat_video/block_sparse_attention/flash_attn_bsa_varlen_mask.py:289-945).
 //
-// Both passes are one kernel with the roles of the operands exchanged.  A CTA owns one 64-row tile pair (A1, A2) and walks
-// a list of tile pairs (B1, B2); per list entry
+// Both passes are one kernel with the roles of the operands exchanged.  A CTA owns one tile pair (A1, A2) of kM rows and
+// walks a list of 64-row tile pairs (B1, B2); per list entry
 //
 //   dQ pass   (CTA = query block i, list = its key blocks j):  A1 = Q_i  A2 = dO_i  B1 = K_j  B2 = V_j
 //       S  = A1 B1^T        dP  = A2 B2^T        dS  = P o (dP - delta_i) * scale        dQ_i += dS B1
 //   dK/dV pass (CTA = key block j, list = the query blocks i that selected it):  A1 = K_j  A2 = V_j  B1 = Q_i  B2 = dO_i
 //       S^T = A1 B1^T       dP^T = A2 B2^T       P^T, dS^T as above, transposed          dV_j += P^T B2   dK_j += dS^T B1
 //
-// with P = exp2(S * scale * log2(e) - lse * log2(e)).  S and dP are M64 N64 K128 MMAs with both operands in shared memory
-// (fp32 in TMEM); P and dS are written back to TMEM in the input dtype and are the A operands of the M64 N128 K64 MMAs
+// with P = exp2(S * scale * log2(e) - lse * log2(e)).  S and dP are (M = kM) N64 K128 MMAs with both operands in shared
+// memory (fp32 in TMEM); P and dS are written back to TMEM in the input dtype and are the A operands of the N128 K64 MMAs
 // that accumulate the gradients in TMEM over the whole list, with the streamed tile as MN-major B operand: a tile is
 // loaded once (two 5-D TMA boxes of 64 columns, 128-byte swizzle) and serves as K-major operand of the first
 // contraction and as MN-major operand of the last.  Nothing is recomputed within a pass, nothing goes through shared
 // memory between the contractions, and no gradient is accumulated with atomics.
 //
-//   warps 0-7 : arithmetic.  A thread serves one TMEM lane = one row of the 64 x 64 tile (lanes 0-15 of every 32-lane
-//               quadrant hold an M=64 accumulator)
-//   warp 8    : TMA producer: the CTA's own tiles once, then a ring of five (B1, B2) slots; in the dK/dV pass also the
+//   warps 0-7 : arithmetic.  A thread serves one TMEM lane = one row of the kM x 64 tile (an M=128 accumulator has row r in
+//               lane r, an M=64 one occupies lanes 0-15 of every 32-lane quadrant)
+//   warp 8    : TMA producer: the CTA's own tiles once, then a ring of five (four for kM = 128) (B1, B2) slots; in the dK/dV pass also the
 //               query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the same barrier
 //               (bwd_stats_kernel lays them out per block)
 //   warp 9    : issues every MMA, one elected lane
