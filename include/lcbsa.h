@@ -208,8 +208,9 @@ int lcbsa_attn_fwd_scatter(const LcbsaTensor* q, const LcbsaTensor* k, const Lcb
  * rowsum(dout * out) and, for every key block, the ascending list of the query blocks that selected it (built through a
  * bitmap of (key block, query block) pairs; the entries of one list are taken as distinct); no atomics on the gradients,
  * so two calls give the same bits.  Every row of dq, dk, dv that exists is written (rows of blocks that nothing selected
- * get zeros).  head_dim 128 on whole grids runs on tcgen05 (TMA tiles, accumulators in TMEM; a CTA owns a block
- * of 64 or 128 tokens, larger blocks are taken as 64-token units); head_dim 64 and ragged grids on warp-level MMAs, with the same bits for 64-token blocks (the environment
+ * get zeros).  head_dim 128 runs on tcgen05 (TMA tiles, accumulators in TMEM; a CTA owns a block of 64 or 128
+ * tokens, larger blocks are taken as 64-token units; on ragged grids 64-token blocks in bf16); head_dim 64 and the
+ * remaining ragged cases on warp-level MMAs, with the same bits for 64-token blocks (the environment
  * variable LCBSA_BWD_IMPL=mma keeps the warp-level kernels, for comparisons).
  */
 size_t lcbsa_attn_bwd_workspace_bytes(const LcbsaTensor* q, const LcbsaGrid* gq, const LcbsaGrid* gk, int cap);

@@ -606,7 +606,7 @@ struct UnitSplit {
 
 // halves the block (w first, then h, then t) until 64 tokens are left; false when that cannot be done
 bool split_units64(const Geom& g, UnitSplit* out) {
-    if (g.ragged || g.bs < kTile) return false;
+    if (g.bs < kTile || (g.ragged && g.bs != kTile)) return false;  // partial blocks are only taken whole
     int ut = g.ct, uh = g.ch, uw = g.cw;
     while (ut * uh * uw > kTile) {
         if (uw % 2 == 0) uw /= 2;

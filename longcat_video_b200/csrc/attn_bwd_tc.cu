@@ -1,8 +1,8 @@
-// Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128 on whole grids: the dQ pass and the dK/dV pass,
-// after the delta kernel and the transposition of the block lists of attn_bwd.cu, which keeps head_dim 64 and ragged grids
-// on warp-level MMAs.  A CTA owns a block of 64 or 128 tokens (kM rows: M=64 or M=128 MMAs) and streams 64-token tiles;
-// attn_bwd.cu writes the lists in those terms (larger blocks are taken as 64-token units).  Stands in for the Triton
-// kernels _attn_bwd_dq_bsa_varlen_align and _attn_bwd_dkdv_bsa_varlen_align
+// Block-sparse attention backward on TMA + tcgen05 + TMEM for head_dim 128: the dQ pass and the dK/dV pass, after the delta
+// kernel and the transposition of the block lists of attn_bwd.cu (which keeps head_dim 64, and ragged grids in fp16 or with
+// blocks above 64 tokens, on warp-level MMAs).  A CTA owns a block of 64 or 128 tokens (kM rows: M=64 or M=128 MMAs) and
+// streams 64-token tiles; attn_bwd.cu writes the lists in those terms (larger blocks are taken as 64-token units).
+// Stands in for the Triton kernels _attn_bwd_dq_bsa_varlen_align and _attn_bwd_dkdv_bsa_varlen_align
 // (longcat_video/block_sparse_attention/flash_attn_bsa_varlen_mask.py:289-945).
 //
 // Both passes are one kernel with the roles of the operands exchanged.  A CTA owns one tile pair (A1, A2) of kM rows and
@@ -20,11 +20,16 @@
 // contraction and as MN-major operand of the last.  Nothing is recomputed within a pass, nothing goes through shared
 // memory between the contractions, and no gradient is accumulated with atomics.
 //
+// Ragged grids (64-token blocks, bf16): the boxes of partial blocks are zero-filled by TMA outside the grid; a key outside
+// the grid then has K = V = 0 and a query row outside has Q = dO = 0, so every term they enter is a finite number times
+// zero and needs no mask (P of such a key is 2^(-lse * log2 e), finite in fp32 and bf16; fp16 could overflow, so fp16 keeps
+// ragged grids on the warp-level kernels); rows outside the grid are not stored.
+//
 //   warps 0-7 : arithmetic.  A thread serves one TMEM lane = one row of the kM x 64 tile (an M=128 accumulator has row r in
 //               lane r, an M=64 one occupies lanes 0-15 of every 32-lane quadrant)
-//   warp 8    : TMA producer: the CTA's own tiles once, then a ring of five (four for kM = 128) (B1, B2) slots; in the dK/dV pass also the
-//               query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the same barrier
-//               (bwd_stats_kernel lays them out per block)
+//   warp 8    : TMA producer: the CTA's own tiles once, then a ring of five (four for kM = 128) (B1, B2) slots; in the
+//               dK/dV pass also the query block's 64 (lse * log2 e) and 64 delta values per slot, by a bulk copy onto the
+//               same barrier (bwd_stats_kernel lays them out per block)
 //   warp 9    : issues every MMA, one elected lane
 //
 // TMEM and the order of the MMAs.  P and dS (16-bit pairs) have columns of their own, twice, in both passes: the values
@@ -123,7 +128,8 @@ __device__ __forceinline__ void load_tile_pair(uint32_t dst, const CUtensorMap* 
 }
 
 // lse * log2(e) and delta of every query row, laid out per 64-token block in slot order, so that a block's 128 values are
-// one contiguous 512-byte piece (whole grids only)
+// one contiguous 512-byte piece.  Slots of a partial block that lie outside the grid get zeros (their q and dO rows are
+// zero-filled by TMA, so every term they enter is a finite number times zero).
 __global__ void __launch_bounds__(256) bwd_stats_kernel(const float* lse, const float* delta, Geom g, long long Sq, long long total,
                                                         float* stats) {
     const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -135,10 +141,12 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const float* lse, const 
     int lt, lh, lw, bt, bhh, bw;
     slot_coords(g, r, lt, lh, lw);
     block_coords(g, blk, bt, bhh, bw);
-    const long long tok = ((long long)(bt * g.ct + lt) * g.H + (bhh * g.ch + lh)) * g.W + (bw * g.cw + lw);
+    const int tt = bt * g.ct + lt, hh = bhh * g.ch + lh, ww = bw * g.cw + lw;
+    const bool inside = tt < g.T && hh < g.H && ww < g.W;
+    const long long tok = ((long long)tt * g.H + hh) * g.W + ww;
     float* dst = stats + (bh * g.nblk + blk) * kStatsFloats;
-    dst[r] = lse[bh * Sq + tok] * 1.4426950408889634f;
-    dst[kBlk + r] = delta[bh * Sq + tok];
+    dst[r] = inside ? lse[bh * Sq + tok] * 1.4426950408889634f : 0.f;
+    dst[kBlk + r] = inside ? delta[bh * Sq + tok] : 0.f;
 }
 
 // 32 columns of this thread's accumulator row -> 64 bytes of the row in global memory (input dtype)
@@ -355,16 +363,20 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
         const int row = kM == 128 ? wq * 32 + lane : wq * 16 + (lane & 15);
         const uint32_t t_lane = (uint32_t)(wq * 32) << 16;
         // the token of this row (rows of a block are its tokens in t, h, w order)
+        // A row of a partial block that lies outside the grid is computed on zero-filled operands and never stored.
         long long tok;
+        bool row_inside;
         {
             int lt, lh, lw, bt, bhh, bw;
             slot_coords(P.ga, row, lt, lh, lw);
             block_coords(P.ga, own, bt, bhh, bw);
-            tok = ((long long)(bt * P.ga.ct + lt) * P.ga.H + (bhh * P.ga.ch + lh)) * P.ga.W + (bw * P.ga.cw + lw);
+            const int tt = bt * P.ga.ct + lt, hh = bhh * P.ga.ch + lh, ww = bw * P.ga.cw + lw;
+            row_inside = tt < P.ga.T && hh < P.ga.H && ww < P.ga.W;
+            tok = ((long long)tt * P.ga.H + hh) * P.ga.W + ww;
         }
         // dQ pass: this thread's query row has one lse and one delta for the whole list
         float my_l2 = 0.f, my_dl = 0.f;
-        if (kMode == 0 && n > 0) {
+        if (kMode == 0 && n > 0 && row_inside) {
             my_l2 = P.lse[(long long)bh * P.Sq + tok] * 1.4426950408889634f;
             my_dl = P.delta[(long long)bh * P.Sq + tok];
         }
@@ -465,7 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 32; ++j) acc[j] = 0u;  // nothing selected this block: its gradient is zero
                     }
-                    if (kM == 128 || lane < 16) store_row32<kBf16>(row_ptr, col_lo + 32 * ch, acc);
+                    if ((kM == 128 || lane < 16) && row_inside) store_row32<kBf16>(row_ptr, col_lo + 32 * ch, acc);
                 }
             }
         }
@@ -495,9 +507,7 @@ cudaError_t launch_pass_any(bool bf16, int rows, const BwdTcParams& P, unsigned 
     return bf16 ? launch_pass<true, kMode, 64>(P, own_blocks, BH, st) : launch_pass<false, kMode, 64>(P, own_blocks, BH, st);
 }
 
-bool grid_fits(const Geom& g, int rows) {
-    return !g.ragged && g.bs == rows && g.ct <= 256 && g.ch <= 256 && g.cw <= 256;
-}
+bool grid_fits(const Geom& g, int rows) { return g.bs == rows && g.ct <= 256 && g.ch <= 256 && g.cw <= 256; }
 
 }  // namespace
 
@@ -507,6 +517,7 @@ bool attn_bwd_tc_supported(const BwdArgs& a, const BwdTcPlan& p) {
     if (a.dtype != LCBSA_BF16 && a.dtype != LCBSA_FP16) return false;
     if (a.D != kD) return false;
     if (!grid_fits(p.unit_q, 64) || !grid_fits(p.unit_k, 64)) return false;
+    if ((p.unit_q.ragged || p.unit_k.ragged) && a.dtype != LCBSA_BF16) return false;  // see the note on ragged grids above
     if (!grid_fits(p.own_q, 64) && !grid_fits(p.own_q, 128)) return false;
     if (!grid_fits(p.own_k, 64) && !grid_fits(p.own_k, 128)) return false;
     if (encode_fn() == nullptr) return false;
@@ -526,7 +537,7 @@ cudaError_t launch_attn_bwd_tc(const BwdArgs& a, const BwdTcPlan& p, cudaStream_
     const long long Sq = (long long)a.gq.T * a.gq.H * a.gq.W;
     const long long BH = (long long)a.B * a.H;
     {
-        const long long total = BH * Sq;  // whole grids: every 64-token query unit has its 64 rows
+        const long long total = BH * p.unit_q.nblk * kBlk;  // every slot of every 64-token query unit
         bwd_stats_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.lse, a.delta, p.unit_q, Sq, total, a.stats);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;

@@ -156,7 +156,7 @@ struct BwdArgs {
 bool attn_bwd_supported(const BwdArgs& a, const char** why);
 size_t attn_bwd_workspace_bytes(long long BH, const Geom& gq, const Geom& gk, int cap);
 cudaError_t launch_attn_bwd(BwdArgs a, void* workspace, cudaStream_t st, const char** why);
-// the dQ and dK/dV passes on tcgen05 (attn_bwd_tc.cu): head_dim 128, whole grids.  A CTA owns a block of 64 or 128
+// the dQ and dK/dV passes on tcgen05 (attn_bwd_tc.cu): head_dim 128.  A CTA owns a block of 64 or 128
 // tokens and streams 64-token units; the plan names the grids and the lists in those terms.
 struct BwdTcPlan {
     Geom own_q, own_k;        // blocks of the CTAs of the dQ pass and of the dK/dV pass (64 or 128 tokens)

@@ -129,6 +129,7 @@ def test_autograd_through_the_entry_point_and_determinism():
 # ---- the tcgen05 passes (head_dim 128, 64-token blocks, whole grids) on the shapes only they see
 
 TC_CASES = {
+    "tc_ragged_hw": Workload("tc_ragged_hw", 6106, 1, 2, 128, (8, 10, 13), (8, 10, 13), (4, 4, 4), 0.5, torch.bfloat16, "normal"),
     "tc_fp16": Workload("tc_fp16", 6101, 1, 2, 128, (8, 8, 16), (8, 8, 16), (4, 4, 4), 0.5, torch.float16, "normal"),
     "tc_batch2": Workload("tc_batch2", 6102, 2, 3, 128, (4, 8, 16), (4, 8, 16), (4, 4, 4), 0.5, torch.bfloat16, "normal"),
     "tc_cross": Workload("tc_cross", 6103, 1, 2, 128, (4, 8, 8), (12, 8, 8), (4, 4, 4), 0.75, torch.bfloat16, "normal"),
