@@ -19,8 +19,9 @@
 // Tiles are 64 x 64 whatever the block sizes (multiples of 64 tokens): a block of 128 or more tokens is a run of
 // 64-row tiles in slot order.  The contractions run on the tensor cores through warp-level mma (mma.sync m16n8k16 fed by
 // ldmatrix, fp32 accumulation); P and dS are rounded to the input dtype before they enter a contraction, as in the
-// forward.  The two passes of this file serve every supported shape; head_dim 128 on whole grids is taken by the tcgen05
-// passes of attn_bwd_tc.cu instead (same delta kernel, same transposition; blocks above 64 tokens as 64-token units).
+// forward.  The two passes of this file serve every supported shape; head_dim 128 is taken by the tcgen05 passes of
+// attn_bwd_tc.cu instead (same delta kernel, same transposition; blocks above 64 tokens as 64-token units), except for
+// ragged grids in fp16 or with blocks above 64 tokens.
 #include "mma_common.cuh"
 
 namespace lcbsa {
@@ -662,7 +663,7 @@ cudaError_t run_bwd(const BwdArgs& a, cudaStream_t st, const char** why) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    // head_dim 128 on whole grids: the tcgen05 passes.  Their CTAs own a block of 64 or 128 tokens and stream 64-token
+    // head_dim 128: the tcgen05 passes.  Their CTAs own a block of 64 or 128 tokens and stream 64-token
     // units, so the lists are rewritten in those terms: for the dQ pass (own query block -> key units) and for the dK/dV
     // pass (query unit -> own key block, which is then transposed).
     BwdTcPlan plan{};
