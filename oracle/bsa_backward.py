@@ -10,9 +10,13 @@ bsa_interface.py:570-596) differentiates the attention of the forward with the b
 so the oracle builds the token-level mask from the lists (as ``create_mask_from_indices_varlen``,
 bsa_interface.py:131-149, expanded to tokens) and lets autograd differentiate a float64 masked softmax attention.
 
-Parity unpinned against the reference's own outputs in this repository: the reference's backward exists only as Triton
-kernels, which need a GPU, so no fixture can be generated where the fixtures are made.  On a machine with a GPU and the
-reference's modules at hand, tests/test_gpu_reference_triton.py compares this library's gradients with the reference's.
+Pinned on fixtures made from the reference: its backward exists only as Triton kernels, which need a GPU, but the forward
+it differentiates has a CPU formulation made of the reference's own functions (block rearrangement, pooling, selection,
+``create_mask_from_indices_varlen``) around a masked fp32 ``scaled_dot_product_attention``.  tests/golden/
+make_golden_backward.py runs that and lets torch autograd take the gradients; tests/test_oracle_backward.py holds this
+oracle to them (rel-L2 3e-7 to 4e-7 on the three fixtures: fp32 against float64 arithmetic).  On a machine with a GPU and
+the reference's modules at hand, tests/test_gpu_reference_triton.py also compares this library's gradients with those of
+the reference's Triton kernels.
 """
 from __future__ import annotations
 

@@ -19,3 +19,16 @@ CASES = {
     "bf16_ties_720p": (Workload("bf16_ties_720p", 1003, 1, 1, 128, (24, 44, 80), (24, 44, 80), (4, 4, 4), 0.9375,
                                 torch.bfloat16, "scaled_lowrank"), False),
 }
+
+# Backward: gradients of the reference's "block-select + masked SDPA" path under torch autograd (make_golden_backward.py)
+BWD_CASES = {
+    "bwd_blocks64": Workload("bwd_blocks64", 8001, 1, 1, 128, (4, 8, 8), (4, 8, 8), (4, 4, 4), 0.5, torch.bfloat16, "normal"),
+    "bwd_blocks128_cross": Workload("bwd_blocks128_cross", 8002, 1, 1, 128, (4, 8, 8), (8, 8, 8), (4, 4, 8), 0.5, torch.bfloat16, "normal"),
+    "bwd_fp16_d64": Workload("bwd_fp16_d64", 8003, 1, 2, 64, (4, 8, 8), (4, 8, 8), (2, 4, 8), 0.5, torch.float16, "normal"),
+}
+
+
+def make_dout(wl: Workload) -> torch.Tensor:
+    """The seeded upstream gradient of a backward case, ``[B, H, Sq, D]`` in the case's dtype."""
+    g = torch.Generator().manual_seed(wl.seed + 7)
+    return (torch.randn(wl.batch, wl.heads, wl.sq, wl.head_dim, generator=g) * 0.5).to(wl.dtype)

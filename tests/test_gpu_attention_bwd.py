@@ -223,3 +223,18 @@ def test_tcgen05_passes_equal_the_warp_level_kernels_at_scale(monkeypatch):
         r = rel_l2(a.float().cpu(), b.float().cpu())
         print(f"BWD tcgen05 vs warp-level, 480p, {n}: rel-L2 {r:.2e}")
         assert torch.isfinite(a.float()).all() and r <= 5e-3, f"{n} rel-L2 {r}"
+
+
+# ---- against the fixtures made from the reference's own CPU path under torch autograd (tests/golden/make_golden_backward.py)
+
+from tests.golden.cases import BWD_CASES  # noqa: E402
+from tests.test_oracle_backward import load_backward_fixture  # noqa: E402
+
+
+@pytest.mark.parametrize("name", list(BWD_CASES))
+def test_gradients_against_the_reference_fixtures(name):
+    """Reference lists -> this library's forward and backward -> the gradients torch autograd took through the reference's
+    block mask and fp32 scaled_dot_product_attention."""
+    wl, q, k, v, do, idx, cnt, want = load_backward_fixture(name)
+    _, dq, dk, dv = _forward_and_backward(wl, q, k, v, do, idx, cnt)
+    print(f"BWD PARITY reference fixture {name}:", _compare(name, (dq, dk, dv), want))

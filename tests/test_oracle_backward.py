@@ -39,3 +39,39 @@ def test_gradients_against_finite_differences():
             args_m = [xm if n == name else t for n, t in (("q", q), ("k", k), ("v", v))]
             fd = (loss(*args_p) - loss(*args_m)) / (2 * eps)
             assert abs(fd - float(gx[pos])) <= 1e-6 * max(1.0, abs(fd)), (name, pos, fd, float(gx[pos]))
+
+
+# ---- pinned on the reference: gradients of the reference's CPU path under torch autograd (tests/golden/make_golden_backward.py)
+
+import os  # noqa: E402
+
+import numpy as np  # noqa: E402
+import pytest  # noqa: E402
+
+from tests.golden.cases import BWD_CASES, make_dout  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load_backward_fixture(name):
+    wl = BWD_CASES[name]
+    f = np.load(os.path.join(GOLDEN, name + ".npz"))
+    q, k, v = make_qkv(wl)
+    do = make_dout(wl)
+    got = [q.double().sum().item(), k.double().sum().item(), v.double().sum().item(), do.double().sum().item()]
+    assert np.allclose(f["checksum"], got, rtol=0, atol=0), "the seeded inputs are not the ones the fixture was made from"
+    idx = torch.sort(torch.from_numpy(f["idx"].astype("int32")), dim=-1).values.contiguous()
+    cnt = torch.from_numpy(f["lens"].astype("int32"))
+    grads = tuple(torch.from_numpy(f[n]) for n in ("dq", "dk", "dv"))
+    return wl, q, k, v, do, idx, cnt, grads
+
+
+@pytest.mark.parametrize("name", list(BWD_CASES))
+def test_backward_oracle_against_the_reference_fixtures(name):
+    """The float64 oracle on the reference's lists against the fp32 gradients that torch autograd took through the
+    reference's own block mask and scaled_dot_product_attention: rel-L2 <= 1e-5 (fp32 against float64 arithmetic)."""
+    wl, q, k, v, do, idx, cnt, want = load_backward_fixture(name)
+    _, dq, dk, dv = OB.attention_backward(q, k, v, do, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk)
+    for n, g, w in zip(("dq", "dk", "dv"), (dq, dk, dv), want):
+        r = float((g.double() - w.double()).norm() / w.double().norm())
+        assert r <= 1e-5, f"{name} {n}: rel-L2 {r}"
