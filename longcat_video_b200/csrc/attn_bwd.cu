@@ -775,10 +775,11 @@ BwdLayout bwd_layout(long long BH, const Geom& gq, const Geom& gk, int cap) {
     l.tidx = off;   off += up((size_t)BH * Nq * capu * sizeof(int32_t));
     l.bitmap = off; off += up((size_t)BH * Nk * ((Nq + 31) / 32) * sizeof(uint32_t));
     l.stats = off;  off += up((size_t)BH * Sq * 2 * sizeof(float));
-    l.idx_u = off;  off += up((size_t)BH * Nq * capu * sizeof(int32_t));
-    l.cnt_u = off;  off += up((size_t)BH * Nq * sizeof(int32_t));
-    l.idx_t = off;  off += up((size_t)BH * Nq * capu * sizeof(int32_t));
-    l.cnt_t = off;  off += up((size_t)BH * Nq * sizeof(int32_t));
+    const size_t rewritten = Uq * Uk > 1 ? 1 : 0;  // 64-token blocks on both sides: the lists are used as they are
+    l.idx_u = off;  off += up(rewritten * BH * Nq * capu * sizeof(int32_t));
+    l.cnt_u = off;  off += up(rewritten * BH * Nq * sizeof(int32_t));
+    l.idx_t = off;  off += up(rewritten * BH * Nq * capu * sizeof(int32_t));
+    l.cnt_t = off;  off += up(rewritten * BH * Nq * sizeof(int32_t));
     l.total = off;
     return l;
 }
