@@ -16,6 +16,8 @@ One step = one attention layer's BSA forward over one batch of inputs.  Rank 0 p
   literal_720p   a short leg on BASELINE's literal 24x45x80 grid (ragged: through ``allow_ragged=True``).
   default_blocks_720p  two short legs on the same tensors with the entry point's default [4, 4, 8] blocks (128 tokens):
              at the headline's sparsity and with every parameter left at its default (sparsity 0.875).
+  backward_720p_8heads  side figure: dq, dk, dv of the first 8 heads of the same tensors (lcbsa_attn_bwd), with the headline's
+             blocks and with every parameter at its default; bench_backward.py is the benchmark of the backward proper.
   gpu_reference  the reference's own Triton BSA (baseline/_ref, see baseline/install_reference.py) timed on the
              same GPU and inputs, outside the timed region of this library; absent checkout -> "unavailable".
   cpu_baseline  the reference's PyTorch block-select + masked-SDPA path (oracle/reference_path.py) on the
@@ -209,6 +211,40 @@ def gpu_reference_leg(wl, q, k, v, params, flops, steps=5, warmup=2):
             **R.versions()}
 
 
+def backward_leg(B, L, q, k, v, wl, heads=8, steps=3, warmup=2):
+    """Side figure: the backward (lcbsa_attn_bwd) of the first ``heads`` heads of the tensors on the device, for the lists the
+    forward selects; same call sequence as bench_backward.py.  Returns a record, or the reason why there is none."""
+    try:
+        qs, ks, vs = (t[:, :heads].contiguous() for t in (q, k, v))
+        g = torch.Generator().manual_seed(11)
+        do = (torch.randn(qs.shape, generator=g) * 0.5).to(qs.dtype).to(qs.device)
+        scale = wl.head_dim ** -0.5
+        idx, cnt = B.get_select_indices(qs, ks, wl.grid_q, wl.grid_k, wl.sparsity, None, wl.chunk, wl.chunk)
+        nsel = int(cnt.flatten()[0])
+        o, lse = B.attn_fwd_bsa_varlen(qs, ks, vs, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk, return_lse=True)
+
+        def step():
+            return B.attn_bwd_bsa_varlen(do, qs, ks, vs, o, lse, scale, idx, cnt, wl.grid_q, wl.grid_k, wl.chunk, wl.chunk)
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        L.check(L.lib().lcbsa_check_device_status())
+        ms = a.elapsed_time(b) / steps
+        flops = 2.5 * algorithmic_flops(wl, heads, nsel)  # five contractions per (query block, key block) against the forward's two
+        return {"workload": wl.name, "heads": heads, "block": list(wl.chunk), "selected_blocks": nsel, "steps": steps, "ms_backward": ms,
+                "algorithmic_tflop": flops / 1e12, "backward_tflops": flops / ms / 1e9,
+                "what": "dq, dk, dv for the lists of the forward (lcbsa_attn_bwd); bench_backward.py times the reference's Triton backward beside it"}
+    except Exception as e:  # noqa: BLE001  (a side figure must not take the headline down)
+        return {"unavailable": f"{e!r}"[:300]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -222,6 +258,7 @@ def main():
     ap.add_argument("--skip-literal", action="store_true", help="no extra leg on the literal 24x45x80 grid")
     ap.add_argument("--skip-blocks128", action="store_true", help="no extra leg with the default [4, 4, 8] blocks")
     ap.add_argument("--skip-gpu-reference", action="store_true", help="do not time the reference's Triton kernels")
+    ap.add_argument("--skip-backward", action="store_true", help="no side figure for the backward")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -354,6 +391,11 @@ def main():
             del bt, bi, bc
         blocks128["note"] = "the headline stays on BASELINE's 4x4x4 blocks; these legs run the same tensors with the entry point's default block shape"
 
+    # ------------------------------------------------------------------ backward of 8 heads, side figure
+    backward = None
+    if wl.name == "720p_legal" and not args.skip_backward:
+        backward = {"blocks_4x4x4": backward_leg(B, L, q, k, v, wl), "all_defaults": backward_leg(B, L, q, k, v, WORKLOADS["720p_defaults"])}
+
     # ------------------------------------------------------------------ the reference's Triton kernels on this GPU
     gpu_reference = None
     if not args.skip_gpu_reference:
@@ -398,7 +440,7 @@ def main():
                        "algorithmic_tflop": flops / 1e12, "ms_select": ms_select, "ms_attention": ms_attn,
                        "timed_call": "flash_attn_bsa_3d, eager", "ms_per_step_cuda_graph": ms_graph,
                        "l2": "inputs (q,k,v,out) exceed the 126 MB L2; no flush between iterations", "parallelism": "1 GPU",
-                       "literal_720p": literal, "default_blocks_720p": blocks128},
+                       "literal_720p": literal, "default_blocks_720p": blocks128, "backward_720p_8heads": backward},
             "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_reference": gpu_reference, "clocks": clocks, "gpu_launches": gpu_launches}
     print(json.dumps(line))
